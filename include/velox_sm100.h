@@ -1,0 +1,161 @@
+/*
+ * velox_sm100 — C ABI of the B200 (sm_100a) quantized-linear kernel set for velox-inferer.
+ *
+ * These are the `extern "C"` launchers a `velox-variant` crate binds for the `Backend` linear
+ * family on NVFP4, FP8-E4M3-per-row and GGML Q4_K weights. Conventions follow the reference's
+ * launchers (crates/velox-cuda/kernels/velox_common.cuh:13-14, crates/velox-cuda/src/lib.rs:85-112):
+ *
+ *   return 0        success (work queued on the launch stream; nothing is synchronised)
+ *   return  > 0     a cudaError_t
+ *   return -1       VELOX_ERR_UNSUPPORTED: shape/format this kernel set does not serve; the
+ *                   caller falls back to the portable path
+ *   return -2       VELOX_ERR_SHAPE: arguments the reference's check::linear would reject
+ *                   (crates/velox-core/src/check.rs:100-131); the Rust side raises Error::Shape
+ *                   before the call, so a binding never sees this code in practice
+ *
+ * All pointers are device pointers unless stated. Weight pointers address the parent payload in
+ * its stored layout (crates/velox-core/src/format.rs:147-160), 256-byte aligned as cudaMalloc
+ * returns it. Buffers are borrowed for the duration of the queued work.
+ *
+ * Streams: like the reference's launchers (per-thread default stream, no stream argument) the
+ * launch stream is implicit: cudaStreamPerThread unless the calling thread chose another with
+ * velox_sm100_set_stream. Launchers do not synchronise, read back or allocate, except for
+ * grow-only private scratch on first use of a larger size (the reference's VeloxScratch rule,
+ * velox_common.cuh:49-70).
+ */
+#ifndef VELOX_SM100_H
+#define VELOX_SM100_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VELOX_ERR_UNSUPPORTED (-1)
+#define VELOX_ERR_SHAPE (-2)
+
+/* Weight format codes: crates/velox-cuda/src/portable.rs:197-216. */
+#define VELOX_FMT_FP8_ROW_BF16 2
+#define VELOX_FMT_NVFP4 3
+#define VELOX_FMT_GGML_Q4_K 17
+
+/* ActPolicy (crates/velox-core/src/backend.rs:757-780). */
+#define VELOX_POLICY_A16_ONLY 0
+#define VELOX_POLICY_ALLOW_A8 1
+#define VELOX_POLICY_ALLOW_A4 2
+
+/* ActQuant (crates/velox-core/src/backend.rs:786-806). */
+#define VELOX_ACT_EXACT 0
+#define VELOX_ACT_BF16 1
+#define VELOX_ACT_FP8_ROW 2
+#define VELOX_ACT_NVFP4 3
+
+/* WeightView (crates/velox-core/src/backend.rs:826-895): rows [row_begin, row_begin+rows) of an
+ * encoded parent [n, k]. `policy`/`divisor` carry the view's ActPolicy. */
+typedef struct velox_sm100_view {
+    const uint8_t* w;
+    int32_t format;
+    int32_t policy;
+    int64_t n;
+    int64_t k;
+    int64_t row_begin;
+    int32_t rows;
+    float divisor;
+} velox_sm100_view;
+
+/* LinearPart + LinearDst (backend.rs:847-867): one view written to columns [col, col+rows) of a
+ * destination with row stride ld. */
+typedef struct velox_sm100_part {
+    velox_sm100_view view;
+    float* y;
+    int64_t ld;
+    int64_t col;
+} velox_sm100_part;
+
+/* Library / build information. Returns the ABI version (1). */
+int velox_sm100_abi_version(void);
+
+/* Launch stream of the calling thread (a cudaStream_t); NULL restores cudaStreamPerThread.
+ * Replaces nothing in the reference: its launchers always use the per-thread default stream
+ * (crates/velox-build/src/lib.rs:120-129). */
+int velox_sm100_set_stream(void* stream);
+
+/* The rounding `linear` applies to x for this view at m rows (Backend::linear_act,
+ * backend.rs:933-937; CudaKernels::linear_act, crates/velox-cuda/src/lib.rs:578). Returns a
+ * VELOX_ACT_* code (>= 0) or a negative error. For VELOX_ACT_NVFP4, *divisor_out (host pointer,
+ * may be NULL) receives the divisor. Never rounds further than the view's policy allows. */
+int velox_sm100_linear_act(const velox_sm100_view* view, int m, float* divisor_out);
+
+/* y[m, rows] = x[m, k] . W^T with the view's policy fixed to A16Only. Same signature as
+ * velox_portable_linear (crates/velox-cuda/src/portable.rs:81-91; kernels/portable_model.cu:1899). */
+int velox_sm100_linear(const float* x, const uint8_t* w, int format, long long n, long long k,
+                       long long row_begin, int rows, int m, float* y);
+
+/* Backend::linear for a view with an activation policy (backend.rs:925-932). yb (may be NULL)
+ * receives the bf16 RNE twin of y, bit for bit. */
+int velox_sm100_linear_view(const float* x, const velox_sm100_view* view, int m, float* y,
+                            uint16_t* yb);
+
+/* Backend::linear_bf16 (backend.rs:1011-1021): the same result from x's bf16 twin. Served where
+ * velox_sm100_linear_act reports VELOX_ACT_BF16 (Backend::takes_bf16). y and yb: either may be
+ * NULL, not both. */
+int velox_sm100_linear_bf16(const uint16_t* xb, const velox_sm100_view* view, int m, float* y,
+                            uint16_t* yb);
+
+/* Backend::linear_swiglu (backend.rs:1102-1118): out[r][i] = silu(x_r . gate_i) * (x_r . up_i).
+ * gate and up: same width, format and k; any two views (adjacent in one parent in either order,
+ * or separate parents). Fused: no intermediate [m, 2w] buffer. outb (may be NULL): bf16 twin. */
+int velox_sm100_linear_swiglu(const float* x, const velox_sm100_view* gate,
+                              const velox_sm100_view* up, int m, float* out, uint16_t* outb);
+
+/* Backend::linear_swiglu_twin (backend.rs:1034-1048): the same from x's bf16 twin. */
+int velox_sm100_linear_swiglu_bf16(const uint16_t* xb, const velox_sm100_view* gate,
+                                   const velox_sm100_view* up, int m, float* out, uint16_t* outb);
+
+/* The rounding linear_swiglu applies (Backend::linear_swiglu_act, backend.rs:1130-1141). */
+int velox_sm100_linear_swiglu_act(const velox_sm100_view* gate, const velox_sm100_view* up, int m,
+                                  float* divisor_out);
+
+/* Backend::linears (backend.rs:938-958): several views of one x, each into a column range of its
+ * destination. `parts` is a HOST array. x may be NULL when xb (bf16 twin) is given and every
+ * part rounds to bf16. */
+int velox_sm100_linears(const float* x, const uint16_t* xb, const velox_sm100_part* parts,
+                        int nparts, int m);
+
+/* Exact decode of a view to f32 [rows, k]: the values format::decode_rows produces
+ * (crates/velox-core/src/format.rs:426-490), bit for bit. */
+int velox_sm100_dequant_rows(const velox_sm100_view* view, float* out);
+
+/* Activation quantisers, bit-exact with quant::quantize_activations (crates/velox-core/src/quant.rs:63-96).
+ * fp8row: codes [m, k] E4M3, scales[m] = amax/448. nvfp4: codes [m, k/2] (two E2M1 per byte, low
+ * nibble first), scale bytes in the weight format's 128x4 swizzled atoms (format.rs:345-354)
+ * over ceil(m/128)*128 rows. */
+int velox_sm100_quantize_act_fp8row(const float* x, int m, long long k, uint8_t* codes,
+                                    float* scales);
+int velox_sm100_quantize_act_nvfp4(const float* x, int m, long long k, float divisor,
+                                   uint8_t* codes, uint8_t* scale_atoms);
+
+/* NVFP4 weight construction on the device (round-to-nearest-even converters of quant.rs:9-59,
+ * layout and divisor convention of format::encode_nvfp4, format.rs:385-423). `amax` is max|w|
+ * over the matrix. Used to build benchmark-sized synthetic weights. */
+int velox_sm100_encode_nvfp4(const float* w, long long n, long long k, float amax,
+                             uint8_t* payload);
+
+/* Elementwise neighbours of the path. Signatures as the portable launchers
+ * (crates/velox-cuda/src/portable.rs:19-66; kernels/portable.cu:109-115, 1519-1550). */
+int velox_sm100_swiglu(const float* src, long long rows, int src_cols, int gate, int up, int width,
+                       float* out);
+int velox_sm100_silu_mul(float* gate, const float* up, long long len);
+int velox_sm100_add(float* acc, const float* x, long long len);
+/* Backend::add_rms_norm_twin (backend.rs:968-983): acc += x (x may be NULL: plain rms_norm of
+ * acc); y = rms_norm(acc) * (offset + weight); yb (may be NULL) = bf16 twin of y. */
+int velox_sm100_add_rms_norm_twin(float* acc, const float* x, const float* weight, float* y,
+                                  uint16_t* yb, int rows, int dim, float eps, int offset);
+/* f32 -> bf16 twin (RNE), as velox_bf16_bits (velox_common.cuh:74-82). */
+int velox_sm100_bf16_twin(const float* x, uint16_t* xb, long long len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

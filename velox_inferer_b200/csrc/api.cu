@@ -1,0 +1,308 @@
+// C ABI of the sm_100a quantized-linear kernel set (declared in include/velox_sm100.h): argument
+// checks as the reference's check::linear (crates/velox-core/src/check.rs:100-131), kernel
+// selection by (format, policy, m, k), and the launch-stream / scratch state the launchers share.
+#include <mutex>
+
+#include "common.cuh"
+#include "gemm.cuh"
+#include "kernels.cuh"
+
+namespace vx {
+
+static thread_local cudaStream_t g_stream = cudaStreamPerThread;
+cudaStream_t stream() { return g_stream; }
+void set_stream(cudaStream_t s) { g_stream = s ? s : cudaStreamPerThread; }
+
+struct Pool {
+    void* ptr = nullptr;
+    size_t cap = 0;
+};
+static std::mutex g_scratch_mu;
+static Pool g_pools[64][SCRATCH_SLOTS];
+
+void* scratch(ScratchSlot slot, size_t bytes) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    Pool& p = g_pools[dev][slot];
+    if (bytes > p.cap) {
+        size_t n = p.cap * 2 > bytes ? p.cap * 2 : bytes;
+        if (n < (1u << 20)) n = 1u << 20;
+        void* q = nullptr;
+        if (cudaMalloc(&q, n) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        p.ptr = q;  // the old buffer is kept alive: queued work or a captured graph may use it
+        p.cap = n;
+    }
+    return p.ptr;
+}
+
+int check_view(const velox_sm100_view* v) {
+    if (!v || !v->w) return VELOX_ERR_SHAPE;
+    if (v->n <= 0 || v->k <= 0) return VELOX_ERR_SHAPE;
+    switch (v->format) {
+        case VELOX_FMT_NVFP4:
+            if (v->n % 128 != 0 || v->k % 64 != 0) return VELOX_ERR_SHAPE;
+            break;
+        case VELOX_FMT_FP8_ROW_BF16:
+            break;
+        case VELOX_FMT_GGML_Q4_K:
+            if (v->k % 256 != 0) return VELOX_ERR_SHAPE;
+            break;
+        default:
+            return VELOX_ERR_UNSUPPORTED;
+    }
+    if (v->rows <= 0 || v->row_begin < 0 || v->row_begin + v->rows > v->n) return VELOX_ERR_SHAPE;
+    return 0;
+}
+
+enum Path { PATH_GEMV, PATH_GEMM_A4, PATH_GEMM_A8, PATH_GEMM_BF16, PATH_GENERIC };
+
+struct Plan {
+    Path path;
+    int act;
+    float divisor;
+};
+
+// Kernel and activation rounding for one view at m rows. The rounding never exceeds the view's
+// policy (crates/velox-conformance/src/lib.rs:64-74): bf16 is always permitted; FP8 rows need
+// AllowA8 or AllowA4; NVFP4 activations need AllowA4 and use its divisor.
+static Plan plan_for(const velox_sm100_view& v, int m) {
+    Plan p{PATH_GENERIC, VELOX_ACT_EXACT, 0.0f};
+    if (v.k % 64 != 0) return p;
+    if (m <= 16) {
+        p.path = PATH_GEMV;
+        p.act = VELOX_ACT_BF16;
+        return p;
+    }
+    if (!gemm_available()) return p;
+    if (v.format == VELOX_FMT_NVFP4 && v.policy == VELOX_POLICY_ALLOW_A4 && v.divisor > 0.0f) {
+        p.path = PATH_GEMM_A4;
+        p.act = VELOX_ACT_NVFP4;
+        p.divisor = v.divisor;
+        return p;
+    }
+    if (v.format == VELOX_FMT_FP8_ROW_BF16 && v.policy != VELOX_POLICY_A16_ONLY && v.k % 128 == 0) {
+        p.path = PATH_GEMM_A8;
+        p.act = VELOX_ACT_FP8_ROW;
+        return p;
+    }
+    p.path = PATH_GEMM_BF16;
+    p.act = VELOX_ACT_BF16;
+    return p;
+}
+
+static int run(const LinearArgs& a, const Plan& p) {
+    int rc = VELOX_ERR_UNSUPPORTED;
+    switch (p.path) {
+        case PATH_GEMV:
+            rc = gemv(a);
+            break;
+        case PATH_GEMM_A4:
+        case PATH_GEMM_A8:
+        case PATH_GEMM_BF16:
+            rc = gemm_linear(a, p.act, p.divisor);
+            break;
+        default:
+            break;
+    }
+    if (rc == VELOX_ERR_UNSUPPORTED) {
+        LinearArgs g = a;
+        g.round_x = p.act == VELOX_ACT_BF16;
+        if (p.act == VELOX_ACT_FP8_ROW || p.act == VELOX_ACT_NVFP4) return VELOX_ERR_UNSUPPORTED;
+        rc = linear_generic(g);
+    }
+    return rc;
+}
+
+static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_view* view, int m,
+                         float* y, uint16_t* yb, long long ld, long long col) {
+    if (m <= 0 || (!x && !xb) || (!y && !yb)) return VELOX_ERR_SHAPE;
+    int rc = check_view(view);
+    if (rc != 0) return rc;
+    LinearArgs a{};
+    a.w = *view;
+    a.swiglu = 0;
+    a.x = x;
+    a.xb = xb;
+    a.m = m;
+    a.y = y;
+    a.yb = yb;
+    a.ld = ld;
+    a.col = col;
+    return run(a, plan_for(*view, m));
+}
+
+static int swiglu_common(const float* x, const uint16_t* xb, const velox_sm100_view* gate,
+                         const velox_sm100_view* up, int m, float* out, uint16_t* outb) {
+    if (m <= 0 || (!x && !xb) || (!out && !outb)) return VELOX_ERR_SHAPE;
+    int rc = check_view(gate);
+    if (rc != 0) return rc;
+    rc = check_view(up);
+    if (rc != 0) return rc;
+    // backend.rs:2329-2334
+    if (up->rows != gate->rows || up->k != gate->k) return VELOX_ERR_SHAPE;
+    if (up->format != gate->format) return VELOX_ERR_UNSUPPORTED;
+    LinearArgs a{};
+    a.w = *gate;
+    a.up = *up;
+    a.swiglu = 1;
+    a.x = x;
+    a.xb = xb;
+    a.m = m;
+    a.y = out;
+    a.yb = outb;
+    a.ld = gate->rows;
+    a.col = 0;
+    velox_sm100_view both = *gate;  // the stricter of the two policies (ActPolicy::meet)
+    if (up->policy != gate->policy || up->divisor != gate->divisor) {
+        both.policy = (gate->policy == VELOX_POLICY_A16_ONLY || up->policy == VELOX_POLICY_A16_ONLY)
+                          ? VELOX_POLICY_A16_ONLY
+                          : VELOX_POLICY_ALLOW_A8;
+    }
+    a.w.policy = a.up.policy = both.policy;
+    return run(a, plan_for(both, m));
+}
+
+}  // namespace vx
+
+using namespace vx;
+
+extern "C" {
+
+int velox_sm100_abi_version(void) { return 1; }
+
+int velox_sm100_set_stream(void* s) {
+    set_stream(reinterpret_cast<cudaStream_t>(s));
+    return 0;
+}
+
+int velox_sm100_linear_act(const velox_sm100_view* view, int m, float* divisor_out) {
+    if (m <= 0) return VELOX_ERR_SHAPE;
+    int rc = check_view(view);
+    if (rc != 0) return rc;
+    const Plan p = plan_for(*view, m);
+    if (divisor_out) *divisor_out = p.divisor;
+    return p.act;
+}
+
+int velox_sm100_linear_swiglu_act(const velox_sm100_view* gate, const velox_sm100_view* up, int m,
+                                  float* divisor_out) {
+    if (m <= 0) return VELOX_ERR_SHAPE;
+    int rc = check_view(gate);
+    if (rc != 0) return rc;
+    rc = check_view(up);
+    if (rc != 0) return rc;
+    velox_sm100_view both = *gate;
+    if (up->policy != gate->policy || up->divisor != gate->divisor) {
+        both.policy = (gate->policy == VELOX_POLICY_A16_ONLY || up->policy == VELOX_POLICY_A16_ONLY)
+                          ? VELOX_POLICY_A16_ONLY
+                          : VELOX_POLICY_ALLOW_A8;
+    }
+    const Plan p = plan_for(both, m);
+    if (divisor_out) *divisor_out = p.divisor;
+    return p.act;
+}
+
+int velox_sm100_linear(const float* x, const uint8_t* w, int format, long long n, long long k,
+                       long long row_begin, int rows, int m, float* y) {
+    velox_sm100_view v{};
+    v.w = w;
+    v.format = format;
+    v.policy = VELOX_POLICY_A16_ONLY;
+    v.n = n;
+    v.k = k;
+    v.row_begin = row_begin;
+    v.rows = rows;
+    return linear_common(x, nullptr, &v, m, y, nullptr, rows, 0);
+}
+
+int velox_sm100_linear_view(const float* x, const velox_sm100_view* view, int m, float* y,
+                            uint16_t* yb) {
+    if (!view) return VELOX_ERR_SHAPE;
+    return linear_common(x, nullptr, view, m, y, yb, view->rows, 0);
+}
+
+int velox_sm100_linear_bf16(const uint16_t* xb, const velox_sm100_view* view, int m, float* y,
+                            uint16_t* yb) {
+    if (!view) return VELOX_ERR_SHAPE;
+    return linear_common(nullptr, xb, view, m, y, yb, view->rows, 0);
+}
+
+int velox_sm100_linear_swiglu(const float* x, const velox_sm100_view* gate,
+                              const velox_sm100_view* up, int m, float* out, uint16_t* outb) {
+    return swiglu_common(x, nullptr, gate, up, m, out, outb);
+}
+
+int velox_sm100_linear_swiglu_bf16(const uint16_t* xb, const velox_sm100_view* gate,
+                                   const velox_sm100_view* up, int m, float* out, uint16_t* outb) {
+    return swiglu_common(nullptr, xb, gate, up, m, out, outb);
+}
+
+int velox_sm100_linears(const float* x, const uint16_t* xb, const velox_sm100_part* parts,
+                        int nparts, int m) {
+    if (!parts || nparts <= 0) return VELOX_ERR_SHAPE;
+    for (int i = 0; i < nparts; i++) {
+        const velox_sm100_part& p = parts[i];
+        // backend.rs:2286-2294: the column range must fit the destination's row stride
+        if (p.col < 0 || p.col + p.view.rows > p.ld || !p.y) return VELOX_ERR_SHAPE;
+        int rc = check_view(&p.view);
+        if (rc != 0) return rc;
+    }
+    for (int i = 0; i < nparts; i++) {
+        const velox_sm100_part& p = parts[i];
+        // A part that rounds to bf16 reads the twin when the caller has one.
+        const Plan pl = plan_for(p.view, m);
+        const bool twin = xb && (pl.act == VELOX_ACT_BF16 || !x);
+        int rc = linear_common(twin ? nullptr : x, twin ? xb : nullptr, &p.view, m, p.y, nullptr,
+                               p.ld, p.col);
+        if (rc != 0) return rc;
+    }
+    return 0;
+}
+
+int velox_sm100_dequant_rows(const velox_sm100_view* view, float* out) {
+    int rc = check_view(view);
+    if (rc != 0) return rc;
+    if (!out) return VELOX_ERR_SHAPE;
+    return dequant_rows_f32(view, out);
+}
+
+int velox_sm100_quantize_act_fp8row(const float* x, int m, long long k, uint8_t* codes,
+                                    float* scales) {
+    if (!x || !codes || !scales) return VELOX_ERR_SHAPE;
+    return quantize_act_fp8row(x, nullptr, m, k, codes, scales);
+}
+
+int velox_sm100_quantize_act_nvfp4(const float* x, int m, long long k, float divisor,
+                                   uint8_t* codes, uint8_t* scale_atoms) {
+    if (!x || !codes || !scale_atoms || !(divisor > 0.0f)) return VELOX_ERR_SHAPE;
+    return quantize_act_nvfp4(x, nullptr, m, k, divisor, codes, scale_atoms);
+}
+
+int velox_sm100_encode_nvfp4(const float* w, long long n, long long k, float amax,
+                             uint8_t* payload) {
+    if (!w || !payload) return VELOX_ERR_SHAPE;
+    return encode_nvfp4(w, n, k, amax, payload);
+}
+
+int velox_sm100_swiglu(const float* src, long long rows, int src_cols, int gate, int up, int width,
+                       float* out) {
+    return swiglu(src, rows, src_cols, gate, up, width, out);
+}
+
+int velox_sm100_silu_mul(float* gate, const float* up, long long len) { return silu_mul(gate, up, len); }
+
+int velox_sm100_add(float* acc, const float* x, long long len) { return add(acc, x, len); }
+
+int velox_sm100_add_rms_norm_twin(float* acc, const float* x, const float* weight, float* y,
+                                  uint16_t* yb, int rows, int dim, float eps, int offset) {
+    if (!acc || !weight || (!y && !yb)) return VELOX_ERR_SHAPE;
+    return add_rms_norm_twin(acc, x, weight, y, yb, rows, dim, eps, offset);
+}
+
+int velox_sm100_bf16_twin(const float* x, uint16_t* xb, long long len) { return bf16_twin(x, xb, len); }
+
+}  // extern "C"

@@ -1,0 +1,113 @@
+// Elementwise neighbours of the linear path: the unfused SwiGLU the composed form uses, the
+// residual add, RMS norm with its bf16 twin, and the twin conversion. f32 arithmetic; the oracle
+// computes these in f64 (crates/velox-cpu/src/lib.rs:188-230, 688-707), results agree to f32
+// rounding. Reference kernels: crates/velox-cuda/kernels/portable.cu:109-115, 1519-1550;
+// portable_model.cu:2011-2022.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace vx {
+
+static unsigned grid_1d(long long n, int block) {
+    long long g = (n + block - 1) / block;
+    if (g > 148LL * 32) g = 148LL * 32;
+    return (unsigned)(g < 1 ? 1 : g);
+}
+
+__device__ __forceinline__ float silu(float g) { return g / (1.0f + expf(-g)); }
+
+__global__ void swiglu_kernel(const float* __restrict__ src, long long rows, int src_cols, int gate,
+                              int up, int width, float* __restrict__ out) {
+    const long long total = rows * width;
+    for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+         idx += (long long)gridDim.x * blockDim.x) {
+        const long long r = idx / width;
+        const int i = (int)(idx % width);
+        const float g = src[r * src_cols + gate + i];
+        const float u = src[r * src_cols + up + i];
+        out[idx] = silu(g) * u;
+    }
+}
+
+__global__ void silu_mul_kernel(float* __restrict__ gate, const float* __restrict__ up, long long len) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < len;
+         i += (long long)gridDim.x * blockDim.x)
+        gate[i] = silu(gate[i]) * up[i];
+}
+
+__global__ void add_kernel(float* __restrict__ acc, const float* __restrict__ x, long long len) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < len;
+         i += (long long)gridDim.x * blockDim.x)
+        acc[i] += x[i];
+}
+
+__global__ void bf16_twin_kernel(const float* __restrict__ x, uint16_t* __restrict__ xb, long long len) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < len;
+         i += (long long)gridDim.x * blockDim.x)
+        xb[i] = bf16_bits(x[i]);
+}
+
+// One block per row: acc += x (when x is given), y = acc * rsqrt(mean(acc^2) + eps) * (offset + weight).
+__global__ void __launch_bounds__(256)
+add_rms_norm_twin_kernel(float* __restrict__ acc, const float* __restrict__ x,
+                         const float* __restrict__ weight, float* __restrict__ y,
+                         uint16_t* __restrict__ yb, int dim, float eps, float offset) {
+    __shared__ float red[8];
+    const long long base = (long long)blockIdx.x * dim;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        float v = acc[base + c];
+        if (x) {
+            v += x[base + c];
+            acc[base + c] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    if (threadIdx.x % VX_WARP == 0) red[threadIdx.x / VX_WARP] = ss;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += red[i];
+    const float inv = 1.0f / sqrtf(total / (float)dim + eps);
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        const float v = acc[base + c] * inv * (offset + weight[c]);
+        if (y) y[base + c] = v;
+        if (yb) yb[base + c] = bf16_bits(v);
+    }
+}
+
+int swiglu(const float* src, long long rows, int src_cols, int gate, int up, int width, float* out) {
+    if (rows < 1 || width < 1 || gate < 0 || up < 0 || gate + width > src_cols || up + width > src_cols)
+        return VELOX_ERR_SHAPE;
+    swiglu_kernel<<<grid_1d(rows * width, 256), 256, 0, stream()>>>(src, rows, src_cols, gate, up, width, out);
+    return launch_status();
+}
+
+int silu_mul(float* gate, const float* up, long long len) {
+    if (len < 1) return 0;
+    silu_mul_kernel<<<grid_1d(len, 256), 256, 0, stream()>>>(gate, up, len);
+    return launch_status();
+}
+
+int add(float* acc, const float* x, long long len) {
+    if (len < 1) return 0;
+    add_kernel<<<grid_1d(len, 256), 256, 0, stream()>>>(acc, x, len);
+    return launch_status();
+}
+
+int bf16_twin(const float* x, uint16_t* xb, long long len) {
+    if (len < 1) return 0;
+    bf16_twin_kernel<<<grid_1d(len, 256), 256, 0, stream()>>>(x, xb, len);
+    return launch_status();
+}
+
+int add_rms_norm_twin(float* acc, const float* x, const float* weight, float* y, uint16_t* yb,
+                      int rows, int dim, float eps, int offset) {
+    if (rows < 1 || dim < 1) return VELOX_ERR_SHAPE;
+    add_rms_norm_twin_kernel<<<(unsigned)rows, 256, 0, stream()>>>(acc, x, weight, y, yb, dim, eps,
+                                                                  offset ? 1.0f : 0.0f);
+    return launch_status();
+}
+
+}  // namespace vx

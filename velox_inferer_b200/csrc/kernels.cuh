@@ -1,0 +1,46 @@
+// Internal launcher declarations shared by the C-ABI dispatcher (api.cu).
+#pragma once
+
+#include <stdint.h>
+
+#include "../../include/velox_sm100.h"
+
+namespace vx {
+
+// One projection of a decode/verify GEMV or of the generic fallback.
+struct LinearArgs {
+    velox_sm100_view w;      // gate view for the fused SwiGLU form
+    velox_sm100_view up;     // used when swiglu != 0
+    int swiglu;
+    const float* x;          // [m, k] f32, or NULL
+    const uint16_t* xb;      // [m, k] bf16 twin, or NULL (one of x / xb is set)
+    int round_x;             // round f32 x to bf16 on load (ActQuant::Bf16)
+    int m;
+    float* y;                // may be NULL when yb is set
+    uint16_t* yb;            // bf16 twin of y, may be NULL
+    long long ld;            // row stride of y / yb in elements
+    long long col;           // first column written
+};
+
+int dequant_rows_f32(const velox_sm100_view* v, float* out);
+int dequant_rows_bf16(const velox_sm100_view* v, uint16_t* out, long long ld_out);
+
+// Memory-bound path, m <= 16, k % 64 == 0.
+int gemv(const LinearArgs& a);
+// Any shape, any m: one warp per output row, per-element decode. Slow but total.
+int linear_generic(const LinearArgs& a);
+
+int quantize_act_fp8row(const float* x, const uint16_t* xb, int m, long long k, uint8_t* codes,
+                        float* scales);
+int quantize_act_nvfp4(const float* x, const uint16_t* xb, int m, long long k, float divisor,
+                       uint8_t* codes, uint8_t* scale_atoms);
+int encode_nvfp4(const float* w, long long n, long long k, float amax, uint8_t* payload);
+
+int swiglu(const float* src, long long rows, int src_cols, int gate, int up, int width, float* out);
+int silu_mul(float* gate, const float* up, long long len);
+int add(float* acc, const float* x, long long len);
+int add_rms_norm_twin(float* acc, const float* x, const float* weight, float* y, uint16_t* yb,
+                      int rows, int dim, float eps, int offset);
+int bf16_twin(const float* x, uint16_t* xb, long long len);
+
+}  // namespace vx
