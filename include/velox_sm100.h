@@ -76,6 +76,11 @@ typedef struct velox_sm100_part {
 /* Library / build information. Returns the ABI version (1). */
 int velox_sm100_abi_version(void);
 
+/* Debug aid with no counterpart in the reference: synchronises the device and returns the status
+ * word of the tensor-core kernels: 0, or the code of the first bounded mbarrier wait that gave up
+ * (the kernel then stopped early and its output is incomplete). Never call it on a hot path. */
+int velox_sm100_debug_status(void);
+
 /* Launch stream of the calling thread (a cudaStream_t); NULL restores cudaStreamPerThread.
  * Replaces nothing in the reference: its launchers always use the per-thread default stream
  * (crates/velox-build/src/lib.rs:120-129). */

@@ -44,6 +44,7 @@ _PV = C.POINTER(View)
 SIGNATURES = {
     "velox_sm100_abi_version": (_I, []),
     "velox_sm100_set_stream": (_I, [_VP]),
+    "velox_sm100_debug_status": (_I, []),
     "velox_sm100_linear_act": (_I, [_PV, _I, C.POINTER(C.c_float)]),
     "velox_sm100_linear": (_I, [_VP, _VP, _I, _LL, _LL, _LL, _I, _I, _VP]),
     "velox_sm100_linear_view": (_I, [_VP, _PV, _I, _VP, _VP]),

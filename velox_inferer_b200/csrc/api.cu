@@ -94,6 +94,20 @@ static Plan plan_for(const velox_sm100_view& v, int m) {
     return p;
 }
 
+// The fused tensor-core SwiGLU pairs column c of the gate tile with column c of the up tile; with
+// NVFP4 scale tiles that needs both views at the same offset inside a 128-row tile. Otherwise the
+// pair runs on the bf16 path, which has no such constraint.
+static Plan plan_swiglu(const velox_sm100_view& both, const velox_sm100_view& gate,
+                        const velox_sm100_view& up, int m) {
+    Plan p = plan_for(both, m);
+    if (p.path == PATH_GEMM_A4 && (gate.row_begin - up.row_begin) % 128 != 0) {
+        p.path = PATH_GEMM_BF16;
+        p.act = VELOX_ACT_BF16;
+        p.divisor = 0.0f;
+    }
+    return p;
+}
+
 static int run(const LinearArgs& a, const Plan& p) {
     int rc = VELOX_ERR_UNSUPPORTED;
     switch (p.path) {
@@ -163,7 +177,7 @@ static int swiglu_common(const float* x, const uint16_t* xb, const velox_sm100_v
                           : VELOX_POLICY_ALLOW_A8;
     }
     a.w.policy = a.up.policy = both.policy;
-    return run(a, plan_for(both, m));
+    return run(a, plan_swiglu(both, *gate, *up, m));
 }
 
 }  // namespace vx
@@ -201,10 +215,12 @@ int velox_sm100_linear_swiglu_act(const velox_sm100_view* gate, const velox_sm10
                           ? VELOX_POLICY_A16_ONLY
                           : VELOX_POLICY_ALLOW_A8;
     }
-    const Plan p = plan_for(both, m);
+    const Plan p = plan_swiglu(both, *gate, *up, m);
     if (divisor_out) *divisor_out = p.divisor;
     return p.act;
 }
+
+int velox_sm100_debug_status(void) { return gemm_status_sync(); }
 
 int velox_sm100_linear(const float* x, const uint8_t* w, int format, long long n, long long k,
                        long long row_begin, int rows, int m, float* y) {

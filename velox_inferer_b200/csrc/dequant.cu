@@ -8,7 +8,8 @@
 // dequant_rows_bf16: the operand the bf16 tensor-core GEMM multiplies. NVFP4 -> e2m1*e4m3 (six
 // significant bits: exact in bf16; the 1/divisor factor is applied to the f32 accumulator), FP8 ->
 // the E4M3 value (exact; the row scale is applied to the accumulator), Q4_K -> the decoded value
-// rounded to bf16 (the only lossy case).
+// as two bf16 terms hi + lo (hi = bf16(v), lo = bf16(v - hi)) laid side by side along K, so the
+// GEMM's f32 accumulation sees the value to about 2^-17 relative.
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -18,7 +19,7 @@ namespace vx {
 template <int FMT, typename OUT>
 __global__ void __launch_bounds__(256)
 dequant_rows_kernel(const uint8_t* __restrict__ w, long long n, long long k, long long row_begin,
-                    int rows, OUT* __restrict__ out, long long ld_out) {
+                    int rows, OUT* __restrict__ out, long long ld_out, long long lo_offset) {
     const long long groups_per_row = k / 16;
     const long long total = (long long)rows * groups_per_row;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
@@ -83,12 +84,24 @@ dequant_rows_kernel(const uint8_t* __restrict__ w, long long n, long long k, lon
             uint4* o4 = reinterpret_cast<uint4*>(o);
             o4[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             o4[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            if (lo_offset > 0) {
+                // second bf16 term: the part of the value its first bf16 rounding dropped
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float r0 = v[2 * j] - round_bf16(v[2 * j]);
+                    const float r1 = v[2 * j + 1] - round_bf16(v[2 * j + 1]);
+                    packed[j] = (uint32_t)bf16_bits(r0) | ((uint32_t)bf16_bits(r1) << 16);
+                }
+                uint4* l4 = reinterpret_cast<uint4*>(o + lo_offset);
+                l4[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                l4[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            }
         }
     }
 }
 
 template <typename OUT>
-static int launch_dequant(const velox_sm100_view* v, OUT* out, long long ld_out) {
+static int launch_dequant(const velox_sm100_view* v, OUT* out, long long ld_out, long long lo_offset) {
     if (v->k % 16 != 0) return VELOX_ERR_UNSUPPORTED;
     const long long total = (long long)v->rows * (v->k / 16);
     long long blocks = (total + 255) / 256;
@@ -98,15 +111,15 @@ static int launch_dequant(const velox_sm100_view* v, OUT* out, long long ld_out)
     switch (v->format) {
         case VELOX_FMT_NVFP4:
             dequant_rows_kernel<VELOX_FMT_NVFP4, OUT><<<(unsigned)blocks, 256, 0, s>>>(
-                v->w, v->n, v->k, v->row_begin, v->rows, out, ld_out);
+                v->w, v->n, v->k, v->row_begin, v->rows, out, ld_out, lo_offset);
             break;
         case VELOX_FMT_FP8_ROW_BF16:
             dequant_rows_kernel<VELOX_FMT_FP8_ROW_BF16, OUT><<<(unsigned)blocks, 256, 0, s>>>(
-                v->w, v->n, v->k, v->row_begin, v->rows, out, ld_out);
+                v->w, v->n, v->k, v->row_begin, v->rows, out, ld_out, lo_offset);
             break;
         case VELOX_FMT_GGML_Q4_K:
             dequant_rows_kernel<VELOX_FMT_GGML_Q4_K, OUT><<<(unsigned)blocks, 256, 0, s>>>(
-                v->w, v->n, v->k, v->row_begin, v->rows, out, ld_out);
+                v->w, v->n, v->k, v->row_begin, v->rows, out, ld_out, lo_offset);
             break;
         default:
             return VELOX_ERR_UNSUPPORTED;
@@ -114,10 +127,10 @@ static int launch_dequant(const velox_sm100_view* v, OUT* out, long long ld_out)
     return launch_status();
 }
 
-int dequant_rows_f32(const velox_sm100_view* v, float* out) { return launch_dequant<float>(v, out, v->k); }
+int dequant_rows_f32(const velox_sm100_view* v, float* out) { return launch_dequant<float>(v, out, v->k, 0); }
 
-int dequant_rows_bf16(const velox_sm100_view* v, uint16_t* out, long long ld_out) {
-    return launch_dequant<uint16_t>(v, out, ld_out);
+int dequant_rows_bf16(const velox_sm100_view* v, uint16_t* out, long long ld_out, long long lo_offset) {
+    return launch_dequant<uint16_t>(v, out, ld_out, lo_offset);
 }
 
 }  // namespace vx

@@ -14,4 +14,8 @@ bool gemm_available();
 // SwiGLU form. Returns VELOX_ERR_UNSUPPORTED for shapes it does not take.
 int gemm_linear(const LinearArgs& a, int act, float divisor);
 
+// Synchronises the device and returns the tensor-core kernels' status word: 0, or the code of the
+// first bounded wait that gave up.
+int gemm_status_sync();
+
 }  // namespace vx

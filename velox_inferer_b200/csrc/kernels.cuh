@@ -23,7 +23,8 @@ struct LinearArgs {
 };
 
 int dequant_rows_f32(const velox_sm100_view* v, float* out);
-int dequant_rows_bf16(const velox_sm100_view* v, uint16_t* out, long long ld_out);
+// lo_offset > 0: also write the bf16 residual of each value lo_offset elements after it.
+int dequant_rows_bf16(const velox_sm100_view* v, uint16_t* out, long long ld_out, long long lo_offset);
 
 // Memory-bound path, m <= 16, k % 64 == 0.
 int gemv(const LinearArgs& a);
