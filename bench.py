@@ -1,0 +1,364 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 linear path on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this repo's CUDA path
+    python bench.py --impl reference --gpus N --steps K ...   # the CPU oracle on the host cores
+
+Workload (default): the 64-layer NVFP4 linear stack of a 32B-class decoder (hidden 5120, 64 query
+/ 8 KV heads of 128, intermediate 25600) at M = 2048 tokens, tensor-parallel over N GPUs
+(column-split q/k/v/gate/up, row-split o/down, one NCCL all-reduce after each row-split
+projection). A step is one pass of all 64 layers over one batch of M tokens; the metric is
+tokens/s of the whole job. ``--workload decode`` runs the same stack at M = 1.
+
+One JSON line is printed by rank 0. ``value`` has inputs resident in HBM; ``e2e`` copies the
+step's activations from pinned host memory and reads the result back inside the timed region.
+``roofline`` is for the dominant kernel (the tcgen05 NVFP4 GEMM at M = 2048, the streaming GEMV at
+M = 1), timed with CUDA events on its launch stream inside the timed region. ``cpu_baseline`` times
+the CPU oracle on a bounded sample of the same workload. Data is synthetic (seeded N(0, 0.02^2)
+weights, N(0, 1) activations).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "nvfp4_layer_stack_tokens_per_s"
+UNIT = "tok/s"
+FP4_OVER_BF16 = 4.0          # nominal dense FP4 : BF16 tensor ratio on B200 (9 : 2.25 PFLOP/s)
+NOMINAL_FP4_TFLOPS = 9000.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_baseline_sample(spec, m_tokens: int, seconds_target: float = 12.0):
+    """The CPU oracle (row-parallel over all host threads, f64 accumulation, same arithmetic as the
+    reference's velox-cpu) on a bounded sample: a row slice of one gate projection. Returns
+    (tokens/s the whole stack would reach at that MAC rate, cores, description)."""
+    import numpy as np
+    from oracle import oracle as O
+
+    cores = os.cpu_count() or 1
+    k, n = spec.hidden, 256
+    rng = np.random.default_rng(0)
+    w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
+    payload = O.encode_nvfp4_rne(w)
+    m = min(m_tokens, 64)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    # calibrate, then size the sample to the time target
+    t0 = time.perf_counter()
+    O.linear(x, payload, O.FMT_NVFP4, n, k, 0, n, m, threads=0, act=O.ACT_NVFP4 if m_tokens > 16 else O.ACT_BF16,
+             divisor=256.0)
+    dt = max(time.perf_counter() - t0, 1e-4)
+    reps = max(1, min(400, int(seconds_target / dt)))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        O.linear(x, payload, O.FMT_NVFP4, n, k, 0, n, m, threads=0,
+                 act=O.ACT_NVFP4 if m_tokens > 16 else O.ACT_BF16, divisor=256.0)
+    dt = time.perf_counter() - t0
+    macs = reps * m * n * k
+    # at decode width the oracle re-decodes the weights every call, exactly as velox-cpu does
+    mac_per_token = spec.flops_per_token() / 2
+    tok_s = (macs / dt) / mac_per_token * (1.0 if m_tokens > 16 else 1.0)
+    sample = (f"{reps} x oracle linear NVFP4 rows 256 of [25600,{k}] at m={m} ({macs / 1e9:.1f} GMAC in "
+              f"{dt:.1f} s), scaled by the stack's {mac_per_token / 1e9:.1f} GMAC per token")
+    return tok_s, cores, sample, dt / reps
+
+
+def run_reference(args):
+    from velox_inferer_b200.stack import StackSpec
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    spec = StackSpec(layers=args.layers)
+    m = 1 if args.workload == "decode" else args.m
+    vals = []
+    cores, sample = os.cpu_count() or 1, ""
+    for i in range(args.warmup + args.steps):
+        tok_s, cores, sample, step_s = cpu_baseline_sample(spec, m, seconds_target=max(2.0, 60.0 / (args.warmup + args.steps)))
+        if i >= args.warmup:
+            vals.append((tok_s, step_s))
+    tok_s = sum(v[0] for v in vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * m / tok_s,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64 accumulate over NVFP4",
+        "data": "synthetic",
+        "config": workload_config(args, spec, m),
+        "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, spec, m):
+    return {"workload": f"{spec.layers}-layer NVFP4 linear stack (hidden {spec.hidden}, q {spec.q_dim}, kv {spec.kv_dim}, "
+                        f"intermediate {spec.intermediate}), M={m}, attention = passthrough of q",
+            "tokens_per_step": m, "layers": spec.layers,
+            "parallelism": f"tp{args.gpus}: column-split q/k/v/gate/up, row-split o/down, bf16 all-reduce after o and down",
+            "activations": "bf16 in HBM; NVFP4 tensor-core operands (ActQuant::Nvfp4, per-use divisors 256/128/16)"
+                           if m > 16 else "bf16 (ActQuant::Bf16)",
+            "l2": "each step streams the layers' distinct weights, far larger than the 126 MB L2"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "decode"])
+    ap.add_argument("--m", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=64)
+    ap.add_argument("--no-components", action="store_true", help="skip the single-linear GEMV / GEMM lines")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from velox_inferer_b200 import ActPolicy, Sm100Backend, WeightFormat, WeightView
+    from velox_inferer_b200.stack import LinearStack, StackSpec
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    b = Sm100Backend(local)
+    spec = StackSpec(layers=args.layers)
+    m = 1 if args.workload == "decode" else args.m
+    peaks = measured_peaks()
+
+    stack = LinearStack(b, spec, max_tokens=m, rank=rank, world=world, a4=True, seed=0)
+    gen = torch.Generator().manual_seed(1234)
+    x_host = torch.randn(m, spec.hidden, generator=gen).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty(m, spec.hidden, dtype=torch.bfloat16).pin_memory()
+    x_dev = x_host.to(b.device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        stack.forward(x_dev, m)
+    barrier()
+    if b.lib.velox_sm100_debug_status() != 0:
+        raise SystemExit("tensor-core kernel reported a timed-out wait")
+
+    # ---- device-resident timing, kernels bracketed by events for the roofline ----
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    b.timing_enable(True)
+    launches0 = b.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        stack.forward(x_dev, m)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = b.launch_count() - launches0
+    timed = b.timing_collect()
+    b.timing_enable(False)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms], device=b.device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+
+    # ---- end to end: pinned host -> device, all layers, result back to the host ----
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        x_dev.copy_(x_host, non_blocking=True)
+        out = stack.forward(x_dev, m)
+        y_host.copy_(out[: m * spec.hidden].view(m, spec.hidden), non_blocking=True)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=b.device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel ----
+    per_rank_flops = spec.flops_per_token() * m / world
+    per_rank_bytes = stack.weight_bytes
+    if m > 16:
+        k_ms, k_n = timed["gemm_nvfp4"]
+        peak = peaks["bf16_tflops"] * FP4_OVER_BF16
+        achieved = per_rank_flops * args.steps / (k_ms * 1e-3) / 1e12 if k_ms > 0 else 0.0
+        roofline = {"bound": "tensor", "kernel": "gemm_kernel<mxf4nvf4> (tcgen05 block-scaled NVFP4)",
+                    "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                    "peak_source": f"{peaks['source']} bf16 cuBLAS {peaks['bf16_tflops']} TFLOP/s x {FP4_OVER_BF16:g} "
+                                   "(no FP4 GEMM peak is measured on this pool; nominal dense FP4 : BF16 ratio)",
+                    "frac_of_nominal_fp4": achieved / NOMINAL_FP4_TFLOPS,
+                    "launches": int(k_n), "avg_launch_us": 1e3 * k_ms / max(k_n, 1), "traffic": None,
+                    "act_quant_ms_per_step": timed["act_quant"][0] / args.steps}
+    else:
+        k_ms, k_n = timed["gemv"]
+        achieved = per_rank_bytes * args.steps / (k_ms * 1e-3) / 1e9 if k_ms > 0 else 0.0
+        roofline = {"bound": "hbm", "kernel": "gemv_kernel<nvfp4>", "achieved": achieved,
+                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                    "peak_source": f"{peaks['source']} copy bandwidth",
+                    "frac_of_nominal_hbm": achieved / NOMINAL_HBM_GBS,
+                    "launches": int(k_n), "avg_launch_us": 1e3 * k_ms / max(k_n, 1), "traffic": None}
+
+    line = {
+        "metric": METRIC, "value": m / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 accumulate (bf16 in/out)" if m > 16 else "nvfp4 x bf16 -> f32",
+        "data": "synthetic", "config": workload_config(args, spec, m),
+        "e2e": {"value": m / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+        "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+        "tflops_per_gpu": per_rank_flops / (ms * 1e-3) / 1e12,
+        "weights_gb_per_gpu": per_rank_bytes / 1e9,
+    }
+
+    if world == 1 and not args.no_components:
+        line["components"] = components(b, peaks)
+    if world == 1 and not args.no_cpu_baseline:
+        tok_s, cores, sample, _ = cpu_baseline_sample(spec, m)
+        line["cpu_baseline"] = {"value": tok_s, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+    else:
+        line["cpu_baseline"] = None
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def components(b, peaks):
+    """Single NVFP4 linear [25600, 5120]: decode GEMV (M = 1, weight copies rotated so they never
+    sit in L2) and prefill GEMM (M = 2048), timed with CUDA events."""
+    import torch
+
+    from velox_inferer_b200 import ActPolicy, WeightFormat, WeightView
+
+    n, k = 25600, 5120
+    copies = 6   # 6 x 73.7 MB > 3 x the 126 MB L2
+    views = []
+    gen = torch.Generator(device=b.device).manual_seed(0)
+    for _ in range(copies):
+        w = torch.randn(n, k, generator=gen, device=b.device) * 0.02
+        views.append(WeightView.full(b.encode_nvfp4(w), WeightFormat.NVFP4, n, k).with_act(ActPolicy.allow_a4(256.0)))
+        del w
+    out = {}
+    payload = WeightFormat.NVFP4.payload_bytes(n, k)
+    for m in (1, 2048):
+        xb = torch.randn(m, k, device=b.device).to(torch.bfloat16)
+        yb = torch.empty(m, n, dtype=torch.bfloat16, device=b.device)
+        for v in views:
+            b.linear_bf16(xb, v, None, m, yb=yb)
+        torch.cuda.synchronize()
+        b.timing_enable(True)
+        rounds = 20 if m == 1 else 3
+        for _ in range(rounds):
+            for v in views:
+                b.linear_bf16(xb, v, None, m, yb=yb)
+        t = b.timing_collect()
+        b.timing_enable(False)
+        if m == 1:
+            ms, cnt = t["gemv"]
+            us = 1e3 * ms / cnt
+            byts = payload + 2 * m * k + 2 * m * n
+            gbs = byts / (us * 1e-6) / 1e9
+            out["decode_gemv_m1"] = {"us": us, "GB/s": gbs, "bytes": byts, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                                     "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS}
+        else:
+            ms, cnt = t["gemm_nvfp4"]
+            us = 1e3 * ms / cnt
+            tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
+            out["prefill_gemm_m2048"] = {"us": us, "TFLOP/s": tf, "quant_us": 1e3 * t["act_quant"][0] / max(t["act_quant"][1], 1),
+                                         "frac_of_measured_bf16_x4": tf / (peaks["bf16_tflops"] * FP4_OVER_BF16),
+                                         "frac_of_nominal_fp4": tf / NOMINAL_FP4_TFLOPS}
+    return out
+
+
+if __name__ == "__main__":
+    main()

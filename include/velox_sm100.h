@@ -81,6 +81,19 @@ int velox_sm100_abi_version(void);
  * (the kernel then stopped early and its output is incomplete). Never call it on a hot path. */
 int velox_sm100_debug_status(void);
 
+/* Kernel launches issued through this library since it was loaded (host counter). No counterpart
+ * in the reference; the benchmark reports it. */
+long long velox_sm100_launch_count(void);
+
+/* CUDA-event timing of the main kernels, the counterpart of the reference's VELOX_GPU_TIMING
+ * (crates/velox-cuda/src/timing.rs:1-97). While enabled every timed kernel is bracketed by an
+ * event pair on its launch stream (do not enable it while capturing a CUDA graph).
+ * velox_sm100_timing_collect synchronises the device and returns, per class, the summed kernel
+ * milliseconds and the launch count since the last collect. Classes: 0 GEMV, 1 GEMM NVFP4,
+ * 2 GEMM FP8, 3 GEMM bf16, 4 activation quantiser, 5 weight dequantiser. `classes` >= 6. */
+int velox_sm100_timing_enable(int on);
+int velox_sm100_timing_collect(double* ms_by_class, long long* count_by_class, int classes);
+
 /* Launch stream of the calling thread (a cudaStream_t); NULL restores cudaStreamPerThread.
  * Replaces nothing in the reference: its launchers always use the per-thread default stream
  * (crates/velox-build/src/lib.rs:120-129). */
@@ -157,6 +170,11 @@ int velox_sm100_add(float* acc, const float* x, long long len);
  * acc); y = rms_norm(acc) * (offset + weight); yb (may be NULL) = bf16 twin of y. */
 int velox_sm100_add_rms_norm_twin(float* acc, const float* x, const float* weight, float* y,
                                   uint16_t* yb, int rows, int dim, float eps, int offset);
+/* The same with a bf16 addend (the all-reduced partial sums of a row-split projection): acc += xb,
+ * then the norm. No counterpart in the reference, which has no tensor parallelism. */
+int velox_sm100_add_bf16_rms_norm_twin(float* acc, const uint16_t* xb, const float* weight, float* y,
+                                       uint16_t* yb, int rows, int dim, float eps, int offset);
+int velox_sm100_add_bf16(float* acc, const uint16_t* xb, long long len);
 /* f32 -> bf16 twin (RNE), as velox_bf16_bits (velox_common.cuh:74-82). */
 int velox_sm100_bf16_twin(const float* x, uint16_t* xb, long long len);
 

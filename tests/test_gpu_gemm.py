@@ -144,3 +144,48 @@ def test_one_hot_operands_pin_nibble_order_and_scale_placement(b):
     assert np.count_nonzero(want) > 50
     assert np.array_equal(got != 0, want != 0)
     assert both_metrics(got, want)[0] <= 1e-6
+
+
+@pytest.mark.parametrize("fmt,policy,n,k,begin,rows,m", [
+    (NV, A4, 512, 1024, 0, 512, 130), (NV, A4, 768, 320, 104, 600, 257), (NV, A4, 1024, 512, 128, 896, 300),
+    (F8, A8, 512, 1024, 64, 384, 130), (NV, A16, 384, 1024, 64, 256, 96), (NV, A4, 2048, 256, 0, 2048, 700),
+])
+def test_bf16_only_output_takes_the_staged_store_and_matches(b, fmt, policy, n, k, begin, rows, m):
+    # bf16-only output goes through shared memory and a tensor-map store; it must equal the RNE of
+    # the f32 output the direct path writes, bit for bit, and leave neighbouring memory alone.
+    r = O.Rng(21)
+    payload = r.random_weight(FMT_O[fmt], n, k)
+    x = r.vec(m * k, 1.0)
+    view = make_view(b, payload, fmt, n, k, begin, rows, policy)
+    xb = b.bf16_twin(b.upload(x))
+    y = b.alloc(m * rows)
+    b.linear_bf16(xb, view, y, m)                      # f32 output: direct stores
+    guard = 64
+    yb = torch.full((m * rows + guard,), 7.0, dtype=torch.bfloat16, device=y.device)
+    b.linear_bf16(xb, view, None, m, yb=yb[: m * rows])   # bf16 only: staged tensor-map stores
+    assert b.lib.velox_sm100_debug_status() == 0
+    assert np.array_equal(bf16_bits(yb[: m * rows]), f32_to_bf16_bits(y.cpu().numpy()))
+    act = b.linear_act(view, m)
+    want = oracle_linear(xb.float().cpu().numpy().reshape(-1), payload, fmt, n, k, begin, rows, m, act)
+    assert both_metrics(y.cpu().numpy().reshape(m, rows), want)[0] <= LINEAR_TOL
+    assert torch.all(yb[m * rows:] == 7.0)
+
+
+def test_swiglu_bf16_only_output_staged(b):
+    fmt, policy, k, w, m = NV, A4, 512, 256, 200
+    r = O.Rng(0x5e3)
+    x = r.vec(m * k, 1.0)
+    p = r.random_weight(FMT_O[fmt], 2 * w, k)
+    parent = WeightView.full(b.upload_bytes(p), fmt, 2 * w, k).with_act(policy)
+    gate, up = parent.rows_view(0, w), parent.rows_view(w, w)
+    xd = b.upload(x)
+    out = b.alloc(m * w)
+    b.linear_swiglu(xd, gate, up, out, m)
+    outb = torch.zeros(m * w, dtype=torch.bfloat16, device=out.device)
+    # f32 x and its twin quantise to the same NVFP4 codes only if x is bf16-exact: use the twin for both
+    xb = b.bf16_twin(xd)
+    out2 = b.alloc(m * w)
+    b.linear_swiglu_twin(xb, gate, up, out2, None, m)
+    b.linear_swiglu_twin(xb, gate, up, None, outb, m)
+    assert b.lib.velox_sm100_debug_status() == 0
+    assert np.array_equal(bf16_bits(outb), f32_to_bf16_bits(out2.cpu().numpy()))

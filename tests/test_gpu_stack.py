@@ -1,0 +1,59 @@
+"""The layer stack on one GPU against the oracle running the identical op sequence with the
+roundings the kernels declare (bf16 twins between ops, NVFP4 activations with the per-use
+divisors at prefill width, bf16 partial sums)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as O
+from velox_inferer_b200.stack import DIV_DOWN_IN, DIV_NORM_OUT, DIV_O_IN, LinearStack, StackSpec
+
+from .gpu_util import backend
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf16(a):
+    return O.quantize_activations(np.asarray(a, dtype=np.float32).reshape(-1), 1, O.ACT_BF16).reshape(np.shape(a))
+
+
+def _oracle_stack(stack, spec, x, m, prefill):
+    def lin(inp, view, div):
+        n, k = view.parent_rows, view.k
+        payload = view.buf.cpu().numpy()
+        act = (O.ACT_NVFP4, div) if prefill else (O.ACT_BF16, 0.0)
+        return O.linear(inp, payload, O.FMT_NVFP4, n, k, 0, n, m, act=act[0], divisor=act[1])
+
+    ones = np.ones(spec.hidden, dtype=np.float32)
+    x = _bf16(x).astype(np.float32)
+    pb = None
+    for l in stack.layers:
+        if pb is not None:
+            x = (x + pb).astype(np.float32)
+        hb = _bf16(O.rms_norm(x, ones, spec.norm_eps))
+        qb = _bf16(lin(hb, l.q, DIV_NORM_OUT))
+        pb = _bf16(lin(qb, l.o, DIV_O_IN))
+        x = (x + pb).astype(np.float32)
+        hb = _bf16(O.rms_norm(x, ones, spec.norm_eps))
+        g, u = lin(hb, l.gate, DIV_NORM_OUT), lin(hb, l.up, DIV_NORM_OUT)
+        gb = _bf16(O.swiglu(np.concatenate([g, u], axis=1), m, 2 * g.shape[1], 0, g.shape[1], g.shape[1]))
+        pb = _bf16(lin(gb, l.down, DIV_DOWN_IN))
+    return _bf16((x + pb).astype(np.float32))
+
+
+@pytest.mark.parametrize("m", [3, 40, 200])
+def test_stack_matches_oracle_sequence(m):
+    b = backend()
+    spec = StackSpec(layers=2, hidden=256, intermediate=512, heads=2, kv_heads=1, head_dim=128)
+    stack = LinearStack(b, spec, max_tokens=m, a4=True, seed=3)
+    x = np.random.default_rng(m).standard_normal((m, spec.hidden)).astype(np.float32)
+    xb = torch.from_numpy(x).to(torch.bfloat16).to(b.device)
+    out = stack.forward(xb, m)
+    torch.cuda.synchronize()
+    assert b.lib.velox_sm100_debug_status() == 0
+    got = out[: m * spec.hidden].float().cpu().numpy().reshape(m, spec.hidden)
+    want = _oracle_stack(stack, spec, xb.float().cpu().numpy(), m, prefill=m > 16)
+    # every stage rounds to bf16 (2^-9 relative); two layers of it stay within a few bf16 ulps
+    err = O.max_abs_diff(got, want) / O.rms(want)
+    assert err <= 2e-2, err
+    assert np.mean(np.abs(got - want) <= 2.0 ** -7 * (np.abs(want) + 0.05)) > 0.999

@@ -15,4 +15,7 @@ def __getattr__(name):
     if name == "Sm100Backend":
         from .backend import Sm100Backend
         return Sm100Backend
+    if name in ("LinearStack", "StackSpec"):
+        from . import stack
+        return getattr(stack, name)
     raise AttributeError(name)

@@ -45,6 +45,11 @@ SIGNATURES = {
     "velox_sm100_abi_version": (_I, []),
     "velox_sm100_set_stream": (_I, [_VP]),
     "velox_sm100_debug_status": (_I, []),
+    "velox_sm100_launch_count": (C.c_longlong, []),
+    "velox_sm100_timing_enable": (_I, [_I]),
+    "velox_sm100_timing_collect": (_I, [_VP, _VP, _I]),
+    "velox_sm100_add_bf16_rms_norm_twin": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _F, _I]),
+    "velox_sm100_add_bf16": (_I, [_VP, _VP, _LL]),
     "velox_sm100_linear_act": (_I, [_PV, _I, C.POINTER(C.c_float)]),
     "velox_sm100_linear": (_I, [_VP, _VP, _I, _LL, _LL, _LL, _I, _I, _VP]),
     "velox_sm100_linear_view": (_I, [_VP, _PV, _I, _VP, _VP]),

@@ -227,12 +227,44 @@ class Sm100Backend:
         self._bind()
         status(self.lib.velox_sm100_add(acc.data_ptr(), x.data_ptr(), n), "sm100 add")
 
-    def add_rms_norm_twin(self, acc, x, weight, y, yb, rows, dim, eps, offset=False) -> None:
-        """Backend::add_rms_norm_twin (backend.rs:968-983); x None = plain rms_norm of acc."""
+    def add_rms_norm_twin(self, acc, x, weight, y, yb, rows, dim, eps, offset=False, xb=None) -> None:
+        """Backend::add_rms_norm_twin (backend.rs:968-983); x None = plain rms_norm of acc. With
+        ``xb`` the addend is a bf16 buffer (the all-reduced partial sums of a row-split projection)."""
         self._bind()
+        if xb is not None:
+            status(self.lib.velox_sm100_add_bf16_rms_norm_twin(
+                acc.data_ptr(), xb.data_ptr(), weight.data_ptr(), _ptr(y), _ptr(yb), rows, dim, eps,
+                int(offset)), "sm100 add_bf16_rms_norm_twin")
+            return
         status(self.lib.velox_sm100_add_rms_norm_twin(acc.data_ptr(), _ptr(x), weight.data_ptr(),
                                                       _ptr(y), _ptr(yb), rows, dim, eps,
                                                       int(offset)), "sm100 add_rms_norm_twin")
+
+    def add_bf16(self, acc, xb, n) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_add_bf16(acc.data_ptr(), xb.data_ptr(), n), "sm100 add_bf16")
+
+    def bf16_twin_into(self, x: torch.Tensor, xb: torch.Tensor, n: int) -> torch.Tensor:
+        self._bind()
+        status(self.lib.velox_sm100_bf16_twin(x.data_ptr(), xb.data_ptr(), n), "bf16_twin")
+        return xb
+
+    # ---- measurement hooks (crates/velox-cuda/src/timing.rs) ---------------------------------
+    TIMED_CLASSES = ("gemv", "gemm_nvfp4", "gemm_fp8", "gemm_bf16", "act_quant", "dequant")
+
+    def timing_enable(self, on: bool) -> None:
+        self.lib.velox_sm100_timing_enable(int(on))
+
+    def timing_collect(self) -> dict:
+        """Summed kernel milliseconds and launch counts per class since the last collect."""
+        n = len(self.TIMED_CLASSES)
+        ms = (C.c_double * n)()
+        cnt = (C.c_longlong * n)()
+        status(self.lib.velox_sm100_timing_collect(ms, cnt, n), "timing_collect")
+        return {name: (ms[i], cnt[i]) for i, name in enumerate(self.TIMED_CLASSES)}
+
+    def launch_count(self) -> int:
+        return int(self.lib.velox_sm100_launch_count())
 
     def bf16_twin(self, x: torch.Tensor) -> torch.Tensor:
         xb = torch.empty(x.shape, dtype=torch.bfloat16, device=self.device)

@@ -146,6 +146,7 @@ static unsigned grid_for(long long total) {
 int quantize_act_fp8row(const float* x, const uint16_t* xb, int m, long long k, uint8_t* codes,
                         float* scales) {
     if (m < 1 || k < 1) return VELOX_ERR_SHAPE;
+    TimedRegion timed(TIMED_ACT_QUANT);
     quantize_fp8row_kernel<<<(unsigned)m, 256, 0, stream()>>>(x, xb, k, codes, scales);
     return launch_status();
 }
@@ -154,6 +155,7 @@ int quantize_act_nvfp4(const float* x, const uint16_t* xb, int m, long long k, f
                        uint8_t* codes, uint8_t* scale_atoms) {
     if (m < 1 || k < 64 || k % 64 != 0) return VELOX_ERR_SHAPE;
     const int rows_padded = (m + 127) / 128 * 128;
+    TimedRegion timed(TIMED_ACT_QUANT);
     quantize_nvfp4_kernel<<<grid_for((long long)rows_padded * (k / 16)), 256, 0, stream()>>>(
         x, xb, m, rows_padded, k, divisor, codes, scale_atoms);
     return launch_status();

@@ -1,7 +1,9 @@
 // C ABI of the sm_100a quantized-linear kernel set (declared in include/velox_sm100.h): argument
 // checks as the reference's check::linear (crates/velox-core/src/check.rs:100-131), kernel
 // selection by (format, policy, m, k), and the launch-stream / scratch state the launchers share.
+#include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 #include "gemm.cuh"
@@ -37,6 +39,34 @@ void* scratch(ScratchSlot slot, size_t bytes) {
         p.cap = n;
     }
     return p.ptr;
+}
+
+static std::atomic<long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+struct TimedPair {
+    cudaEvent_t a, b;
+    int cls;
+};
+static std::mutex g_timing_mu;
+static bool g_timing_on = false;
+static std::vector<TimedPair> g_timed;
+
+TimedRegion::TimedRegion(int cls) : slot(-1) {
+    if (!g_timing_on) return;
+    std::lock_guard<std::mutex> lock(g_timing_mu);
+    TimedPair t;
+    t.cls = cls;
+    if (cudaEventCreate(&t.a) != cudaSuccess || cudaEventCreate(&t.b) != cudaSuccess) return;
+    cudaEventRecord(t.a, stream());
+    g_timed.push_back(t);
+    slot = (int)g_timed.size() - 1;
+}
+
+TimedRegion::~TimedRegion() {
+    if (slot < 0) return;
+    std::lock_guard<std::mutex> lock(g_timing_mu);
+    cudaEventRecord(g_timed[slot].b, stream());
 }
 
 int check_view(const velox_sm100_view* v) {
@@ -222,6 +252,36 @@ int velox_sm100_linear_swiglu_act(const velox_sm100_view* gate, const velox_sm10
 
 int velox_sm100_debug_status(void) { return gemm_status_sync(); }
 
+long long velox_sm100_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int velox_sm100_timing_enable(int on) {
+    std::lock_guard<std::mutex> lock(g_timing_mu);
+    g_timing_on = on != 0;
+    return 0;
+}
+
+int velox_sm100_timing_collect(double* ms_by_class, long long* count_by_class, int classes) {
+    if (!ms_by_class || !count_by_class || classes < TIMED_CLASSES) return VELOX_ERR_SHAPE;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    std::lock_guard<std::mutex> lock(g_timing_mu);
+    for (int i = 0; i < classes; i++) {
+        ms_by_class[i] = 0.0;
+        count_by_class[i] = 0;
+    }
+    for (TimedPair& t : g_timed) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, t.a, t.b) == cudaSuccess) {
+            ms_by_class[t.cls] += ms;
+            count_by_class[t.cls] += 1;
+        }
+        cudaEventDestroy(t.a);
+        cudaEventDestroy(t.b);
+    }
+    g_timed.clear();
+    return 0;
+}
+
 int velox_sm100_linear(const float* x, const uint8_t* w, int format, long long n, long long k,
                        long long row_begin, int rows, int m, float* y) {
     velox_sm100_view v{};
@@ -316,7 +376,18 @@ int velox_sm100_add(float* acc, const float* x, long long len) { return add(acc,
 int velox_sm100_add_rms_norm_twin(float* acc, const float* x, const float* weight, float* y,
                                   uint16_t* yb, int rows, int dim, float eps, int offset) {
     if (!acc || !weight || (!y && !yb)) return VELOX_ERR_SHAPE;
-    return add_rms_norm_twin(acc, x, weight, y, yb, rows, dim, eps, offset);
+    return add_rms_norm_twin(acc, x, nullptr, weight, y, yb, rows, dim, eps, offset);
+}
+
+int velox_sm100_add_bf16_rms_norm_twin(float* acc, const uint16_t* xb, const float* weight, float* y,
+                                       uint16_t* yb, int rows, int dim, float eps, int offset) {
+    if (!acc || !xb || !weight || (!y && !yb)) return VELOX_ERR_SHAPE;
+    return add_rms_norm_twin(acc, nullptr, xb, weight, y, yb, rows, dim, eps, offset);
+}
+
+int velox_sm100_add_bf16(float* acc, const uint16_t* xb, long long len) {
+    if (!acc || !xb) return VELOX_ERR_SHAPE;
+    return add_bf16(acc, xb, len);
 }
 
 int velox_sm100_bf16_twin(const float* x, uint16_t* xb, long long len) { return bf16_twin(x, xb, len); }

@@ -115,7 +115,23 @@ enum ScratchSlot { SCRATCH_ACT_CODES = 0, SCRATCH_ACT_SCALES, SCRATCH_WEIGHT_BF1
                    SCRATCH_Y_F32, SCRATCH_SLOTS };
 void* scratch(ScratchSlot slot, size_t bytes);
 
-static inline int launch_status() { return (int)cudaGetLastError(); }
+// Counts kernel launches (for the benchmark's launch report) and returns the launch's status.
+void note_launch();
+static inline int launch_status() {
+    note_launch();
+    return (int)cudaGetLastError();
+}
+
+// Optional CUDA-event timing of the main kernels, the counterpart of the reference's
+// VELOX_GPU_TIMING (crates/velox-cuda/src/timing.rs:1-97): when enabled, an event pair brackets
+// the kernel on its launch stream; totals per class are read back after a synchronise.
+enum TimedClass { TIMED_GEMV = 0, TIMED_GEMM_FP4, TIMED_GEMM_FP8, TIMED_GEMM_BF16, TIMED_ACT_QUANT,
+                  TIMED_DEQUANT, TIMED_CLASSES };
+struct TimedRegion {
+    int slot;
+    explicit TimedRegion(int cls);
+    ~TimedRegion();
+};
 
 // check::weight + check::linear on the extents a C caller can state (check.rs:100-131).
 int check_view(const velox_sm100_view* v);

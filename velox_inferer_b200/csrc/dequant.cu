@@ -108,6 +108,7 @@ static int launch_dequant(const velox_sm100_view* v, OUT* out, long long ld_out,
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (blocks < 1) blocks = 1;
     cudaStream_t s = stream();
+    TimedRegion timed(TIMED_DEQUANT);
     switch (v->format) {
         case VELOX_FMT_NVFP4:
             dequant_rows_kernel<VELOX_FMT_NVFP4, OUT><<<(unsigned)blocks, 256, 0, s>>>(

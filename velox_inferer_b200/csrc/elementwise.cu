@@ -50,7 +50,8 @@ __global__ void bf16_twin_kernel(const float* __restrict__ x, uint16_t* __restri
 // One block per row: acc += x (when x is given), y = acc * rsqrt(mean(acc^2) + eps) * (offset + weight).
 __global__ void __launch_bounds__(256)
 add_rms_norm_twin_kernel(float* __restrict__ acc, const float* __restrict__ x,
-                         const float* __restrict__ weight, float* __restrict__ y,
+                         const uint16_t* __restrict__ xb, const float* __restrict__ weight,
+                         float* __restrict__ y,
                          uint16_t* __restrict__ yb, int dim, float eps, float offset) {
     __shared__ float red[8];
     const long long base = (long long)blockIdx.x * dim;
@@ -59,6 +60,9 @@ add_rms_norm_twin_kernel(float* __restrict__ acc, const float* __restrict__ x,
         float v = acc[base + c];
         if (x) {
             v += x[base + c];
+            acc[base + c] = v;
+        } else if (xb) {
+            v += bf16_bits_to_f32(xb[base + c]);
             acc[base + c] = v;
         }
         ss = fmaf(v, v, ss);
@@ -102,10 +106,22 @@ int bf16_twin(const float* x, uint16_t* xb, long long len) {
     return launch_status();
 }
 
-int add_rms_norm_twin(float* acc, const float* x, const float* weight, float* y, uint16_t* yb,
-                      int rows, int dim, float eps, int offset) {
+__global__ void add_bf16_kernel(float* __restrict__ acc, const uint16_t* __restrict__ xb, long long len) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < len;
+         i += (long long)gridDim.x * blockDim.x)
+        acc[i] += bf16_bits_to_f32(xb[i]);
+}
+
+int add_bf16(float* acc, const uint16_t* xb, long long len) {
+    if (len < 1) return 0;
+    add_bf16_kernel<<<grid_1d(len, 256), 256, 0, stream()>>>(acc, xb, len);
+    return launch_status();
+}
+
+int add_rms_norm_twin(float* acc, const float* x, const uint16_t* xb, const float* weight, float* y,
+                      uint16_t* yb, int rows, int dim, float eps, int offset) {
     if (rows < 1 || dim < 1) return VELOX_ERR_SHAPE;
-    add_rms_norm_twin_kernel<<<(unsigned)rows, 256, 0, stream()>>>(acc, x, weight, y, yb, dim, eps,
+    add_rms_norm_twin_kernel<<<(unsigned)rows, 256, 0, stream()>>>(acc, x, xb, weight, y, yb, dim, eps,
                                                                   offset ? 1.0f : 0.0f);
     return launch_status();
 }

@@ -1,14 +1,21 @@
 // Prefill GEMM on the 5th-generation tensor cores: y[m, rows] = x[m, k] . W^T for m > 16.
 //
-// One persistent CTA per SM walks output tiles of 128 tokens x 256 weight rows. Three roles:
-//   warp 0      TMA producer: cp.async.bulk.tensor tiles of x and W (128-byte swizzled rows) and,
-//               for NVFP4, whole 512-byte scale atoms, into a 4-stage shared-memory ring;
+// One persistent CTA per SM walks output tiles of 128 tokens x 256 weight rows. Roles:
+//   warp 0      operand producer: cp.async.bulk.tensor tiles of x and W (128-byte swizzled rows)
+//               into a 3-stage shared-memory ring;
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma with the accumulator in tensor
-//               memory (128 lanes x 256 f32 columns); for NVFP4 it first copies the scale atoms
-//               shared memory -> tensor memory (tcgen05.cp) and issues the block-scaled
-//               kind::mxf4nvf4 form, for FP8 kind::f8f6f4, for bf16 kind::f16;
+//               memory (128 lanes x 256 f32 columns): block-scaled kind::mxf4nvf4 for NVFP4,
+//               kind::f8f6f4 for FP8, kind::f16 for bf16;
 //   warps 2-5   epilogue: tcgen05.ld the accumulator, apply the per-tensor / per-row / per-token
-//               factors, optionally silu(gate)*up, write f32 and/or bf16.
+//               factors, optionally silu(gate)*up; bf16 tiles go through a swizzled staging
+//               buffer and a tensor-map store, f32 (or ragged) output is written directly.
+//               Tensor memory is handed back as soon as the last columns are in registers;
+//   warp 6      (NVFP4) scale producer: bulk copies of whole 512-byte scale atoms into a 4-stage
+//               ring of their own, so scales run ahead of the operands;
+//   warps 8-11  (NVFP4) scale movers: shared memory -> registers -> tensor memory (tcgen05.st),
+//               one warp per lane quadrant, into one of four column sets. Measured on B200, the
+//               tcgen05.cp route (twelve 32x128b copies per k-block on the MMA pipe) serialised
+//               with the MMAs and cost more than they did.
 // Tokens are the MMA M operand and weight rows the N operand, so a lane of the epilogue owns one
 // token and writes contiguous output columns. The stored NVFP4 layout is consumed as is: codes are
 // K-major with the lower k in the low nibble, and the 128-row x 4-group scale tiles
@@ -23,6 +30,8 @@
 // No TMA load here uses cluster multicast; each CTA fetches its own tiles.
 //
 // Reference counterpart (SIMT f32): linear_tiled_kernel, crates/velox-cuda/kernels/portable_model.cu:349-398.
+#include <cstdlib>
+
 #include <cuda.h>  // CUtensorMap types; the encode entry point is resolved at run time
 
 #include "common.cuh"
@@ -35,21 +44,27 @@ enum GemmKind { KIND_MXF4 = 0, KIND_F8 = 1, KIND_BF16 = 2 };
 constexpr int BM = 128;        // tokens per tile (MMA M)
 constexpr int BN = 256;        // weight rows per tile (MMA N): two 128-row halves
 constexpr int BK_BYTES = 128;  // bytes of K per row per stage: one swizzle row, four MMA k-steps
-constexpr int STAGES = 4;
+constexpr int OP_STAGES = 3;   // operand ring (x tile + W tile)
+constexpr int SF_STAGES = 4;   // scale ring in shared memory and scale column sets in tensor memory
 constexpr int A_BYTES = BM * BK_BYTES;
 constexpr int B_HALF_BYTES = 128 * BK_BYTES;
 constexpr int B_BYTES = 2 * B_HALF_BYTES;
+constexpr int OP_STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SFA_BYTES = 4 * 512;
 constexpr int SFB_BYTES = 2 * 4 * 512;
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SF_STAGE_BYTES = SFA_BYTES + SFB_BYTES;
+constexpr int STAGING_BYTES = 2 * 16384;  // 128 tokens x 128 bf16 columns as two swizzled 64-column boxes
+constexpr int OFF_STAGING = OP_STAGES * OP_STAGE_BYTES;
+constexpr int OFF_SF = OFF_STAGING + STAGING_BYTES;
+constexpr int OFF_BARS = OFF_SF + SF_STAGES * SF_STAGE_BYTES;
+constexpr int SMEM_BYTES = OFF_BARS + 1024 + 512;
 constexpr int TMEM_COLS = 512;
-constexpr int TMEM_SFA_COL = 256;  // 4 k-steps x 4 columns
-constexpr int TMEM_SFB_COL = 272;  // 4 k-steps x 8 columns
-constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_SF_COL = 256;  // scale sets follow the accumulator
+constexpr int TMEM_SF_SET = 48;   // per set: 16 columns of x scales, 32 columns of W scales
+constexpr int GEMM_THREADS = 384;
 
 enum { ST_OK = 0, ST_TIMEOUT_EMPTY = 1, ST_TIMEOUT_FULL = 2, ST_TIMEOUT_ACC_EMPTY = 3,
-       ST_TIMEOUT_ACC_FULL = 4 };
+       ST_TIMEOUT_ACC_FULL = 4, ST_TIMEOUT_SF = 5 };
 
 struct GemmParams {
     int m;
@@ -73,10 +88,29 @@ struct GemmParams {
     float* y;
     uint16_t* yb;
     long long ld, col;
+    int tma_store;  // bf16-only output that a tensor map over yb + col describes
     int* status;
+    int dbg;        // profiling builds only: 1 no epilogue at all, 2 loads only, 4 no staging writes / stores
 };
 
 __device__ int g_gemm_status = 0;
+
+#ifdef VX_GEMM_PROFILE
+// Per-CTA cycle counters of a profiling build: [0] producer waiting for a free stage, [1] producer
+// total, [2] MMA thread waiting for operands, [3] MMA thread waiting for the accumulator to drain,
+// [4] MMA thread total, [5] epilogue waiting for the accumulator, [6] epilogue total, [7] MMA
+// thread waiting for scales.
+__device__ long long g_gemm_prof[160][12];
+#define PROF_DECL long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
+#define PROF_T0(var) const long long var = clock64()
+#define PROF_ADD(slot, t0) prof[slot] += clock64() - (t0)
+#define PROF_OUT(slot) g_gemm_prof[blockIdx.x][slot] = prof[slot]
+#else
+#define PROF_DECL
+#define PROF_T0(var)
+#define PROF_ADD(slot, t0)
+#define PROF_OUT(slot)
+#endif
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------
 
@@ -115,11 +149,14 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
     return t;
 }
 
-// Bounded wait: false after ~2 s without the phase completing.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait: false after ~2 s without the phase completing. Between polls the thread sleeps
+// `backoff_ns`, so roles that wait for long stretches do not take issue slots from the warps
+// that are working.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t backoff_ns = 0) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = global_timer_ns();
     for (uint32_t spins = 1;; spins++) {
+        if (backoff_ns) __nanosleep(backoff_ns);
         if (mbar_try_wait(bar, parity)) return true;
         if ((spins & 255u) == 0 && global_timer_ns() - t0 > 2000000000ull) return false;
     }
@@ -131,6 +168,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
         : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(map), "r"(src), "r"(x), "r"(y)
+                 : "memory");
 }
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
@@ -153,19 +196,11 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                  : "memory");
 }
 
-// Shared-memory matrix descriptor, K-major. 128-byte swizzle: rows of 128 bytes, groups of eight
-// rows 1024 bytes apart. No swizzle (scale atoms): 16-byte rows, groups of eight 128 bytes apart.
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, groups of eight
+// rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
     return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t addr) {
-    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
-}
-
-__device__ __forceinline__ void tc_cp_sf(uint32_t tmem_col_addr, uint64_t desc) {
-    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col_addr), "l"(desc)
-                 : "memory");
 }
 
 template <int KIND>
@@ -209,6 +244,48 @@ __device__ __forceinline__ void tc_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// 32 lanes x 16 / x 32 consecutive 32-bit columns written from registers.
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+          "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+          "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+          "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+          "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts16(uint32_t addr, const uint4& v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+// Two f32 -> packed bf16 pair (round to nearest even), the first value in the low half.
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __float22bfloat162_rn(make_float2(lo, hi));
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 // Instruction descriptor: M = 128, N = 256, K-major operands, f32 accumulate.
 template <int KIND>
 __device__ __forceinline__ constexpr uint32_t instr_desc() {
@@ -223,23 +300,36 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
 template <int KIND, bool SWIGLU>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
-            const __grid_constant__ CUtensorMap tmap_b1, const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out,
+            const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = base + STAGES * STAGE_BYTES;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    const uint32_t acc_full = bars + 8u * (2 * STAGES);
-    const uint32_t acc_empty = bars + 8u * (2 * STAGES + 1);
-    const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 2);
+    const uint32_t staging = base + OFF_STAGING;
+    const uint32_t sf_ring = base + OFF_SF;
+    const uint32_t bars = base + OFF_BARS;
+    auto op_full = [&](int s) { return bars + 8u * s; };
+    auto op_empty = [&](int s) { return bars + 8u * (OP_STAGES + s); };
+    auto sf_full = [&](int s) { return bars + 8u * (2 * OP_STAGES + s); };
+    auto sf_empty = [&](int s) { return bars + 8u * (2 * OP_STAGES + SF_STAGES + s); };
+    auto tsf_full = [&](int s) { return bars + 8u * (2 * OP_STAGES + 2 * SF_STAGES + s); };
+    auto tsf_empty = [&](int s) { return bars + 8u * (2 * OP_STAGES + 3 * SF_STAGES + s); };
+    const uint32_t acc_full = bars + 8u * (2 * OP_STAGES + 4 * SF_STAGES);
+    const uint32_t acc_empty = acc_full + 8u;
+    const uint32_t tmem_slot = acc_full + 16u;
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
-            mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+        for (int s = 0; s < OP_STAGES; s++) {
+            mbar_init(op_full(s), 1);
+            mbar_init(op_empty(s), 1);
+        }
+        for (int s = 0; s < SF_STAGES; s++) {
+            mbar_init(sf_full(s), 1);
+            mbar_init(sf_empty(s), 4);
+            mbar_init(tsf_full(s), 4);
+            mbar_init(tsf_empty(s), 1);
         }
         mbar_init(acc_full, 1);
         mbar_init(acc_empty, 4);
@@ -247,6 +337,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b0) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b1) : "memory");
+        if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_out) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
@@ -262,163 +353,236 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int num_tiles = p.tiles_m * p.tiles_n;
 
     if (warp == 0) {
-        // ---------------- TMA producer ----------------
+        // ---------------- operand producer: x tile and the two W half tiles per k-block ----------------
         if (lane == 0) {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            PROF_DECL;
+            PROF_T0(t_all);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
-                const long long r0 = p.b_row0[0] + (long long)nt * p.b_tile_rows;
-                const long long r1 = p.b_row0[1] + (long long)nt * p.b_tile_rows;
+                const int r0 = (int)(p.b_row0[0] + (long long)nt * p.b_tile_rows);
+                const int r1 = (int)(p.b_row0[1] + (long long)nt * p.b_tile_rows);
                 for (int kb = 0; kb < p.k_blocks; kb++) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1u)) {
+                    PROF_T0(t_w);
+                    if (!mbar_wait(op_empty(stage), phase ^ 1u, 40)) {
                         atomicExch(p.status, ST_TIMEOUT_EMPTY);
                         ok = false;
                         break;
                     }
-                    const int steps = min(4, p.k_steps - 4 * kb);
-                    const uint32_t sa = base + stage * STAGE_BYTES;
+                    PROF_ADD(0, t_w);
+                    const uint32_t sa = base + stage * OP_STAGE_BYTES;
                     const uint32_t sb = sa + A_BYTES;
-                    uint32_t tx = A_BYTES + B_BYTES;
-                    const bool sf0 = KIND == KIND_MXF4 && r0 < p.b_rows_total[0];
-                    const bool sf1 = KIND == KIND_MXF4 && r1 < p.b_rows_total[1];
-                    if (KIND == KIND_MXF4) tx += (uint32_t)steps * 512u * (1u + (sf0 ? 1u : 0u) + (sf1 ? 1u : 0u));
-                    mbar_arrive_expect_tx(full_bar(stage), tx);
-                    tma_load_2d(sa, &tmap_a, full_bar(stage), (kb % p.a_k_blocks) * p.k_elems_per_block, mt * BM);
-                    tma_load_2d(sb, &tmap_b0, full_bar(stage), kx, (int)r0);
-                    tma_load_2d(sb + B_HALF_BYTES, &tmap_b1, full_bar(stage), kx, (int)r1);
-                    if (KIND == KIND_MXF4) {
-                        const uint32_t ssfa = sb + B_BYTES, ssfb = ssfa + SFA_BYTES;
-                        const long long atom = 4LL * kb;
-                        bulk_load_1d(ssfa, p.sfa + ((long long)mt * p.k_tiles64 + atom) * 512,
-                                     (uint32_t)steps * 512u, full_bar(stage));
-                        if (sf0)
-                            bulk_load_1d(ssfb, p.sfb[0] + ((r0 / 128) * p.k_tiles64 + atom) * 512,
-                                         (uint32_t)steps * 512u, full_bar(stage));
-                        if (sf1)
-                            bulk_load_1d(ssfb + 4 * 512, p.sfb[1] + ((r1 / 128) * p.k_tiles64 + atom) * 512,
-                                         (uint32_t)steps * 512u, full_bar(stage));
-                    }
-                    if (++stage == STAGES) {
+                    mbar_arrive_expect_tx(op_full(stage), A_BYTES + B_BYTES);
+                    const int kx = kb * p.k_elems_per_block;
+                    tma_load_2d(sa, &tmap_a, op_full(stage), (kb % p.a_k_blocks) * p.k_elems_per_block, mt * BM);
+                    tma_load_2d(sb, &tmap_b0, op_full(stage), kx, r0);
+                    tma_load_2d(sb + B_HALF_BYTES, &tmap_b1, op_full(stage), kx, r1);
+                    if (++stage == OP_STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
             }
             if (!ok) __nanosleep(200000);  // let copies already in flight land before the CTA exits
+            PROF_ADD(1, t_all);
+            PROF_OUT(0);
+            PROF_OUT(1);
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0, acc_phase = 0;
+            int stage = 0, sstage = 0;
+            uint32_t phase = 0, sphase = 0, acc_phase = 0;
             bool ok = true;
             const uint32_t idesc = instr_desc<KIND>();
+            PROF_DECL;
+            PROF_T0(t_all);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                PROF_T0(t_acc);
                 if (!mbar_wait(acc_empty, acc_phase ^ 1u)) {
                     atomicExch(p.status, ST_TIMEOUT_ACC_EMPTY);
                     break;
                 }
-                tc_fence_after();
+                PROF_ADD(3, t_acc);
                 for (int kb = 0; kb < p.k_blocks; kb++) {
-                    if (!mbar_wait(full_bar(stage), phase)) {
+                    PROF_T0(t_w);
+                    if (!mbar_wait(op_full(stage), phase)) {
                         atomicExch(p.status, ST_TIMEOUT_FULL);
                         ok = false;
                         break;
                     }
+                    PROF_ADD(2, t_w);
+                    if (KIND == KIND_MXF4) {
+                        PROF_T0(t_s);
+                        if (!mbar_wait(tsf_full(sstage), sphase)) {
+                            atomicExch(p.status, ST_TIMEOUT_SF);
+                            ok = false;
+                            break;
+                        }
+                        PROF_ADD(7, t_s);
+                    }
                     tc_fence_after();
                     const int steps = min(4, p.k_steps - 4 * kb);
-                    const uint32_t sa = base + stage * STAGE_BYTES;
+                    const uint32_t sa = base + stage * OP_STAGE_BYTES;
                     const uint32_t sb = sa + A_BYTES;
-                    if (KIND == KIND_MXF4) {
-                        const uint32_t ssfa = sb + B_BYTES, ssfb = ssfa + SFA_BYTES;
-                        for (int j = 0; j < steps; j++) {
-                            tc_cp_sf(tmem + TMEM_SFA_COL + 4 * j, smem_desc_sf(ssfa + 512 * j));
-                            tc_cp_sf(tmem + TMEM_SFB_COL + 8 * j, smem_desc_sf(ssfb + 512 * j));
-                            tc_cp_sf(tmem + TMEM_SFB_COL + 8 * j + 4, smem_desc_sf(ssfb + 4 * 512 + 512 * j));
-                        }
-                    }
                     const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
+                    const uint32_t tsf = tmem + TMEM_SF_COL + sstage * TMEM_SF_SET;
                     for (int j = 0; j < steps; j++) {
                         // advancing 32 bytes along K inside the swizzle row: +2 in the address field
                         tc_mma<KIND>(tmem, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u,
-                                     tmem + TMEM_SFA_COL + 4 * j, tmem + TMEM_SFB_COL + 8 * j);
+                                     tsf + 4 * j, tsf + 16 + 8 * j);
                     }
-                    tc_commit(empty_bar(stage));
-                    if (++stage == STAGES) {
+                    tc_commit(op_empty(stage));
+                    if (++stage == OP_STAGES) {
                         stage = 0;
                         phase ^= 1u;
+                    }
+                    if (KIND == KIND_MXF4) {
+                        tc_commit(tsf_empty(sstage));
+                        if (++sstage == SF_STAGES) {
+                            sstage = 0;
+                            sphase ^= 1u;
+                        }
                     }
                 }
                 if (ok) tc_commit(acc_full);
                 acc_phase ^= 1u;
             }
+            PROF_ADD(4, t_all);
+            PROF_OUT(2);
+            PROF_OUT(3);
+            PROF_OUT(4);
+            PROF_OUT(7);
         }
-    } else {
+    } else if (warp >= 2 && warp <= 5) {
         // ---------------- epilogue ----------------
         const int quad = warp % 4;
         uint32_t acc_phase = 0;
         const float d0 = p.wdiv[0] ? *p.wdiv[0] : 1.0f;
         const float d1 = p.wdiv[1] ? *p.wdiv[1] : 1.0f;
-        const float s_half[2] = {p.alpha / d0, p.alpha / d1};
+        const float s0 = p.alpha / d0, s1 = p.alpha / d1;
+        const uint16_t* cs0 = p.col_scale[0];
+        const uint16_t* cs1 = p.col_scale[1];
+        const long long cs_rows0 = p.b_rows_total[0], cs_rows1 = p.b_rows_total[1];
+        const long long vb0 = p.valid_begin[0], ve0 = p.valid_end[0], vb1 = p.valid_begin[1], ve1 = p.valid_end[1];
+        const bool store_thread = warp == 2 && lane == 0;
+        PROF_DECL;
+        PROF_T0(t_all);
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
-            if (!mbar_wait(acc_full, acc_phase)) {
+            PROF_T0(t_w);
+            if (!mbar_wait(acc_full, acc_phase, 100)) {
                 if (lane == 0) atomicExch(p.status, ST_TIMEOUT_ACC_FULL);
                 break;
             }
+            PROF_ADD(5, t_w);
             tc_fence_after();
-            const long long token = (long long)mt * BM + quad * 32 + lane;
+            const int row_in_tile = quad * 32 + lane;
+            const long long token = (long long)mt * BM + row_in_tile;
             const bool tok_ok = token < p.m;
             const float ts = (p.tok_scale && tok_ok) ? p.tok_scale[token] : 1.0f;
             const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
             const long long rbase[2] = {p.b_row0[0] + (long long)nt * p.b_tile_rows,
                                         p.b_row0[1] + (long long)nt * p.b_tile_rows};
             constexpr int CHUNKS = SWIGLU ? 4 : 8;
-            for (int ch = 0; ch < CHUNKS; ch++) {
-                uint32_t r[32], r2[32];
-                tc_ld32(taddr + ch * 32, r);
-                if (SWIGLU) tc_ld32(taddr + 128 + ch * 32, r2);
-                tc_wait_ld();
+            // Whole-tile bf16 output through shared memory and a tensor-map store: taken when the
+            // tile does not start left of the output's first column.
+            const bool staged = p.tma_store && rbase[0] >= p.out_row0;
+            auto process = [&](const int ch, const uint32_t (&r)[32], const uint32_t (&r2)[32]) {
+#ifdef VX_GEMM_PROFILE
+                if (p.dbg & 2) {
+                    if (r[3] == 0x7fc12345u) prof[11]++;
+                    return;
+                }
+#endif
+                if (staged && (ch & 1) == 0) {
+                    // the store that last read this 64-column box (two groups ago) must be done with it
+                    PROF_T0(t_s);
+                    if (store_thread) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    PROF_ADD(9, t_s);
+                }
+                PROF_T0(t_c);
                 const int half = SWIGLU ? 0 : ch / 4;
                 const long long row0 = rbase[half] + (ch % 4) * 32;   // first row of this chunk
                 const long long urow0 = rbase[1] + ch * 32;           // SwiGLU: matching up rows
+                // per-chunk factors hoisted out of the column loop
+                const float sg = (half ? s1 : s0) * ts;
+                const float su = s1 * ts;
+                const uint16_t* csg = half ? cs1 : cs0;
+                const long long csg_rows = half ? cs_rows1 : cs_rows0;
                 float v[32];
+#ifdef VX_GEMM_PROFILE
+                if (p.dbg & 8) {
+#pragma unroll
+                    for (int c = 0; c < 32; c++) v[c] = __uint_as_float(r[c]);
+                } else if (p.dbg & 16) {
+#pragma unroll
+                    for (int c = 0; c < 32; c++) v[c] = __uint_as_float(r[c]) * 1.5f;
+                } else
+#endif
 #pragma unroll
                 for (int c = 0; c < 32; c++) {
-                    float g = __uint_as_float(r[c]) * s_half[half] * ts;
-                    if (p.col_scale[half]) {
-                        const long long rr = row0 + c;
-                        g *= (rr < p.b_rows_total[half]) ? bf16_bits_to_f32(p.col_scale[half][rr]) : 0.0f;
-                    }
+                    float g = __uint_as_float(r[c]) * sg;
+                    if (csg) g *= (row0 + c < csg_rows) ? bf16_bits_to_f32(csg[row0 + c]) : 0.0f;
                     if (SWIGLU) {
-                        float u = __uint_as_float(r2[c]) * s_half[1] * ts;
-                        if (p.col_scale[1]) {
-                            const long long rr = urow0 + c;
-                            u *= (rr < p.b_rows_total[1]) ? bf16_bits_to_f32(p.col_scale[1][rr]) : 0.0f;
-                        }
-                        g = g / (1.0f + expf(-g)) * u;
+                        float u = __uint_as_float(r2[c]) * su;
+                        if (cs1) u *= (urow0 + c < cs_rows1) ? bf16_bits_to_f32(cs1[urow0 + c]) : 0.0f;
+                        g = g / (1.0f + __expf(-g)) * u;
                     }
                     v[c] = g;
                 }
-                if (tok_ok) {
+#ifdef VX_GEMM_PROFILE
+                if (v[31] == 1.2345e-30f && v[0] == 1.2345e-30f) prof[11]++;
+#endif
+                PROF_ADD(10, t_c);
+#ifdef VX_GEMM_PROFILE
+                if (p.dbg & 4) return;
+#endif
+                if (staged) {
+                    // box (ch / 2) % 2 holds 64 columns; 16-byte piece index XOR row % 8 (128-byte swizzle)
+                    const uint32_t box = staging + (uint32_t)((ch >> 1) & 1) * 16384u;
+                    const uint32_t rowp = box + (uint32_t)row_in_tile * 128u;
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        uint4 pk;
+                        pk.x = pack_bf16(v[8 * q], v[8 * q + 1]);
+                        pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
+                        pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
+                        pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
+                        const uint32_t piece = (uint32_t)((ch & 1) * 4 + q);
+                        sts16(rowp + ((piece ^ (uint32_t)(row_in_tile & 7)) << 4), pk);
+                    }
+                    if (ch & 1) {
+                        PROF_T0(t_s);
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        asm volatile("bar.sync 1, 128;" ::: "memory");
+                        PROF_ADD(9, t_s);
+                        if (store_thread) {
+                            tma_store_2d(&tmap_out, box, (int)(rbase[0] - p.out_row0) + (ch >> 1) * 64, mt * BM);
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                    }
+                } else if (tok_ok) {
                     const long long o0 = token * p.ld + p.col + (row0 - p.out_row0);
-                    const bool all = row0 >= p.valid_begin[half] && row0 + 32 <= p.valid_end[half];
+                    const long long vb = half ? vb1 : vb0, ve = half ? ve1 : ve0;
+                    const bool all = row0 >= vb && row0 + 32 <= ve;
                     if (all && p.yb && ((reinterpret_cast<uintptr_t>(p.yb + o0) & 15) == 0)) {
 #pragma unroll
                         for (int q = 0; q < 4; q++) {
                             uint4 pk;
-                            pk.x = (uint32_t)bf16_bits(v[8 * q]) | ((uint32_t)bf16_bits(v[8 * q + 1]) << 16);
-                            pk.y = (uint32_t)bf16_bits(v[8 * q + 2]) | ((uint32_t)bf16_bits(v[8 * q + 3]) << 16);
-                            pk.z = (uint32_t)bf16_bits(v[8 * q + 4]) | ((uint32_t)bf16_bits(v[8 * q + 5]) << 16);
-                            pk.w = (uint32_t)bf16_bits(v[8 * q + 6]) | ((uint32_t)bf16_bits(v[8 * q + 7]) << 16);
+                            pk.x = pack_bf16(v[8 * q], v[8 * q + 1]);
+                            pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
+                            pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
+                            pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
                             *reinterpret_cast<uint4*>(p.yb + o0 + 8 * q) = pk;
                         }
                     } else if (p.yb) {
 #pragma unroll
                         for (int c = 0; c < 32; c++)
-                            if (row0 + c >= p.valid_begin[half] && row0 + c < p.valid_end[half])
+                            if (row0 + c >= vb && row0 + c < ve)
                                 p.yb[o0 + c] = bf16_bits(v[c]);
                     }
                     if (all && p.y && ((reinterpret_cast<uintptr_t>(p.y + o0) & 15) == 0)) {
@@ -429,15 +593,145 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     } else if (p.y) {
 #pragma unroll
                         for (int c = 0; c < 32; c++)
-                            if (row0 + c >= p.valid_begin[half] && row0 + c < p.valid_end[half])
+                            if (row0 + c >= vb && row0 + c < ve)
                                 p.y[o0 + c] = v[c];
                     }
                 }
+            };
+            // Chunks are read from tensor memory one ahead of the one being processed, so the load
+            // latency hides behind the arithmetic and the shared-memory writes.
+            auto release_acc = [&]() {
+                // the whole accumulator is in registers: hand tensor memory back to the MMA issuer
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty);
+            };
+#ifdef VX_GEMM_PROFILE
+            if (p.dbg & 1) {
+                release_acc();
+                acc_phase ^= 1u;
+                continue;
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty);
+#endif
+            if (SWIGLU) {
+                for (int ch = 0; ch < CHUNKS; ch++) {
+                    uint32_t r[32], r2[32];
+                    tc_ld32(taddr + ch * 32, r);
+                    tc_ld32(taddr + 128 + ch * 32, r2);
+                    tc_wait_ld();
+                    if (ch == CHUNKS - 1) release_acc();
+                    process(ch, r, r2);
+                }
+            } else {
+                uint32_t ra[32], rb[32];
+                tc_ld32(taddr, ra);
+                tc_wait_ld();
+                for (int ch = 0; ch < CHUNKS; ch += 2) {
+                    tc_ld32(taddr + (ch + 1) * 32, rb);
+                    process(ch, ra, ra);
+                    tc_wait_ld();
+                    if (ch + 2 < CHUNKS)
+                        tc_ld32(taddr + (ch + 2) * 32, ra);
+                    else
+                        release_acc();
+                    process(ch + 1, rb, rb);
+                    if (ch + 2 < CHUNKS) tc_wait_ld();
+                }
+            }
             acc_phase ^= 1u;
+        }
+        if (store_thread) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        PROF_ADD(6, t_all);
+        if (warp == 2 && lane == 0) {
+            PROF_OUT(5);
+            PROF_OUT(6);
+            PROF_OUT(8);
+            PROF_OUT(9);
+            PROF_OUT(10);
+        }
+    } else if (KIND == KIND_MXF4 && warp == 6) {
+        // ---------------- scale producer: whole 512-byte atoms, x then the two W halves ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
+                const long long r0 = p.b_row0[0] + (long long)nt * p.b_tile_rows;
+                const long long r1 = p.b_row0[1] + (long long)nt * p.b_tile_rows;
+                const bool sf0 = r0 < p.b_rows_total[0], sf1 = r1 < p.b_rows_total[1];
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!mbar_wait(sf_empty(stage), phase ^ 1u, 100)) {
+                        atomicExch(p.status, ST_TIMEOUT_SF);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bytes = (uint32_t)min(4, p.k_steps - 4 * kb) * 512u;
+                    const uint32_t ssfa = sf_ring + stage * SF_STAGE_BYTES, ssfb = ssfa + SFA_BYTES;
+                    mbar_arrive_expect_tx(sf_full(stage), bytes * (1u + (sf0 ? 1u : 0u) + (sf1 ? 1u : 0u)));
+                    const long long atom = 4LL * kb;
+                    bulk_load_1d(ssfa, p.sfa + ((long long)mt * p.k_tiles64 + atom) * 512, bytes, sf_full(stage));
+                    if (sf0)
+                        bulk_load_1d(ssfb, p.sfb[0] + ((r0 / 128) * p.k_tiles64 + atom) * 512, bytes, sf_full(stage));
+                    if (sf1)
+                        bulk_load_1d(ssfb + 4 * 512, p.sfb[1] + ((r1 / 128) * p.k_tiles64 + atom) * 512, bytes,
+                                     sf_full(stage));
+                    if (++stage == SF_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (!ok) __nanosleep(200000);
+        }
+    } else if (KIND == KIND_MXF4 && warp >= 8) {
+        // ---------------- scale movers: shared memory -> tensor memory through registers ----------------
+        // Lane i of the warp serving lane quadrant q writes rows i, i+32, i+64, i+96 of each
+        // 128-row atom: the 16 bytes of atom row i are the four 32-bit columns of that atom,
+        // replicated in every quadrant as the block-scaled MMA reads them.
+        const int quad = warp % 4;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < p.k_blocks; kb++) {
+                if (!mbar_wait(sf_full(stage), phase, 100)) {
+                    if (lane == 0) atomicExch(p.status, ST_TIMEOUT_SF);
+                    ok = false;
+                    break;
+                }
+                const uint32_t ssfa = sf_ring + stage * SF_STAGE_BYTES + (uint32_t)lane * 16u;
+                uint32_t ra[16], rb[32];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint4 a = lds16(ssfa + 512 * j);
+                    ra[4 * j] = a.x; ra[4 * j + 1] = a.y; ra[4 * j + 2] = a.z; ra[4 * j + 3] = a.w;
+                    const uint4 b0 = lds16(ssfa + SFA_BYTES + 512 * j);
+                    const uint4 b1 = lds16(ssfa + SFA_BYTES + 2048 + 512 * j);
+                    rb[8 * j] = b0.x; rb[8 * j + 1] = b0.y; rb[8 * j + 2] = b0.z; rb[8 * j + 3] = b0.w;
+                    rb[8 * j + 4] = b1.x; rb[8 * j + 5] = b1.y; rb[8 * j + 6] = b1.z; rb[8 * j + 7] = b1.w;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sf_empty(stage));
+                // the MMAs that read this column set (SF_STAGES k-blocks ago) must have completed
+                if (!mbar_wait(tsf_empty(stage), phase ^ 1u, 100)) {
+                    if (lane == 0) atomicExch(p.status, ST_TIMEOUT_SF);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tsf = tmem + ((uint32_t)(quad * 32) << 16) + TMEM_SF_COL + stage * TMEM_SF_SET;
+                tc_st16(tsf, ra);
+                tc_st32(tsf + 16, rb);
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tsf_full(stage));
+                if (++stage == SF_STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
         }
     }
 
@@ -497,9 +791,28 @@ static int make_map(CUtensorMap* map, const void* ptr, bool bf16, long long rows
     return r == CUDA_SUCCESS ? 0 : VELOX_ERR_UNSUPPORTED;
 }
 
+// Tensor map over the bf16 output columns [col, col + out_cols) of yb, for whole-tile stores.
+// Leaves p.tma_store at 0 when the output is not bf16-only or not 16-byte friendly.
+static void make_out_map(CUtensorMap* map, GemmParams& p, long long out_cols, long long first_row) {
+    p.tma_store = 0;
+    if (!p.yb || p.y || p.ld % 8 != 0 || p.col % 8 != 0 || first_row % 8 != 0) return;
+    uint16_t* basep = p.yb + p.col;
+    if (reinterpret_cast<uintptr_t>(basep) & 15) return;
+    const cuuint64_t dims[2] = {(cuuint64_t)out_cols, (cuuint64_t)p.m};
+    const cuuint64_t strides[1] = {(cuuint64_t)p.ld * 2};
+    const cuuint32_t box[2] = {64u, 128u};
+    const cuuint32_t estr[2] = {1, 1};
+    if (encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, basep, dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+        p.tma_store = 1;
+}
+
 template <int KIND>
 static int launch(bool swiglu, const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1,
-                  const GemmParams& p) {
+                  GemmParams& p, long long out_cols, long long first_row) {
+    CUtensorMap mo = a;
+    make_out_map(&mo, p, out_cols, first_row);
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -510,16 +823,17 @@ static int launch(bool swiglu, const CUtensorMap& a, const CUtensorMap& b0, cons
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sms ? tiles : sms;
     cudaError_t e;
+    TimedRegion timed(KIND == KIND_MXF4 ? TIMED_GEMM_FP4 : KIND == KIND_F8 ? TIMED_GEMM_FP8 : TIMED_GEMM_BF16);
     if (swiglu) {
         auto kern = gemm_kernel<KIND, true>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream()>>>(a, b0, b1, p);
+        kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream()>>>(a, b0, b1, mo, p);
     } else {
         auto kern = gemm_kernel<KIND, false>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream()>>>(a, b0, b1, p);
+        kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream()>>>(a, b0, b1, mo, p);
     }
     return launch_status();
 }
@@ -529,6 +843,12 @@ static int* status_ptr() {
     if (!ptr) cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_gemm_status);
     return ptr;
 }
+
+#ifdef VX_GEMM_PROFILE
+extern "C" int velox_sm100_debug_profile(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, g_gemm_prof, sizeof(long long) * 160 * 12);
+}
+#endif
 
 int gemm_status_sync() {
     int v = -1;
@@ -553,6 +873,10 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
     p.col = a.col;
     p.status = status_ptr();
     p.alpha = 1.0f;
+#ifdef VX_GEMM_PROFILE
+    if (const char* e = getenv("VX_GEMM_DBG")) p.dbg = atoi(e);
+#endif
+
     if (!p.status) return VELOX_ERR_UNSUPPORTED;
 
     CUtensorMap ma, mb0, mb1;
@@ -600,7 +924,7 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
         if ((rc = make_map(&mb1, w1.w, false, w1.n, k / 2)) != 0) return rc;
         p.k_blocks = (p.k_steps + 3) / 4;
         p.a_k_blocks = p.k_blocks;
-        return launch<KIND_MXF4>(sw, ma, mb0, mb1, p);
+        return launch<KIND_MXF4>(sw, ma, mb0, mb1, p, w.rows, w.row_begin);
     }
 
     if (act == VELOX_ACT_FP8_ROW) {
@@ -631,7 +955,7 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
         if ((rc = make_map(&mb1, w1.w, false, w1.n, k)) != 0) return rc;
         p.k_blocks = (p.k_steps + 3) / 4;
         p.a_k_blocks = p.k_blocks;
-        return launch<KIND_F8>(sw, ma, mb0, mb1, p);
+        return launch<KIND_F8>(sw, ma, mb0, mb1, p, w.rows, 0);
     }
 
     if (act != VELOX_ACT_BF16) return VELOX_ERR_UNSUPPORTED;
@@ -680,7 +1004,7 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
     if ((rc = make_map(&mb0, wq, true, w.rows, kw)) != 0) return rc;
     if ((rc = make_map(&mb1, sw ? wq + (size_t)w.rows * kw : wq, true, w.rows, kw)) != 0) return rc;
     p.k_blocks = (p.k_steps + 3) / 4;
-    return launch<KIND_BF16>(sw, ma, mb0, mb1, p);
+    return launch<KIND_BF16>(sw, ma, mb0, mb1, p, w.rows, 0);
 }
 
 }  // namespace vx

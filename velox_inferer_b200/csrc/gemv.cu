@@ -366,6 +366,7 @@ static int launch_gemv(const GemvParams& p, long long units) {
         if (e != cudaSuccess) return (int)e;
     }
     const long long blocks = (units + GEMV_WARPS - 1) / GEMV_WARPS;
+    TimedRegion timed(TIMED_GEMV);
     kern<<<(unsigned)blocks, GEMV_WARPS * VX_WARP, smem, stream()>>>(p);
     return launch_status();
 }

@@ -40,8 +40,10 @@ int encode_nvfp4(const float* w, long long n, long long k, float amax, uint8_t* 
 int swiglu(const float* src, long long rows, int src_cols, int gate, int up, int width, float* out);
 int silu_mul(float* gate, const float* up, long long len);
 int add(float* acc, const float* x, long long len);
-int add_rms_norm_twin(float* acc, const float* x, const float* weight, float* y, uint16_t* yb,
-                      int rows, int dim, float eps, int offset);
+int add_bf16(float* acc, const uint16_t* xb, long long len);
+// acc += x (f32) or xb (bf16) when given, then the norm of acc.
+int add_rms_norm_twin(float* acc, const float* x, const uint16_t* xb, const float* weight, float* y,
+                      uint16_t* yb, int rows, int dim, float eps, int offset);
 int bf16_twin(const float* x, uint16_t* xb, long long len);
 
 }  // namespace vx

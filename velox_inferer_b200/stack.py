@@ -1,0 +1,190 @@
+"""A decoder's linear path as a tensor-parallel layer stack on NVFP4 weights.
+
+Per layer, in the op order of the reference's ``Stack::forward`` (crates/velox-core/src/model.rs
+:178-215) with attention replaced by a passthrough of the q projection::
+
+    h = rms_norm(x)               q, k, v = linear(h)          (k, v computed, unused)
+    x += all_reduce(linear(q, o)) h = rms_norm(x)
+    g = silu(linear(h, gate)) * linear(h, up)                  (one fused launch)
+    x += all_reduce(linear(g, down))
+
+Tensor parallelism (absent from the reference, which is single-device): q/k/v/gate/up are split by
+output rows (a rank keeps rows ``[r*N/p, (r+1)*N/p)`` re-based as a smaller parent with the same
+per-tensor divisor); o/down are split along K (codes are a byte-aligned column slice, block
+scales whole 512-byte atoms, same divisor: a re-layout of stored bytes, not a re-quantisation).
+One all-reduce of the bf16 partial sums follows each row-split projection.
+
+The geometry is the reference's ``qwen3-32b`` preset (crates/velox-core/src/plan.rs:59-72).
+Weights are synthetic: N(0, 0.02^2) f32 per matrix from a per-(layer, projection) seed, quantised
+on the device by ``encode_nvfp4``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+from .backend import Sm100Backend
+from .weights import ActPolicy, WeightFormat, WeightView, align256
+
+NV = WeightFormat.NVFP4
+
+
+@dataclass(frozen=True)
+class StackSpec:
+    layers: int = 64
+    hidden: int = 5120
+    intermediate: int = 25600
+    heads: int = 64
+    kv_heads: int = 8
+    head_dim: int = 128
+    norm_eps: float = 1e-6
+
+    @property
+    def q_dim(self) -> int:
+        return self.heads * self.head_dim
+
+    @property
+    def kv_dim(self) -> int:
+        return self.kv_heads * self.head_dim
+
+    def payload_bytes_per_layer(self) -> int:
+        h, i, q, kv = self.hidden, self.intermediate, self.q_dim, self.kv_dim
+        pb = NV.payload_bytes
+        return pb(q, h) + 2 * pb(kv, h) + pb(h, q) + 2 * pb(i, h) + pb(h, i)
+
+    def flops_per_token(self) -> int:
+        h, i, q, kv = self.hidden, self.intermediate, self.q_dim, self.kv_dim
+        return 2 * self.layers * (q * h + 2 * kv * h + h * q + 2 * i * h + h * i)
+
+
+# Static activation divisors per use (the reference keeps one per projection in the artifact,
+# `activation_input_divisor`): chosen so that e4m3(divisor * amax16 / 6) stays inside E4M3 for the
+# activations each projection sees in this stack (unit-RMS norm output; q ~ N(0, 1.4^2);
+# silu(g)*u with heavier tails).
+DIV_NORM_OUT = 256.0
+DIV_O_IN = 128.0
+DIV_DOWN_IN = 16.0
+
+
+def slice_rows_nvfp4(payload: torch.Tensor, n: int, k: int, begin: int, rows: int) -> torch.Tensor:
+    """Rows [begin, begin+rows) of an NVFP4 parent as a parent of its own (column split).
+    begin and rows are multiples of 128 so whole scale tiles move."""
+    assert begin % 128 == 0 and rows % 128 == 0
+    plane = align256(n * k // 2)
+    out = torch.zeros(align256(NV.payload_bytes(rows, k)), dtype=torch.uint8, device=payload.device)
+    out[: rows * k // 2] = payload[begin * k // 2:(begin + rows) * k // 2]
+    oplane = align256(rows * k // 2)
+    sb = begin * k // 16
+    out[oplane:oplane + rows * k // 16] = payload[plane + sb:plane + sb + rows * k // 16]
+    out[oplane + rows * k // 16:oplane + rows * k // 16 + 4] = payload[plane + n * k // 16:plane + n * k // 16 + 4]
+    return out
+
+
+def slice_k_nvfp4(payload: torch.Tensor, n: int, k: int, k_begin: int, k_len: int) -> torch.Tensor:
+    """Columns [k_begin, k_begin+k_len) of an NVFP4 parent as a parent [n, k_len] (row split).
+    k_begin and k_len are multiples of 64 so whole 512-byte scale atoms move."""
+    assert k_begin % 64 == 0 and k_len % 64 == 0
+    plane = align256(n * k // 2)
+    out = torch.zeros(align256(NV.payload_bytes(n, k_len)), dtype=torch.uint8, device=payload.device)
+    codes = payload[: n * k // 2].view(n, k // 2)[:, k_begin // 2:(k_begin + k_len) // 2]
+    out[: n * k_len // 2] = codes.reshape(-1)
+    atoms = payload[plane:plane + n * k // 16].view(n // 128, k // 64, 512)
+    oplane = align256(n * k_len // 2)
+    out[oplane:oplane + n * k_len // 16] = atoms[:, k_begin // 64:(k_begin + k_len) // 64, :].reshape(-1)
+    out[oplane + n * k_len // 16:oplane + n * k_len // 16 + 4] = payload[plane + n * k // 16:plane + n * k // 16 + 4]
+    return out
+
+
+@dataclass
+class LayerWeights:
+    q: WeightView
+    k: WeightView
+    v: WeightView
+    o: WeightView
+    gate: WeightView
+    up: WeightView
+    down: WeightView
+
+
+class LinearStack:
+    """The stack on one rank of a tensor-parallel group of ``world`` ranks."""
+
+    def __init__(self, backend: Sm100Backend, spec: StackSpec, max_tokens: int, rank: int = 0,
+                 world: int = 1, a4: bool = True, seed: int = 0, group=None):
+        self.b, self.spec, self.rank, self.world, self.group = backend, spec, rank, world, group
+        self.max_tokens = max_tokens
+        s = spec
+        assert s.q_dim % (128 * world) == 0 and s.kv_dim % (128 * world) == 0
+        assert s.intermediate % (128 * world) == 0
+        dev = backend.device
+        pol = (lambda d: ActPolicy.allow_a4(d)) if a4 else (lambda d: ActPolicy.a16_only())
+        self.layers: List[LayerWeights] = []
+        gen = torch.Generator(device=dev)
+        for layer in range(s.layers):
+            def make(proj: int, n: int, k: int) -> torch.Tensor:
+                gen.manual_seed(seed * 1_000_003 + layer * 16 + proj)
+                w = torch.randn(n, k, generator=gen, device=dev, dtype=torch.float32) * 0.02
+                return backend.encode_nvfp4(w)
+
+            def col(proj, n, k, div):
+                full = make(proj, n, k)
+                rows = n // world
+                buf = full if world == 1 else slice_rows_nvfp4(full, n, k, rank * rows, rows)
+                return WeightView.full(buf, NV, rows, k).with_act(pol(div))
+
+            def row(proj, n, k, div):
+                full = make(proj, n, k)
+                kl = k // world
+                buf = full if world == 1 else slice_k_nvfp4(full, n, k, rank * kl, kl)
+                return WeightView.full(buf, NV, n, kl).with_act(pol(div))
+
+            self.layers.append(LayerWeights(
+                q=col(0, s.q_dim, s.hidden, DIV_NORM_OUT), k=col(1, s.kv_dim, s.hidden, DIV_NORM_OUT),
+                v=col(2, s.kv_dim, s.hidden, DIV_NORM_OUT), o=row(3, s.hidden, s.q_dim, DIV_O_IN),
+                gate=col(4, s.intermediate, s.hidden, DIV_NORM_OUT),
+                up=col(5, s.intermediate, s.hidden, DIV_NORM_OUT),
+                down=row(6, s.hidden, s.intermediate, DIV_DOWN_IN)))
+        m = max_tokens
+        bf, f32 = torch.bfloat16, torch.float32
+        self.norm_w = torch.ones(s.hidden, dtype=f32, device=dev)
+        self.x = torch.zeros(m * s.hidden, dtype=f32, device=dev)       # residual stream
+        self.hb = torch.zeros(m * s.hidden, dtype=bf, device=dev)       # norm output (bf16 twin)
+        self.qb = torch.zeros(m * s.q_dim // world, dtype=bf, device=dev)
+        self.kb = torch.zeros(m * s.kv_dim // world, dtype=bf, device=dev)
+        self.vb = torch.zeros(m * s.kv_dim // world, dtype=bf, device=dev)
+        self.gb = torch.zeros(m * s.intermediate // world, dtype=bf, device=dev)
+        self.pb = torch.zeros(m * s.hidden, dtype=bf, device=dev)       # row-split partial sums
+        self.outb = torch.zeros(m * s.hidden, dtype=bf, device=dev)
+        self.weight_bytes = sum(v.buf.numel() for l in self.layers
+                                for v in (l.q, l.k, l.v, l.o, l.gate, l.up, l.down))
+
+    def _all_reduce(self, t: torch.Tensor) -> None:
+        if self.world > 1:
+            torch.distributed.all_reduce(t, group=self.group)
+
+    def forward(self, xb_in: torch.Tensor, m: int) -> torch.Tensor:
+        """One step over m tokens: xb_in is bf16 [m, hidden] on the device; returns the final
+        residual stream rounded to bf16 ([m, hidden], device)."""
+        b, s = self.b, self.spec
+        h = s.hidden
+        assert m <= self.max_tokens
+        self.x[: m * h].copy_(xb_in.reshape(-1)[: m * h])
+        first = True
+        for l in self.layers:
+            # x (+= previous down partial), h = rms_norm(x)
+            b.add_rms_norm_twin(self.x, None, self.norm_w, None, self.hb, m, h, s.norm_eps,
+                                xb=None if first else self.pb)
+            first = False
+            b.linear_bf16(self.hb, l.q, None, m, yb=self.qb)
+            b.linear_bf16(self.hb, l.k, None, m, yb=self.kb)
+            b.linear_bf16(self.hb, l.v, None, m, yb=self.vb)
+            b.linear_bf16(self.qb, l.o, None, m, yb=self.pb)       # attention passthrough: a = q
+            self._all_reduce(self.pb[: m * h])
+            b.add_rms_norm_twin(self.x, None, self.norm_w, None, self.hb, m, h, s.norm_eps, xb=self.pb)
+            b.linear_swiglu_twin(self.hb, l.gate, l.up, None, self.gb, m)
+            b.linear_bf16(self.gb, l.down, None, m, yb=self.pb)
+            self._all_reduce(self.pb[: m * h])
+        b.add_bf16(self.x, self.pb, m * h)
+        return b.bf16_twin_into(self.x, self.outb, m * h)
