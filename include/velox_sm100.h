@@ -34,6 +34,9 @@ extern "C" {
 
 #define VELOX_ERR_UNSUPPORTED (-1)
 #define VELOX_ERR_SHAPE (-2)
+/* velox_sm100_linear_nvfp4_a4_static only: the call needs more than the fixed scratch array holds. */
+#define VELOX_ERR_STATIC_SCRATCH (-3)
+#define VELOX_SM100_STATIC_SCRATCH_BYTES (8u << 20)
 
 /* Weight format codes: crates/velox-cuda/src/portable.rs:197-216. */
 #define VELOX_FMT_FP8_ROW_BF16 2
@@ -120,6 +123,31 @@ int velox_sm100_linear_view(const float* x, const velox_sm100_view* view, int m,
  * NULL, not both. */
 int velox_sm100_linear_bf16(const uint16_t* xb, const velox_sm100_view* view, int m, float* y,
                             uint16_t* yb);
+
+/* NVFP4 prefill linear that allocates nothing. It has no counterpart in the reference.
+ *
+ * For whom: hosts that may not call cudaMalloc while they run the model - a server whose memory
+ * planner has already handed every byte of the device to weights, KV cache and workspaces, a
+ * real-time loop that must not take the allocator's lock, a process whose allocations are
+ * audited or capped. The regular entry points keep the quantised activations of the tensor-core
+ * path (E2M1 codes and their scale atoms) in scratch that they cudaMalloc on first use and grow
+ * when a larger call arrives; this one keeps them in a fixed 8 MiB array inside the library
+ * image (VELOX_SM100_STATIC_SCRATCH_BYTES; every GPU that loads the library carries it until the
+ * process ends) and calls no cudaMalloc, cudaFree or other allocating routine, ever.
+ *
+ * Same result as velox_sm100_linear_bf16 for an NVFP4 view whose policy is AllowA4 at m > 16
+ * (activations rounded as VELOX_ACT_NVFP4 with the view's divisor). Anything else returns
+ * VELOX_ERR_UNSUPPORTED. The call needs align256(m*k/2) + ceil(m/128)*128*k/16 bytes of the
+ * array (m = 2048, k = 5120: 5.9 MiB); a larger call returns VELOX_ERR_STATIC_SCRATCH and does
+ * nothing.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ * that device current): make that first call before starting any stream capture.
+ * All calls on a device share the one array. Each call rewrites every byte it later reads, so
+ * contents left by an earlier call are harmless, but two calls whose kernels can run at the same
+ * time (different streams, or different threads) race on it: keep such calls on one stream. */
+int velox_sm100_linear_nvfp4_a4_static(const uint16_t* xb, const velox_sm100_view* view, int m,
+                                       float* y, uint16_t* yb);
 
 /* Backend::linear_swiglu (backend.rs:1102-1118): out[r][i] = silu(x_r . gate_i) * (x_r . up_i).
  * gate and up: same width, format and k; any two views (adjacent in one parent in either order,

@@ -54,6 +54,7 @@ SIGNATURES = {
     "velox_sm100_linear": (_I, [_VP, _VP, _I, _LL, _LL, _LL, _I, _I, _VP]),
     "velox_sm100_linear_view": (_I, [_VP, _PV, _I, _VP, _VP]),
     "velox_sm100_linear_bf16": (_I, [_VP, _PV, _I, _VP, _VP]),
+    "velox_sm100_linear_nvfp4_a4_static": (_I, [_VP, _PV, _I, _VP, _VP]),
     "velox_sm100_linear_swiglu": (_I, [_VP, _PV, _PV, _I, _VP, _VP]),
     "velox_sm100_linear_swiglu_bf16": (_I, [_VP, _PV, _PV, _I, _VP, _VP]),
     "velox_sm100_linear_swiglu_act": (_I, [_PV, _PV, _I, C.POINTER(C.c_float)]),

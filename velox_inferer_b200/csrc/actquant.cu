@@ -161,6 +161,17 @@ int quantize_act_nvfp4(const float* x, const uint16_t* xb, int m, long long k, f
     return launch_status();
 }
 
+// The same launch without the optional event timing (which creates events): for callers that must
+// not allocate anything.
+int quantize_act_nvfp4_untimed(const uint16_t* xb, int m, long long k, float divisor, uint8_t* codes,
+                               uint8_t* scale_atoms) {
+    if (m < 1 || k < 64 || k % 64 != 0) return VELOX_ERR_SHAPE;
+    const int rows_padded = (m + 127) / 128 * 128;
+    quantize_nvfp4_kernel<<<grid_for((long long)rows_padded * (k / 16)), 256, 0, stream()>>>(
+        nullptr, xb, m, rows_padded, k, divisor, codes, scale_atoms);
+    return launch_status();
+}
+
 int encode_nvfp4(const float* w, long long n, long long k, float amax, uint8_t* payload) {
     if (n < 128 || n % 128 != 0 || k < 64 || k % 64 != 0) return VELOX_ERR_SHAPE;
     const float divisor = amax > 0.0f ? 448.0f * 6.0f / amax : 1.0f;

@@ -31,6 +31,7 @@
 //
 // Reference counterpart (SIMT f32): linear_tiled_kernel, crates/velox-cuda/kernels/portable_model.cu:349-398.
 #include <cstdlib>
+#include <mutex>
 
 #include <cuda.h>  // CUtensorMap types; the encode entry point is resolved at run time
 
@@ -1008,3 +1009,113 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
 }
 
 }  // namespace vx
+
+// ---- prefill linear for callers that cannot allocate ------------------------------------------------
+//
+// The NVFP4 prefill path needs room for the quantised activations (codes and scale atoms). The
+// regular entry points take it from grow-only cudaMalloc'd scratch; this one keeps it in a fixed
+// array that is part of the library image, so nothing is allocated at any point.
+
+namespace vx {
+
+constexpr size_t STATIC_SCRATCH_BYTES = 8u << 20;  // 8 MiB per device, held until the process exits
+static __device__ __align__(256) uint8_t g_static_act_scratch[STATIC_SCRATCH_BYTES];
+
+// Device address of the array, per device ordinal. In host code the array's name is only a handle
+// for the runtime, not an address a kernel can use, so it is resolved once per device here.
+static uint8_t* g_static_scratch_ptr[64] = {};
+static int* g_static_status_ptr[64] = {};
+static std::mutex g_static_mu;
+
+static int static_scratch_setup(int dev, uint8_t** scratch_out, int** status_out) {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_scratch_ptr[dev]) {
+        void* ptr = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_act_scratch);
+        if (e != cudaSuccess) return (int)e;
+        void* st = nullptr;
+        e = cudaGetSymbolAddress(&st, g_gemm_status);
+        if (e != cudaSuccess) return (int)e;
+        g_static_scratch_ptr[dev] = static_cast<uint8_t*>(ptr);
+        g_static_status_ptr[dev] = static_cast<int*>(st);
+    }
+    *scratch_out = g_static_scratch_ptr[dev];
+    *status_out = g_static_status_ptr[dev];
+    return 0;
+}
+
+}  // namespace vx
+
+extern "C" int velox_sm100_linear_nvfp4_a4_static(const uint16_t* xb, const velox_sm100_view* view, int m,
+                                                  float* y, uint16_t* yb) {
+    using namespace vx;
+    if (!xb || (!y && !yb) || m <= 0) return VELOX_ERR_SHAPE;
+    int rc = check_view(view);
+    if (rc != 0) return rc;
+    const velox_sm100_view& w = *view;
+    if (w.format != VELOX_FMT_NVFP4 || w.policy != VELOX_POLICY_ALLOW_A4 || !(w.divisor > 0.0f) || m <= 16)
+        return VELOX_ERR_UNSUPPORTED;
+    if (!gemm_available()) return VELOX_ERR_UNSUPPORTED;
+    const long long k = w.k;
+    const int tiles_m = (m + BM - 1) / BM;
+    const size_t code_bytes = ((size_t)m * k / 2 + 255) / 256 * 256;
+    const size_t atom_bytes = (size_t)tiles_m * BM * k / 16;
+    if (code_bytes + atom_bytes > STATIC_SCRATCH_BYTES) return VELOX_ERR_STATIC_SCRATCH;
+
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return VELOX_ERR_UNSUPPORTED;
+    uint8_t* scratch_base = nullptr;
+    int* status = nullptr;
+    if ((rc = static_scratch_setup(dev, &scratch_base, &status)) != 0) return rc;
+    uint8_t* codes = scratch_base;
+    uint8_t* atoms = scratch_base + code_bytes;
+    // Every byte the GEMM reads is rewritten here: codes of rows < m, and the scale atoms of all
+    // tiles_m * 128 rows (zeros past m). Nothing left over from an earlier call is consumed.
+    if ((rc = quantize_act_nvfp4_untimed(xb, m, k, w.divisor, codes, atoms)) != 0) return rc;
+
+    GemmParams p{};
+    p.m = m;
+    p.tiles_m = tiles_m;
+    p.y = y;
+    p.yb = yb;
+    p.ld = w.rows;
+    p.col = 0;
+    p.status = status;
+    p.k_steps = (int)(k / 64);
+    p.k_blocks = (p.k_steps + 3) / 4;
+    p.a_k_blocks = p.k_blocks;
+    p.k_elems_per_block = 128;
+    p.k_tiles64 = (int)(k / 64);
+    p.sfa = atoms;
+    p.alpha = 1.0f / w.divisor;
+    const long long plane = align256(w.n * k / 2);
+    const long long base0 = w.row_begin / 128 * 128;
+    for (int h = 0; h < 2; h++) {
+        p.sfb[h] = w.w + plane;
+        p.wdiv[h] = reinterpret_cast<const float*>(w.w + plane + w.n * k / 16);
+        p.b_rows_total[h] = w.n;
+        p.valid_begin[h] = w.row_begin;
+        p.valid_end[h] = w.row_begin + w.rows;
+    }
+    p.b_row0[0] = base0;
+    p.b_row0[1] = base0 + 128;
+    p.b_tile_rows = 256;
+    p.tiles_n = (int)((w.row_begin + w.rows - base0 + 255) / 256);
+    p.out_row0 = w.row_begin;
+    CUtensorMap ma, mb, mo;
+    if ((rc = make_map(&ma, codes, false, m, k / 2)) != 0) return rc;
+    if ((rc = make_map(&mb, w.w, false, w.n, k / 2)) != 0) return rc;
+    mo = ma;
+    make_out_map(&mo, p, w.rows, w.row_begin);
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+    const int tiles = p.tiles_m * p.tiles_n;
+    auto kern = gemm_kernel<KIND_MXF4, false>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    kern<<<tiles < sms ? tiles : sms, GEMM_THREADS, SMEM_BYTES, stream()>>>(ma, mb, mb, mo, p);
+    return launch_status();
+}

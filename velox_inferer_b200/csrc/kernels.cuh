@@ -35,6 +35,8 @@ int quantize_act_fp8row(const float* x, const uint16_t* xb, int m, long long k, 
                         float* scales);
 int quantize_act_nvfp4(const float* x, const uint16_t* xb, int m, long long k, float divisor,
                        uint8_t* codes, uint8_t* scale_atoms);
+int quantize_act_nvfp4_untimed(const uint16_t* xb, int m, long long k, float divisor, uint8_t* codes,
+                               uint8_t* scale_atoms);
 int encode_nvfp4(const float* w, long long n, long long k, float amax, uint8_t* payload);
 
 int swiglu(const float* src, long long rows, int src_cols, int gate, int up, int width, float* out);
