@@ -250,7 +250,10 @@ int velox_sm100_linear_swiglu_act(const velox_sm100_view* gate, const velox_sm10
     return p.act;
 }
 
-int velox_sm100_debug_status(void) { return gemm_status_sync(); }
+int velox_sm100_debug_status(void) {
+    const int a = gemm_status_sync();
+    return a != 0 ? a : gemv_status_sync();
+}
 
 long long velox_sm100_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 

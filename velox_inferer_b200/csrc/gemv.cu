@@ -409,7 +409,12 @@ int gemv(const LinearArgs& a) {
     if (a.x && (reinterpret_cast<uintptr_t>(a.x) & 15)) return VELOX_ERR_UNSUPPORTED;
     if (a.xb && (reinterpret_cast<uintptr_t>(a.xb) & 15)) return VELOX_ERR_UNSUPPORTED;
     switch (a.w.format) {
-        case VELOX_FMT_NVFP4:
+        case VELOX_FMT_NVFP4: {
+            int rc = gemv_nvfp4_tma(a);
+            if (rc != VELOX_ERR_UNSUPPORTED) return rc;
+            rc = gemv_nvfp4_mma(a);
+            if (rc != VELOX_ERR_UNSUPPORTED) return rc;
+        }
             return a.swiglu ? gemv_fmt<VELOX_FMT_NVFP4, true>(a) : gemv_fmt<VELOX_FMT_NVFP4, false>(a);
         case VELOX_FMT_FP8_ROW_BF16:
             return a.swiglu ? gemv_fmt<VELOX_FMT_FP8_ROW_BF16, true>(a)

@@ -28,6 +28,11 @@ int dequant_rows_bf16(const velox_sm100_view* v, uint16_t* out, long long ld_out
 
 // Memory-bound path, m <= 16, k % 64 == 0.
 int gemv(const LinearArgs& a);
+// NVFP4 only: inner products on the tensor cores (mma.sync); k % 128 == 0.
+int gemv_nvfp4_mma(const LinearArgs& a);
+// NVFP4 only: TMA-staged weight stream + mma.sync; k % 128 == 0. The preferred decode kernel.
+int gemv_nvfp4_tma(const LinearArgs& a);
+int gemv_status_sync();
 // Any shape, any m: one warp per output row, per-element decode. Slow but total.
 int linear_generic(const LinearArgs& a);
 
