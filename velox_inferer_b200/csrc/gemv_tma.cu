@@ -56,6 +56,9 @@ struct TmaGemvParams {
     uint16_t* yb;
     long long ld, col;
     long long units;
+    int splits;            // K splits per 64-row unit (work items = units * splits)
+    float* partial;        // [items][V][64 rows][NT*8] partial sums when splits > 1
+    int* tickets;          // [units] arrival counters, zero between launches
     int* status;
     int dbg;   // profiling builds only: 1 no arithmetic, 2 no mma, 4 no unpack
 };
@@ -143,6 +146,7 @@ gemv_nvfp4_tma_kernel(const __grid_constant__ CUtensorMap map_codes0, const __gr
     const uint32_t bars = base + TG_STAGES * TG_STAGE_BYTES;
     __half* xs = reinterpret_cast<__half*>(gen_base + TG_STAGES * TG_STAGE_BYTES + 128);
     float* tok_scale = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(xs) + (size_t)p.m * xpitch * 2);
+    int* ticket_flag = reinterpret_cast<int*>(tok_scale + NT * 8 + TG_CONSUMERS);
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (TG_STAGES + s); };
 
@@ -164,12 +168,16 @@ gemv_nvfp4_tma_kernel(const __grid_constant__ CUtensorMap map_codes0, const __gr
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (long long unit = blockIdx.x; unit < p.units && ok; unit += gridDim.x) {
+            for (long long item = blockIdx.x; item < p.units * p.splits && ok; item += gridDim.x) {
+                const long long unit = item / p.splits;
+                const int split = (int)(item % p.splits);
+                const int ks_begin = (int)((long long)split * stages_per_pass / p.splits);
+                const int ks_end = (int)((long long)(split + 1) * stages_per_pass / p.splits);
                 for (int v = 0; v < V && ok; v++) {
                     const CUtensorMap* mc = v ? &map_codes1 : &map_codes0;
                     const long long tile128 = p.row_begin[v] / 128 + unit / 2;
                     const int row0 = (int)(tile128 * 128 + (unit % 2) * 64);
-                    for (int ks = 0; ks < stages_per_pass; ks++) {
+                    for (int ks = ks_begin; ks < ks_end; ks++) {
                         if (!wait(empty_bar(stage), phase ^ 1u)) {
                             atomicExch(p.status, 11);
                             ok = false;
@@ -296,7 +304,11 @@ gemv_nvfp4_tma_kernel(const __grid_constant__ CUtensorMap map_codes0, const __gr
         bool ok = true;
         const float div0 = *p.wdiv[0];
         const float div1 = SWIGLU ? *p.wdiv[1] : 1.0f;
-        for (long long unit = blockIdx.x; unit < p.units && ok; unit += gridDim.x) {
+        for (long long item = blockIdx.x; item < p.units * p.splits && ok; item += gridDim.x) {
+            const long long unit = item / p.splits;
+            const int split = (int)(item % p.splits);
+            const int ks_begin = (int)((long long)split * stages_per_pass / p.splits);
+            const int ks_end = (int)((long long)(split + 1) * stages_per_pass / p.splits);
             const int band0 = (int)(unit % 2) * 2;    // the unit's two bands of the 128-row tile
             float acc[V][NT][2][4];
 #pragma unroll
@@ -307,7 +319,7 @@ gemv_nvfp4_tma_kernel(const __grid_constant__ CUtensorMap map_codes0, const __gr
                     for (int q = 0; q < 4; q++) acc[v][nt][0][q] = acc[v][nt][1][q] = 0.0f;
 #pragma unroll
             for (int v = 0; v < V; v++) {
-                for (int ks = 0; ks < stages_per_pass && ok; ks++) {
+                for (int ks = ks_begin; ks < ks_end && ok; ks++) {
                     if (!wait(full_bar(stage), phase)) {
                         if (lane == 0) atomicExch(p.status, 12);
                         ok = false;
@@ -388,6 +400,49 @@ gemv_nvfp4_tma_kernel(const __grid_constant__ CUtensorMap map_codes0, const __gr
 
             // lane (g, t): d0, d1 = chunk row rho of the lo band, tokens 2t, 2t+1; d2, d3 = the hi band
             const long long tile128 = p.row_begin[0] / 128 + unit / 2;
+            bool finish = true;
+            if (p.splits > 1) {
+                // K-split: park this item's partial sums; the CTA that arrives last adds the splits
+                // in index order (so the result does not depend on arrival order) and finishes.
+                float* mine = p.partial + (size_t)item * (V * 64 * NT * 8);
+#pragma unroll
+                for (int v = 0; v < V; v++)
+#pragma unroll
+                    for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                        for (int q = 0; q < 4; q++)
+                            mine[((v * 64 + (q >> 1) * 32 + warp * 8 + rho) * NT + nt) * 8 + 2 * t + (q & 1)] =
+                                acc[v][nt][0][q] + acc[v][nt][1][q];
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"r"(TG_CONSUMERS * VX_WARP) : "memory");
+                if (threadIdx.x == 0) {
+                    const int prev = atomicAdd(p.tickets + unit, 1);
+                    const int last = prev == p.splits - 1;
+                    if (last) p.tickets[unit] = 0;     // self-cleaning for the next launch
+                    *ticket_flag = last;
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(TG_CONSUMERS * VX_WARP) : "memory");
+                finish = *ticket_flag != 0;
+                if (finish) {
+                    __threadfence();
+                    const float* first = p.partial + (size_t)(unit * p.splits) * (V * 64 * NT * 8);
+#pragma unroll
+                    for (int v = 0; v < V; v++)
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                const int idx = ((v * 64 + (q >> 1) * 32 + warp * 8 + rho) * NT + nt) * 8 + 2 * t + (q & 1);
+                                float sum = 0.0f;
+                                for (int sp = 0; sp < p.splits; sp++)
+                                    sum += __ldcg(first + (size_t)sp * (V * 64 * NT * 8) + idx);
+                                acc[v][nt][0][q] = sum;
+                                acc[v][nt][1][q] = 0.0f;
+                            }
+                }
+                asm volatile("bar.sync 1, %0;" ::"r"(TG_CONSUMERS * VX_WARP) : "memory");
+            }
+            if (finish) {
 #pragma unroll
             for (int nt = 0; nt < NT; nt++)
 #pragma unroll
@@ -404,6 +459,7 @@ gemv_nvfp4_tma_kernel(const __grid_constant__ CUtensorMap map_codes0, const __gr
                     if (p.y) p.y[o] = val;
                     if (p.yb) p.yb[o] = bf16_bits(val);
                 }
+            }
         }
     }
     __syncthreads();
@@ -454,10 +510,11 @@ static int launch_tma_gemv(const CUtensorMap (&maps)[2], const TmaGemvParams& p)
         if (sms <= 0) sms = 148;
     }
     const size_t smem = 1024 + (size_t)TG_STAGES * TG_STAGE_BYTES + 128 + (size_t)p.m * (p.k + TG_XPAD) * 2 +
-                        (size_t)NT * 8 * 4 + TG_CONSUMERS * 4;
+                        (size_t)NT * 8 * 4 + TG_CONSUMERS * 4 + 16;
     if (smem > 220 * 1024) return VELOX_ERR_UNSUPPORTED;
     const int per_sm = smem <= 56 * 1024 ? 4 : smem <= 74 * 1024 ? 3 : smem <= 112 * 1024 ? 2 : 1;
-    const long long blocks = p.units < (long long)per_sm * sms ? p.units : (long long)per_sm * sms;
+    const long long items = p.units * p.splits;
+    const long long blocks = items < (long long)per_sm * sms ? items : (long long)per_sm * sms;
     auto kern = gemv_nvfp4_tma_kernel<NT, SWIGLU>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
@@ -471,6 +528,26 @@ static int* gemv_status_ptr() {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
     if (!ptrs[dev]) cudaGetSymbolAddress(reinterpret_cast<void**>(&ptrs[dev]), g_gemv_status);
+    return ptrs[dev];
+}
+
+// Arrival counters of the K-split fix-up: zeroed when (re)allocated, returned to zero by the kernel.
+static int* gemv_tickets(size_t count) {
+    static int* ptrs[64] = {};
+    static size_t caps[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (count > caps[dev]) {
+        size_t n = count < 4096 ? 4096 : count * 2;
+        int* q = nullptr;
+        if (cudaMalloc(&q, n * sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        if (cudaMemsetAsync(q, 0, n * sizeof(int), stream()) != cudaSuccess) return nullptr;
+        ptrs[dev] = q;   // the old block stays allocated: queued work may still use it
+        caps[dev] = n;
+    }
     return ptrs[dev];
 }
 
@@ -507,6 +584,21 @@ int gemv_nvfp4_tma(const LinearArgs& a) {
     p.wdiv[1] = reinterpret_cast<const float*>(u.w + align256(u.n * u.k / 2) + u.n * u.k / 16);
     p.x = a.x; p.xb = a.xb; p.m = a.m; p.y = a.y; p.yb = a.yb; p.ld = a.ld; p.col = a.col;
     p.units = ((a.w.row_begin + a.w.rows - 1) / 128 - a.w.row_begin / 128 + 1) * 2;
+    // K splits: enough work items to give every SM about two, each split at least four stages long
+    {
+        const long long stages = (a.w.k + 255) / 256;
+        long long want = (2LL * 148 + p.units - 1) / p.units;
+        if (want > stages / 4) want = stages / 4;
+        if (want < 1) want = 1;
+        if (want > 16) want = 16;
+        p.splits = (int)want;
+        if (p.splits > 1) {
+            const size_t per_item = (size_t)(a.swiglu ? 2 : 1) * 64 * (a.m <= 8 ? 8 : 16) * sizeof(float);
+            p.partial = static_cast<float*>(scratch(SCRATCH_Y_F32, (size_t)p.units * p.splits * per_item));
+            p.tickets = gemv_tickets((size_t)p.units);
+            if (!p.partial || !p.tickets) return (int)cudaErrorMemoryAllocation;
+        }
+    }
     p.status = gemv_status_ptr();
 #ifdef VX_GEMM_PROFILE
     if (const char* e = getenv("VX_GEMV_DBG")) p.dbg = atoi(e);

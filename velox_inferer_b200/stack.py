@@ -170,6 +170,7 @@ class LinearStack:
         b, s = self.b, self.spec
         h = s.hidden
         assert m <= self.max_tokens
+        launches0 = b.launch_count()
         self.x[: m * h].copy_(xb_in.reshape(-1)[: m * h])
         first = True
         for l in self.layers:
@@ -187,4 +188,6 @@ class LinearStack:
             b.linear_bf16(self.gb, l.down, None, m, yb=self.pb)
             self._all_reduce(self.pb[: m * h])
         b.add_bf16(self.x, self.pb, m * h)
-        return b.bf16_twin_into(self.x, self.outb, m * h)
+        out = b.bf16_twin_into(self.x, self.outb, m * h)
+        self.launches_per_step = b.launch_count() - launches0   # this library's kernels per step
+        return out
