@@ -515,25 +515,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 const uint16_t* csg = half ? cs1 : cs0;
                 const long long csg_rows = half ? cs_rows1 : cs_rows0;
                 float v[32];
-#ifdef VX_GEMM_PROFILE
-                if (p.dbg & 8) {
+                // The per-row (FP8) scales are applied in a loop of their own: testing for them per
+                // element put 32 branches into every chunk and made this loop the slowest part of
+                // the kernel.
 #pragma unroll
-                    for (int c = 0; c < 32; c++) v[c] = __uint_as_float(r[c]);
-                } else if (p.dbg & 16) {
+                for (int c = 0; c < 32; c++) v[c] = __uint_as_float(r[c]) * sg;
+                if (csg) {
 #pragma unroll
-                    for (int c = 0; c < 32; c++) v[c] = __uint_as_float(r[c]) * 1.5f;
-                } else
-#endif
-#pragma unroll
-                for (int c = 0; c < 32; c++) {
-                    float g = __uint_as_float(r[c]) * sg;
-                    if (csg) g *= (row0 + c < csg_rows) ? bf16_bits_to_f32(csg[row0 + c]) : 0.0f;
-                    if (SWIGLU) {
-                        float u = __uint_as_float(r2[c]) * su;
-                        if (cs1) u *= (urow0 + c < cs_rows1) ? bf16_bits_to_f32(cs1[urow0 + c]) : 0.0f;
-                        g = g / (1.0f + __expf(-g)) * u;
+                    for (int c = 0; c < 32; c++) {
+                        const long long rr = row0 + c < csg_rows ? row0 + c : csg_rows - 1;
+                        const float f = bf16_bits_to_f32(csg[rr]);
+                        v[c] *= row0 + c < csg_rows ? f : 0.0f;
                     }
-                    v[c] = g;
+                }
+                if (SWIGLU) {
+                    float u[32];
+#pragma unroll
+                    for (int c = 0; c < 32; c++) u[c] = __uint_as_float(r2[c]) * su;
+                    if (cs1) {
+#pragma unroll
+                        for (int c = 0; c < 32; c++) {
+                            const long long rr = urow0 + c < cs_rows1 ? urow0 + c : cs_rows1 - 1;
+                            const float f = bf16_bits_to_f32(cs1[rr]);
+                            u[c] *= urow0 + c < cs_rows1 ? f : 0.0f;
+                        }
+                    }
+#pragma unroll
+                    for (int c = 0; c < 32; c++) v[c] = v[c] / (1.0f + __expf(-v[c])) * u[c];
                 }
 #ifdef VX_GEMM_PROFILE
                 if (v[31] == 1.2345e-30f && v[0] == 1.2345e-30f) prof[11]++;
@@ -625,6 +633,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 }
             } else {
                 uint32_t ra[32], rb[32];
+#ifdef VX_GEMM_PROFILE
+                if (p.dbg & 32) {
+                    // timing only: no tensor-memory loads at all, arithmetic and stores on dummies
+#pragma unroll
+                    for (int i = 0; i < 32; i++) ra[i] = rb[i] = 0x3f800000u + i + lane;
+                    for (int ch = 0; ch < CHUNKS; ch += 2) {
+                        process(ch, ra, ra);
+                        if (ch + 2 >= CHUNKS) release_acc();
+                        process(ch + 1, rb, rb);
+                    }
+                } else
+#endif
+                {
                 tc_ld32(taddr, ra);
                 tc_wait_ld();
                 for (int ch = 0; ch < CHUNKS; ch += 2) {
@@ -637,6 +658,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         release_acc();
                     process(ch + 1, rb, rb);
                     if (ch + 2 < CHUNKS) tc_wait_ld();
+                }
                 }
             }
             acc_phase ^= 1u;
