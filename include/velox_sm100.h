@@ -198,6 +198,23 @@ int velox_sm100_add(float* acc, const float* x, long long len);
  * acc); y = rms_norm(acc) * (offset + weight); yb (may be NULL) = bf16 twin of y. */
 int velox_sm100_add_rms_norm_twin(float* acc, const float* x, const float* weight, float* y,
                                   uint16_t* yb, int rows, int dim, float eps, int offset);
+/* FP4 activation twins, the counterpart for NVFP4 of the reference's int8 twins
+ * (Backend::add_rms_norm_q8 / linear_q8 / linear_swiglu_q8, backend.rs:1050-1100): the norm also
+ * writes its result as the activation blob the FP4 tensor-core linears read - E2M1 codes [rows,
+ * dim/2] and E4M3 scale atoms over ceil(rows/128)*128 rows, quantised from the bf16-rounded values
+ * with `divisor` exactly as quant::quantize_activations(Nvfp4{divisor}) does - so the projections
+ * that follow run without a quantisation pass. velox_sm100_linear_q4 / _swiglu_q4 take that blob
+ * in place of x; they serve NVFP4 views whose policy is AllowA4 with the same divisor at m > 16
+ * and return VELOX_ERR_UNSUPPORTED otherwise (use the bf16 entry points then). */
+int velox_sm100_add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float* weight,
+                                uint16_t* yb, uint8_t* codes, uint8_t* atoms, int rows, int dim, float eps,
+                                int offset, float divisor);
+int velox_sm100_linear_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                          const velox_sm100_view* view, int m, float* y, uint16_t* yb);
+int velox_sm100_linear_swiglu_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                                 const velox_sm100_view* gate, const velox_sm100_view* up, int m, float* out,
+                                 uint16_t* outb);
+
 /* The same with a bf16 addend (the all-reduced partial sums of a row-split projection): acc += xb,
  * then the norm. No counterpart in the reference, which has no tensor parallelism. */
 int velox_sm100_add_bf16_rms_norm_twin(float* acc, const uint16_t* xb, const float* weight, float* y,

@@ -189,3 +189,84 @@ def test_swiglu_bf16_only_output_staged(b):
     b.linear_swiglu_twin(xb, gate, up, None, outb, m)
     assert b.lib.velox_sm100_debug_status() == 0
     assert np.array_equal(bf16_bits(outb), f32_to_bf16_bits(out2.cpu().numpy()))
+
+
+def _atoms_of(scales: np.ndarray, m: int, k: int) -> np.ndarray:
+    from velox_inferer_b200.weights import nvfp4_scale_offset
+    mp = (m + 127) // 128 * 128
+    want = np.zeros(mp * k // 16, dtype=np.uint8)
+    r, g = np.meshgrid(np.arange(m), np.arange(k // 16), indexing="ij")
+    want[nvfp4_scale_offset(r, g, k)] = scales
+    return want
+
+
+@pytest.mark.parametrize("m,dim,addend", [(37, 640, "bf16"), (130, 256, "f32"), (300, 1024, None)])
+def test_norm_emits_the_nvfp4_blob_the_quantiser_would(b, m, dim, addend):
+    """add_rms_norm_q4: the bf16 twin matches the plain norm's, and codes and scale atoms are,
+    bit for bit, the oracle's Nvfp4 quantiser applied to that twin (padding rows zeroed)."""
+    r = O.Rng(31)
+    acc0, add, w = r.vec(m * dim, 1.0), r.vec(m * dim, 0.5), 1.0 + r.vec(dim, 0.1)
+    div = 256.0
+    acc = b.upload(acc0)
+    acc_ref = b.upload(acc0)
+    yb = torch.zeros(m * dim, dtype=torch.bfloat16, device=acc.device)
+    yb_ref = torch.zeros_like(yb)
+    q4 = b.q4_blob(m, dim)
+    q4[1].fill_(0xAB)                                     # stale bytes must not survive in padding rows
+    x = xb = None
+    if addend == "f32":
+        x = b.upload(add)
+    elif addend == "bf16":
+        xb = b.upload(add).to(torch.bfloat16)
+    b.add_rms_norm_q4(acc, x, b.upload(w), yb, q4, m, dim, 1e-6, div, xb=xb)
+    b.add_rms_norm_twin(acc_ref, x, b.upload(w), None, yb_ref, m, dim, 1e-6, xb=xb)
+    assert torch.equal(acc, acc_ref)
+    assert np.array_equal(bf16_bits(yb), bf16_bits(yb_ref))
+    twin = yb.float().cpu().numpy().reshape(m, dim)
+    wc, ws = O.act_codes_nvfp4(twin, div)
+    assert np.array_equal(q4[0].cpu().numpy().reshape(m, dim // 2), wc)
+    assert np.array_equal(q4[1].cpu().numpy(), _atoms_of(ws, m, dim))
+
+
+@pytest.mark.parametrize("n,k,m", [(256, 640, 37), (512, 1024, 300)])
+def test_linear_q4_equals_linear_bf16_on_the_same_twin(b, n, k, m):
+    """A linear fed the pre-quantised blob is the same launch minus the quantiser: bit-equal."""
+    r = O.Rng(41)
+    payload = r.random_weight(FMT_O[NV], n, k)
+    view = make_view(b, payload, NV, n, k, 0, n, ActPolicy.allow_a4(256.0))
+    acc = b.upload(r.vec(m * k, 1.0))
+    yb = torch.zeros(m * k, dtype=torch.bfloat16, device=acc.device)
+    q4 = b.q4_blob(m, k)
+    b.add_rms_norm_q4(acc, None, b.upload(np.ones(k, np.float32)), yb, q4, m, k, 1e-6, 256.0)
+    y1, y2 = b.alloc(m * n), b.alloc(m * n)
+    b.linear_bf16(yb, view, y1, m)
+    b.linear_q4(q4, 256.0, view, y2, m)
+    assert b.lib.velox_sm100_debug_status() == 0
+    assert torch.equal(y1, y2)
+    want = oracle_linear(yb.float().cpu().numpy(), payload, NV, n, k, 0, n, m, ActQuant(ActQuant.NVFP4, 256.0))
+    e_conf, e_rms = both_metrics(y2.cpu().numpy().reshape(m, n), want)
+    assert e_conf <= LINEAR_TOL and e_rms <= RMS_TOL
+    # SwiGLU twin
+    half = n // 2
+    g = make_view(b, payload, NV, n, k, 0, half, ActPolicy.allow_a4(256.0))
+    u = make_view(b, payload, NV, n, k, half, half, ActPolicy.allow_a4(256.0))
+    o1 = torch.zeros(m * half, dtype=torch.bfloat16, device=acc.device)
+    o2 = torch.zeros_like(o1)
+    b.linear_swiglu_twin(yb, g, u, None, o1, m)
+    b.linear_swiglu_q4(q4, 256.0, g, u, None, o2, m)
+    assert torch.equal(o1, o2)
+
+
+def test_linear_q4_refuses_what_the_fp4_gemm_does_not_serve(b):
+    from velox_inferer_b200.errors import Unsupported
+    r = O.Rng(43)
+    n, k = 256, 256
+    payload = r.random_weight(FMT_O[NV], n, k)
+    q4 = b.q4_blob(128, k)
+    y = b.alloc(128 * n)
+    with pytest.raises(Unsupported):                     # divisor differs from the view's
+        b.linear_q4(q4, 128.0, make_view(b, payload, NV, n, k, 0, n, ActPolicy.allow_a4(256.0)), y, 128)
+    with pytest.raises(Unsupported):                     # policy does not allow FP4 activations
+        b.linear_q4(q4, 256.0, make_view(b, payload, NV, n, k, 0, n, A16), y, 128)
+    with pytest.raises(Unsupported):                     # decode sizes take the bf16 GEMV
+        b.linear_q4(q4, 256.0, make_view(b, payload, NV, n, k, 0, n, ActPolicy.allow_a4(256.0)), y, 4)

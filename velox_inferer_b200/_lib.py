@@ -50,6 +50,9 @@ SIGNATURES = {
     "velox_sm100_timing_collect": (_I, [_VP, _VP, _I]),
     "velox_sm100_add_bf16_rms_norm_twin": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _F, _I]),
     "velox_sm100_add_bf16": (_I, [_VP, _VP, _LL]),
+    "velox_sm100_add_rms_norm_q4": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _F, _I, _F]),
+    "velox_sm100_linear_q4": (_I, [_VP, _VP, _F, _PV, _I, _VP, _VP]),
+    "velox_sm100_linear_swiglu_q4": (_I, [_VP, _VP, _F, _PV, _PV, _I, _VP, _VP]),
     "velox_sm100_linear_act": (_I, [_PV, _I, C.POINTER(C.c_float)]),
     "velox_sm100_linear": (_I, [_VP, _VP, _I, _LL, _LL, _LL, _I, _I, _VP]),
     "velox_sm100_linear_view": (_I, [_VP, _PV, _I, _VP, _VP]),

@@ -240,6 +240,33 @@ class Sm100Backend:
                                                       _ptr(y), _ptr(yb), rows, dim, eps,
                                                       int(offset)), "sm100 add_rms_norm_twin")
 
+    # -- FP4 activation twins (the NVFP4 counterpart of add_rms_norm_q8 / linear_q8 /
+    #    linear_swiglu_q8, crates/velox-core/src/backend.rs:1050-1100)
+    def q4_blob(self, rows: int, dim: int):
+        """Device storage for [rows, dim] NVFP4 activations: (codes, atoms)."""
+        codes = torch.zeros(rows * dim // 2, dtype=torch.uint8, device=self.device)
+        atoms = torch.zeros((rows + 127) // 128 * 128 * dim // 16, dtype=torch.uint8, device=self.device)
+        return codes, atoms
+
+    def add_rms_norm_q4(self, acc, x, weight, yb, q4, rows, dim, eps, divisor, offset=False, xb=None) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_add_rms_norm_q4(acc.data_ptr(), _ptr(x), _ptr(xb), weight.data_ptr(),
+                                                    _ptr(yb), q4[0].data_ptr(), q4[1].data_ptr(), rows, dim,
+                                                    eps, 1 if offset else 0, divisor), "sm100 add_rms_norm_q4")
+
+    def linear_q4(self, q4, divisor: float, w: WeightView, y: Optional[torch.Tensor], m: int,
+                  yb: Optional[torch.Tensor] = None) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_linear_q4(q4[0].data_ptr(), q4[1].data_ptr(), divisor,
+                                              C.byref(_view_struct(w)), m, _ptr(y), _ptr(yb)), "sm100 linear_q4")
+
+    def linear_swiglu_q4(self, q4, divisor: float, gate: WeightView, up: WeightView,
+                         out: Optional[torch.Tensor], outb: Optional[torch.Tensor], m: int) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_linear_swiglu_q4(q4[0].data_ptr(), q4[1].data_ptr(), divisor,
+                                                     C.byref(_view_struct(gate)), C.byref(_view_struct(up)), m,
+                                                     _ptr(out), _ptr(outb)), "sm100 linear_swiglu_q4")
+
     def add_bf16(self, acc, xb, n) -> None:
         self._bind()
         status(self.lib.velox_sm100_add_bf16(acc.data_ptr(), xb.data_ptr(), n), "sm100 add_bf16")

@@ -162,8 +162,9 @@ static int run(const LinearArgs& a, const Plan& p) {
 }
 
 static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_view* view, int m,
-                         float* y, uint16_t* yb, long long ld, long long col) {
-    if (m <= 0 || (!x && !xb) || (!y && !yb)) return VELOX_ERR_SHAPE;
+                         float* y, uint16_t* yb, long long ld, long long col,
+                         const uint8_t* q_codes = nullptr, const uint8_t* q_atoms = nullptr) {
+    if (m <= 0 || (!x && !xb && !q_codes) || (!y && !yb)) return VELOX_ERR_SHAPE;
     int rc = check_view(view);
     if (rc != 0) return rc;
     LinearArgs a{};
@@ -176,12 +177,17 @@ static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.yb = yb;
     a.ld = ld;
     a.col = col;
-    return run(a, plan_for(*view, m));
+    a.q_codes = q_codes;
+    a.q_atoms = q_atoms;
+    const Plan p = plan_for(*view, m);
+    if (q_codes && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;   // only the FP4 GEMM reads them
+    return run(a, p);
 }
 
 static int swiglu_common(const float* x, const uint16_t* xb, const velox_sm100_view* gate,
-                         const velox_sm100_view* up, int m, float* out, uint16_t* outb) {
-    if (m <= 0 || (!x && !xb) || (!out && !outb)) return VELOX_ERR_SHAPE;
+                         const velox_sm100_view* up, int m, float* out, uint16_t* outb,
+                         const uint8_t* q_codes = nullptr, const uint8_t* q_atoms = nullptr) {
+    if (m <= 0 || (!x && !xb && !q_codes) || (!out && !outb)) return VELOX_ERR_SHAPE;
     int rc = check_view(gate);
     if (rc != 0) return rc;
     rc = check_view(up);
@@ -207,7 +213,11 @@ static int swiglu_common(const float* x, const uint16_t* xb, const velox_sm100_v
                           : VELOX_POLICY_ALLOW_A8;
     }
     a.w.policy = a.up.policy = both.policy;
-    return run(a, plan_swiglu(both, *gate, *up, m));
+    a.q_codes = q_codes;
+    a.q_atoms = q_atoms;
+    const Plan p = plan_swiglu(both, *gate, *up, m);
+    if (q_codes && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
+    return run(a, p);
 }
 
 }  // namespace vx
@@ -386,6 +396,30 @@ int velox_sm100_add_bf16_rms_norm_twin(float* acc, const uint16_t* xb, const flo
                                        uint16_t* yb, int rows, int dim, float eps, int offset) {
     if (!acc || !xb || !weight || (!y && !yb)) return VELOX_ERR_SHAPE;
     return add_rms_norm_twin(acc, nullptr, xb, weight, y, yb, rows, dim, eps, offset);
+}
+
+int velox_sm100_add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float* weight,
+                                uint16_t* yb, uint8_t* codes, uint8_t* atoms, int rows, int dim, float eps,
+                                int offset, float divisor) {
+    if (!acc || !weight || !codes || !atoms) return VELOX_ERR_SHAPE;
+    return add_rms_norm_q4(acc, x, xb, weight, yb, codes, atoms, rows, dim, eps, offset, divisor);
+}
+
+int velox_sm100_linear_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                          const velox_sm100_view* view, int m, float* y, uint16_t* yb) {
+    if (!view || !codes || !atoms) return VELOX_ERR_SHAPE;
+    if (view->policy != VELOX_POLICY_ALLOW_A4 || view->divisor != divisor) return VELOX_ERR_UNSUPPORTED;
+    return linear_common(nullptr, nullptr, view, m, y, yb, view->rows, 0, codes, atoms);
+}
+
+int velox_sm100_linear_swiglu_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                                 const velox_sm100_view* gate, const velox_sm100_view* up, int m, float* out,
+                                 uint16_t* outb) {
+    if (!gate || !up || !codes || !atoms) return VELOX_ERR_SHAPE;
+    if (gate->policy != VELOX_POLICY_ALLOW_A4 || gate->divisor != divisor || up->policy != VELOX_POLICY_ALLOW_A4 ||
+        up->divisor != divisor)
+        return VELOX_ERR_UNSUPPORTED;
+    return swiglu_common(nullptr, nullptr, gate, up, m, out, outb, codes, atoms);
 }
 
 int velox_sm100_add_bf16(float* acc, const uint16_t* xb, long long len) {

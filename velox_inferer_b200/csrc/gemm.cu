@@ -909,11 +909,18 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
         if (w.format != VELOX_FMT_NVFP4) return VELOX_ERR_UNSUPPORTED;
         if (sw && (w.row_begin - w1.row_begin) % 128 != 0) return VELOX_ERR_UNSUPPORTED;
         const int mp = p.tiles_m * BM;
-        uint8_t* codes = static_cast<uint8_t*>(scratch(SCRATCH_ACT_CODES, (size_t)a.m * k / 2));
-        uint8_t* atoms = static_cast<uint8_t*>(scratch(SCRATCH_ACT_SCALES, (size_t)mp * k / 16));
-        if (!codes || !atoms) return (int)cudaErrorMemoryAllocation;
-        rc = quantize_act_nvfp4(a.x, a.xb, a.m, k, divisor, codes, atoms);
-        if (rc != 0) return rc;
+        const uint8_t* codes = a.q_codes;
+        const uint8_t* atoms = a.q_atoms;
+        if (!codes || !atoms) {
+            // no producer has quantised x already: do it here, into scratch
+            uint8_t* c = static_cast<uint8_t*>(scratch(SCRATCH_ACT_CODES, (size_t)a.m * k / 2));
+            uint8_t* s = static_cast<uint8_t*>(scratch(SCRATCH_ACT_SCALES, (size_t)mp * k / 16));
+            if (!c || !s) return (int)cudaErrorMemoryAllocation;
+            rc = quantize_act_nvfp4(a.x, a.xb, a.m, k, divisor, c, s);
+            if (rc != 0) return rc;
+            codes = c;
+            atoms = s;
+        }
         p.k_steps = (int)(k / 64);
         p.k_elems_per_block = 128;
         p.k_tiles64 = (int)(k / 64);

@@ -18,6 +18,8 @@ struct LinearArgs {
     int m;
     float* y;                // may be NULL when yb is set
     uint16_t* yb;            // bf16 twin of y, may be NULL
+    const uint8_t* q_codes;  // activations already quantised to NVFP4 (codes [m, k/2]) ...
+    const uint8_t* q_atoms;  // ... and their scale atoms; both NULL unless the caller has them
     long long ld;            // row stride of y / yb in elements
     long long col;           // first column written
 };
@@ -52,5 +54,7 @@ int add_bf16(float* acc, const uint16_t* xb, long long len);
 int add_rms_norm_twin(float* acc, const float* x, const uint16_t* xb, const float* weight, float* y,
                       uint16_t* yb, int rows, int dim, float eps, int offset);
 int bf16_twin(const float* x, uint16_t* xb, long long len);
+int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float* weight, uint16_t* yb,
+                    uint8_t* codes, uint8_t* atoms, int rows, int dim, float eps, int offset, float divisor);
 
 }  // namespace vx

@@ -157,6 +157,8 @@ class LinearStack:
         self.gb = torch.zeros(m * s.intermediate // world, dtype=bf, device=dev)
         self.pb = torch.zeros(m * s.hidden, dtype=bf, device=dev)       # row-split partial sums
         self.outb = torch.zeros(m * s.hidden, dtype=bf, device=dev)
+        self.a4 = a4
+        self.hq = backend.q4_blob(m, s.hidden)                          # norm output as NVFP4
         self.weight_bytes = sum(v.buf.numel() for l in self.layers
                                 for v in (l.q, l.k, l.v, l.o, l.gate, l.up, l.down))
 
@@ -173,18 +175,32 @@ class LinearStack:
         launches0 = b.launch_count()
         self.x[: m * h].copy_(xb_in.reshape(-1)[: m * h])
         first = True
+        # at prefill sizes the norm hands the FP4 linears their quantised input directly
+        q4 = self.a4 and m > 16
         for l in self.layers:
             # x (+= previous down partial), h = rms_norm(x)
-            b.add_rms_norm_twin(self.x, None, self.norm_w, None, self.hb, m, h, s.norm_eps,
-                                xb=None if first else self.pb)
+            if q4:
+                b.add_rms_norm_q4(self.x, None, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT,
+                                  xb=None if first else self.pb)
+                b.linear_q4(self.hq, DIV_NORM_OUT, l.q, None, m, yb=self.qb)
+                b.linear_q4(self.hq, DIV_NORM_OUT, l.k, None, m, yb=self.kb)
+                b.linear_q4(self.hq, DIV_NORM_OUT, l.v, None, m, yb=self.vb)
+            else:
+                b.add_rms_norm_twin(self.x, None, self.norm_w, None, self.hb, m, h, s.norm_eps,
+                                    xb=None if first else self.pb)
+                b.linear_bf16(self.hb, l.q, None, m, yb=self.qb)
+                b.linear_bf16(self.hb, l.k, None, m, yb=self.kb)
+                b.linear_bf16(self.hb, l.v, None, m, yb=self.vb)
             first = False
-            b.linear_bf16(self.hb, l.q, None, m, yb=self.qb)
-            b.linear_bf16(self.hb, l.k, None, m, yb=self.kb)
-            b.linear_bf16(self.hb, l.v, None, m, yb=self.vb)
             b.linear_bf16(self.qb, l.o, None, m, yb=self.pb)       # attention passthrough: a = q
             self._all_reduce(self.pb[: m * h])
-            b.add_rms_norm_twin(self.x, None, self.norm_w, None, self.hb, m, h, s.norm_eps, xb=self.pb)
-            b.linear_swiglu_twin(self.hb, l.gate, l.up, None, self.gb, m)
+            if q4:
+                b.add_rms_norm_q4(self.x, None, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT,
+                                  xb=self.pb)
+                b.linear_swiglu_q4(self.hq, DIV_NORM_OUT, l.gate, l.up, None, self.gb, m)
+            else:
+                b.add_rms_norm_twin(self.x, None, self.norm_w, None, self.hb, m, h, s.norm_eps, xb=self.pb)
+                b.linear_swiglu_twin(self.hb, l.gate, l.up, None, self.gb, m)
             b.linear_bf16(self.gb, l.down, None, m, yb=self.pb)
             self._all_reduce(self.pb[: m * h])
         b.add_bf16(self.x, self.pb, m * h)
