@@ -62,7 +62,9 @@ constexpr int SMEM_BYTES = OFF_BARS + 1024 + 512;
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_SF_COL = 256;  // scale sets follow the accumulator
 constexpr int TMEM_SF_SET = 48;   // per set: 16 columns of x scales, 32 columns of W scales
-constexpr int GEMM_THREADS = 384;
+constexpr int GEMM_THREADS = 512;
+constexpr int EPI_WARP0 = 4;     // warps 4..11 drain the accumulator, two per lane quadrant
+constexpr int MOVER_WARP0 = 12;  // warps 12..15 move scales into tensor memory
 
 enum { ST_OK = 0, ST_TIMEOUT_EMPTY = 1, ST_TIMEOUT_FULL = 2, ST_TIMEOUT_ACC_EMPTY = 3,
        ST_TIMEOUT_ACC_FULL = 4, ST_TIMEOUT_SF = 5 };
@@ -91,7 +93,7 @@ struct GemmParams {
     long long ld, col;
     int tma_store;  // bf16-only output that a tensor map over yb + col describes
     int* status;
-    int dbg;        // profiling builds only: 1 no epilogue at all, 2 loads only, 4 no staging writes / stores
+    int dbg;        // profiling builds only: 1 no epilogue at all, 2 loads only, 4 no staging writes / stores, 8 no operand loads
 };
 
 __device__ int g_gemm_status = 0;
@@ -142,6 +144,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
+}
+
+// One lane of a converged warp, chosen by the hardware; the same lane every time it is asked.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
 }
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
@@ -333,7 +346,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             mbar_init(tsf_empty(s), 1);
         }
         mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 4);
+        mbar_init(acc_empty, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b0) : "memory");
@@ -355,70 +368,108 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
     if (warp == 0) {
         // ---------------- operand producer: x tile and the two W half tiles per k-block ----------------
-        if (lane == 0) {
+        // (whole warp in the loop, one elected lane issuing, as in the MMA warp below)
+        {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            const bool leader = elect_one();
             PROF_DECL;
             PROF_T0(t_all);
+#ifdef VX_GEMM_PROFILE
+            if (p.dbg & 64) ok = false;   // MMA-rate probe: nobody but the issuer and the epilogue runs
+#endif
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
                 const int r0 = (int)(p.b_row0[0] + (long long)nt * p.b_tile_rows);
                 const int r1 = (int)(p.b_row0[1] + (long long)nt * p.b_tile_rows);
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     PROF_T0(t_w);
-                    if (!mbar_wait(op_empty(stage), phase ^ 1u, 40)) {
-                        atomicExch(p.status, ST_TIMEOUT_EMPTY);
+                    if (!mbar_wait(op_empty(stage), phase ^ 1u, 20)) {
+                        if (leader) atomicExch(p.status, ST_TIMEOUT_EMPTY);
                         ok = false;
                         break;
                     }
                     PROF_ADD(0, t_w);
                     const uint32_t sa = base + stage * OP_STAGE_BYTES;
                     const uint32_t sb = sa + A_BYTES;
-                    mbar_arrive_expect_tx(op_full(stage), A_BYTES + B_BYTES);
                     const int kx = kb * p.k_elems_per_block;
-                    tma_load_2d(sa, &tmap_a, op_full(stage), (kb % p.a_k_blocks) * p.k_elems_per_block, mt * BM);
-                    tma_load_2d(sb, &tmap_b0, op_full(stage), kx, r0);
-                    tma_load_2d(sb + B_HALF_BYTES, &tmap_b1, op_full(stage), kx, r1);
+                    if (leader) {
+#ifdef VX_GEMM_PROFILE
+                        if (p.dbg & 8) {   // timing only: operands are whatever the stage holds
+                            mbar_arrive(op_full(stage));
+                        } else
+#endif
+                        {
+                            mbar_arrive_expect_tx(op_full(stage), A_BYTES + B_BYTES);
+                            tma_load_2d(sa, &tmap_a, op_full(stage), (kb % p.a_k_blocks) * p.k_elems_per_block,
+                                        mt * BM);
+                            tma_load_2d(sb, &tmap_b0, op_full(stage), kx, r0);
+                            tma_load_2d(sb + B_HALF_BYTES, &tmap_b1, op_full(stage), kx, r1);
+                        }
+                    }
                     if (++stage == OP_STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
             }
-            if (!ok) __nanosleep(200000);  // let copies already in flight land before the CTA exits
+            if (!ok && !(p.dbg & 64)) __nanosleep(200000);  // let copies already in flight land before the CTA exits
             PROF_ADD(1, t_all);
-            PROF_OUT(0);
-            PROF_OUT(1);
+            if (leader) {
+                PROF_OUT(0);
+                PROF_OUT(1);
+            }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (lane == 0) {
+        // The whole warp walks the loop and one elected lane issues: addresses, descriptors and
+        // barrier operands are then warp-uniform values, which is what the asynchronous tensor
+        // instructions take; a loop run by a single diverged lane pays a register move per operand.
+        {
             int stage = 0, sstage = 0;
             uint32_t phase = 0, sphase = 0, acc_phase = 0;
             bool ok = true;
             const uint32_t idesc = instr_desc<KIND>();
+            const bool leader = elect_one();
             PROF_DECL;
             PROF_T0(t_all);
+#ifdef VX_GEMM_PROFILE
+            const unsigned long long ns0 = global_timer_ns();
+#endif
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 PROF_T0(t_acc);
                 if (!mbar_wait(acc_empty, acc_phase ^ 1u)) {
-                    atomicExch(p.status, ST_TIMEOUT_ACC_EMPTY);
+                    if (leader) atomicExch(p.status, ST_TIMEOUT_ACC_EMPTY);
                     break;
                 }
                 PROF_ADD(3, t_acc);
                 for (int kb = 0; kb < p.k_blocks; kb++) {
+#ifdef VX_GEMM_PROFILE
+                    if (p.dbg & 64) {   // MMA-rate probe: back-to-back MMAs on whatever shared memory holds
+                        const uint32_t pb = (p.dbg & 4096) ? base + (kb % OP_STAGES) * OP_STAGE_BYTES : base;
+                        const uint64_t da = smem_desc_sw128(pb), db = smem_desc_sw128(pb + A_BYTES);
+                        if (leader) {
+                            for (int j = 0; j < 4; j++)
+                                tc_mma<KIND>(tmem, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u,
+                                             tmem + TMEM_SF_COL + 4 * j, tmem + TMEM_SF_COL + 16 + 8 * j);
+                            if (p.dbg & 1024) tc_commit(op_empty(kb % OP_STAGES));
+                        }
+                        if (p.dbg & 2048) { mbar_try_wait(op_full(0), 1); tc_fence_after(); }
+                        continue;
+                    }
+#endif
                     PROF_T0(t_w);
                     if (!mbar_wait(op_full(stage), phase)) {
-                        atomicExch(p.status, ST_TIMEOUT_FULL);
+                        if (leader) atomicExch(p.status, ST_TIMEOUT_FULL);
                         ok = false;
                         break;
                     }
                     PROF_ADD(2, t_w);
-                    if (KIND == KIND_MXF4) {
+                    if (KIND == KIND_MXF4 && !(p.dbg & 16384)) {
                         PROF_T0(t_s);
                         if (!mbar_wait(tsf_full(sstage), sphase)) {
-                            atomicExch(p.status, ST_TIMEOUT_SF);
+                            if (leader) atomicExch(p.status, ST_TIMEOUT_SF);
                             ok = false;
                             break;
                         }
@@ -430,36 +481,54 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t sb = sa + A_BYTES;
                     const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
                     const uint32_t tsf = tmem + TMEM_SF_COL + sstage * TMEM_SF_SET;
-                    for (int j = 0; j < steps; j++) {
+                    PROF_T0(t_i);
+                    if (leader) {
                         // advancing 32 bytes along K inside the swizzle row: +2 in the address field
-                        tc_mma<KIND>(tmem, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u,
-                                     tsf + 4 * j, tsf + 16 + 8 * j);
+                        if (steps == 4) {
+                            tc_mma<KIND>(tmem, da, db, idesc, kb != 0 ? 1u : 0u, tsf, tsf + 16);
+                            tc_mma<KIND>(tmem, da + 2u, db + 2u, idesc, 1u, tsf + 4, tsf + 24);
+                            tc_mma<KIND>(tmem, da + 4u, db + 4u, idesc, 1u, tsf + 8, tsf + 32);
+                            tc_mma<KIND>(tmem, da + 6u, db + 6u, idesc, 1u, tsf + 12, tsf + 40);
+                        } else {
+                            for (int j = 0; j < steps; j++)
+                                tc_mma<KIND>(tmem, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u,
+                                             tsf + 4 * j, tsf + 16 + 8 * j);
+                        }
+                        tc_commit(op_empty(stage));
+                        if (KIND == KIND_MXF4 && !(p.dbg & 16384)) tc_commit(tsf_empty(sstage));
                     }
-                    tc_commit(op_empty(stage));
+                    PROF_ADD(11, t_i);
                     if (++stage == OP_STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                     if (KIND == KIND_MXF4) {
-                        tc_commit(tsf_empty(sstage));
                         if (++sstage == SF_STAGES) {
                             sstage = 0;
                             sphase ^= 1u;
                         }
                     }
                 }
-                if (ok) tc_commit(acc_full);
+                if (ok && leader) tc_commit(acc_full);
                 acc_phase ^= 1u;
             }
             PROF_ADD(4, t_all);
-            PROF_OUT(2);
-            PROF_OUT(3);
-            PROF_OUT(4);
-            PROF_OUT(7);
+#ifdef VX_GEMM_PROFILE
+            prof[9] = (long long)(global_timer_ns() - ns0);   // wall time of this warp's loop, ns
+#endif
+            if (leader) {
+                PROF_OUT(9);
+                PROF_OUT(2);
+                PROF_OUT(3);
+                PROF_OUT(4);
+                PROF_OUT(7);
+                PROF_OUT(11);
+            }
         }
-    } else if (warp >= 2 && warp <= 5) {
-        // ---------------- epilogue ----------------
+    } else if (warp >= EPI_WARP0 && warp < EPI_WARP0 + 8) {
+        // ---------------- epilogue: eight warps, two per lane quadrant, each taking half the columns ----------------
         const int quad = warp % 4;
+        const int hsel = (warp - EPI_WARP0) / 4;
         uint32_t acc_phase = 0;
         const float d0 = p.wdiv[0] ? *p.wdiv[0] : 1.0f;
         const float d1 = p.wdiv[1] ? *p.wdiv[1] : 1.0f;
@@ -468,13 +537,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const uint16_t* cs1 = p.col_scale[1];
         const long long cs_rows0 = p.b_rows_total[0], cs_rows1 = p.b_rows_total[1];
         const long long vb0 = p.valid_begin[0], ve0 = p.valid_end[0], vb1 = p.valid_begin[1], ve1 = p.valid_end[1];
-        const bool store_thread = warp == 2 && lane == 0;
+        const bool store_thread = (warp - EPI_WARP0) % 4 == 0 && lane == 0;   // one per column half
+        const uint32_t my_box = staging + (uint32_t)hsel * 16384u;
+        const int bar_id = 1 + hsel;                                          // the four warps of a half
+        constexpr int CHUNKS = SWIGLU ? 4 : 8;   // 32-column output chunks in a tile
+        constexpr int MINE = CHUNKS / 2;         // ... of which this warp takes half
         PROF_DECL;
         PROF_T0(t_all);
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
             const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
             PROF_T0(t_w);
-            if (!mbar_wait(acc_full, acc_phase, 100)) {
+            if (!mbar_wait(acc_full, acc_phase, 60)) {
                 if (lane == 0) atomicExch(p.status, ST_TIMEOUT_ACC_FULL);
                 break;
             }
@@ -487,37 +560,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
             const long long rbase[2] = {p.b_row0[0] + (long long)nt * p.b_tile_rows,
                                         p.b_row0[1] + (long long)nt * p.b_tile_rows};
-            constexpr int CHUNKS = SWIGLU ? 4 : 8;
             // Whole-tile bf16 output through shared memory and a tensor-map store: taken when the
             // tile does not start left of the output's first column.
             const bool staged = p.tma_store && rbase[0] >= p.out_row0;
-            auto process = [&](const int ch, const uint32_t (&r)[32], const uint32_t (&r2)[32]) {
-#ifdef VX_GEMM_PROFILE
-                if (p.dbg & 2) {
-                    if (r[3] == 0x7fc12345u) prof[11]++;
-                    return;
-                }
-#endif
-                if (staged && (ch & 1) == 0) {
-                    // the store that last read this 64-column box (two groups ago) must be done with it
-                    PROF_T0(t_s);
-                    if (store_thread) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                    asm volatile("bar.sync 1, 128;" ::: "memory");
-                    PROF_ADD(9, t_s);
-                }
-                PROF_T0(t_c);
+            // chunk ch of the accumulator (and its partner in the up half) -> 32 finished values
+            auto compute = [&](const int ch, const uint32_t (&r)[32], const uint32_t (&r2)[32], float (&v)[32]) {
                 const int half = SWIGLU ? 0 : ch / 4;
                 const long long row0 = rbase[half] + (ch % 4) * 32;   // first row of this chunk
                 const long long urow0 = rbase[1] + ch * 32;           // SwiGLU: matching up rows
-                // per-chunk factors hoisted out of the column loop
                 const float sg = (half ? s1 : s0) * ts;
                 const float su = s1 * ts;
                 const uint16_t* csg = half ? cs1 : cs0;
                 const long long csg_rows = half ? cs_rows1 : cs_rows0;
-                float v[32];
                 // The per-row (FP8) scales are applied in a loop of their own: testing for them per
-                // element put 32 branches into every chunk and made this loop the slowest part of
-                // the kernel.
+                // element puts 32 branches into every chunk.
 #pragma unroll
                 for (int c = 0; c < 32; c++) v[c] = __uint_as_float(r[c]) * sg;
                 if (csg) {
@@ -543,17 +599,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
                     for (int c = 0; c < 32; c++) v[c] = v[c] / (1.0f + __expf(-v[c])) * u[c];
                 }
-#ifdef VX_GEMM_PROFILE
-                if (v[31] == 1.2345e-30f && v[0] == 1.2345e-30f) prof[11]++;
-#endif
-                PROF_ADD(10, t_c);
-#ifdef VX_GEMM_PROFILE
-                if (p.dbg & 4) return;
-#endif
-                if (staged) {
-                    // box (ch / 2) % 2 holds 64 columns; 16-byte piece index XOR row % 8 (128-byte swizzle)
-                    const uint32_t box = staging + (uint32_t)((ch >> 1) & 1) * 16384u;
-                    const uint32_t rowp = box + (uint32_t)row_in_tile * 128u;
+            };
+            auto store_direct = [&](const int ch, const float (&v)[32]) {
+                if (!tok_ok) return;
+                const int half = SWIGLU ? 0 : ch / 4;
+                const long long row0 = rbase[half] + (ch % 4) * 32;
+                const long long o0 = token * p.ld + p.col + (row0 - p.out_row0);
+                const long long vb = half ? vb1 : vb0, ve = half ? ve1 : ve0;
+                const bool all = row0 >= vb && row0 + 32 <= ve;
+                if (all && p.yb && ((reinterpret_cast<uintptr_t>(p.yb + o0) & 15) == 0)) {
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         uint4 pk;
@@ -561,56 +615,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
                         pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
                         pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
-                        const uint32_t piece = (uint32_t)((ch & 1) * 4 + q);
-                        sts16(rowp + ((piece ^ (uint32_t)(row_in_tile & 7)) << 4), pk);
+                        *reinterpret_cast<uint4*>(p.yb + o0 + 8 * q) = pk;
                     }
-                    if (ch & 1) {
-                        PROF_T0(t_s);
-                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                        asm volatile("bar.sync 1, 128;" ::: "memory");
-                        PROF_ADD(9, t_s);
-                        if (store_thread) {
-                            tma_store_2d(&tmap_out, box, (int)(rbase[0] - p.out_row0) + (ch >> 1) * 64, mt * BM);
-                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                        }
-                    }
-                } else if (tok_ok) {
-                    const long long o0 = token * p.ld + p.col + (row0 - p.out_row0);
-                    const long long vb = half ? vb1 : vb0, ve = half ? ve1 : ve0;
-                    const bool all = row0 >= vb && row0 + 32 <= ve;
-                    if (all && p.yb && ((reinterpret_cast<uintptr_t>(p.yb + o0) & 15) == 0)) {
+                } else if (p.yb) {
 #pragma unroll
-                        for (int q = 0; q < 4; q++) {
-                            uint4 pk;
-                            pk.x = pack_bf16(v[8 * q], v[8 * q + 1]);
-                            pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
-                            pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
-                            pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
-                            *reinterpret_cast<uint4*>(p.yb + o0 + 8 * q) = pk;
-                        }
-                    } else if (p.yb) {
+                    for (int c = 0; c < 32; c++)
+                        if (row0 + c >= vb && row0 + c < ve) p.yb[o0 + c] = bf16_bits(v[c]);
+                }
+                if (all && p.y && ((reinterpret_cast<uintptr_t>(p.y + o0) & 15) == 0)) {
 #pragma unroll
-                        for (int c = 0; c < 32; c++)
-                            if (row0 + c >= vb && row0 + c < ve)
-                                p.yb[o0 + c] = bf16_bits(v[c]);
-                    }
-                    if (all && p.y && ((reinterpret_cast<uintptr_t>(p.y + o0) & 15) == 0)) {
+                    for (int q = 0; q < 8; q++)
+                        *reinterpret_cast<float4*>(p.y + o0 + 4 * q) =
+                            make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                } else if (p.y) {
 #pragma unroll
-                        for (int q = 0; q < 8; q++)
-                            *reinterpret_cast<float4*>(p.y + o0 + 4 * q) =
-                                make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                    } else if (p.y) {
-#pragma unroll
-                        for (int c = 0; c < 32; c++)
-                            if (row0 + c >= vb && row0 + c < ve)
-                                p.y[o0 + c] = v[c];
-                    }
+                    for (int c = 0; c < 32; c++)
+                        if (row0 + c >= vb && row0 + c < ve) p.y[o0 + c] = v[c];
                 }
             };
-            // Chunks are read from tensor memory one ahead of the one being processed, so the load
-            // latency hides behind the arithmetic and the shared-memory writes.
             auto release_acc = [&]() {
-                // the whole accumulator is in registers: hand tensor memory back to the MMA issuer
+                // this warp's part of the accumulator is in registers: hand it back to the MMA issuer
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(acc_empty);
@@ -622,92 +646,124 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 continue;
             }
 #endif
-            if (SWIGLU) {
-                for (int ch = 0; ch < CHUNKS; ch++) {
-                    uint32_t r[32], r2[32];
-                    tc_ld32(taddr + ch * 32, r);
-                    tc_ld32(taddr + 128 + ch * 32, r2);
-                    tc_wait_ld();
-                    if (ch == CHUNKS - 1) release_acc();
-                    process(ch, r, r2);
-                }
-            } else {
-                uint32_t ra[32], rb[32];
-#ifdef VX_GEMM_PROFILE
-                if (p.dbg & 32) {
-                    // timing only: no tensor-memory loads at all, arithmetic and stores on dummies
+            if (staged) {
+                // Drain first: finish this warp's values and keep them as packed bf16 (16 registers
+                // per chunk), release tensor memory so the next tile's MMAs can start, and only then
+                // spend time on shared-memory staging and the tensor-map stores.
+                uint32_t pk[MINE][16];
 #pragma unroll
-                    for (int i = 0; i < 32; i++) ra[i] = rb[i] = 0x3f800000u + i + lane;
-                    for (int ch = 0; ch < CHUNKS; ch += 2) {
-                        process(ch, ra, ra);
-                        if (ch + 2 >= CHUNKS) release_acc();
-                        process(ch + 1, rb, rb);
-                    }
-                } else
-#endif
-                {
-                tc_ld32(taddr, ra);
-                tc_wait_ld();
-                for (int ch = 0; ch < CHUNKS; ch += 2) {
-                    tc_ld32(taddr + (ch + 1) * 32, rb);
-                    process(ch, ra, ra);
+                for (int i = 0; i < MINE; i++) {
+                    const int ch = hsel * MINE + i;
+                    uint32_t r[32], r2[32];
+                    float v[32];
+                    tc_ld32(taddr + ch * 32, r);
+                    if (SWIGLU) tc_ld32(taddr + 128 + ch * 32, r2);
                     tc_wait_ld();
-                    if (ch + 2 < CHUNKS)
-                        tc_ld32(taddr + (ch + 2) * 32, ra);
-                    else
-                        release_acc();
-                    process(ch + 1, rb, rb);
-                    if (ch + 2 < CHUNKS) tc_wait_ld();
+                    if (i == MINE - 1) release_acc();
+                    compute(ch, r, SWIGLU ? r2 : r, v);
+#pragma unroll
+                    for (int c = 0; c < 16; c++) pk[i][c] = pack_bf16(v[2 * c], v[2 * c + 1]);
                 }
+                PROF_T0(t_c);
+#pragma unroll
+                for (int bx = 0; bx < MINE / 2; bx++) {
+                    // the store that last read this half's 64-column box must be done with it
+                    if (store_thread) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+                    const uint32_t rowp = my_box + (uint32_t)row_in_tile * 128u;
+#pragma unroll
+                    for (int i2 = 0; i2 < 2; i2++) {
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            // 16-byte piece index XOR row % 8 (128-byte swizzle)
+                            const uint4 w4 = make_uint4(pk[2 * bx + i2][4 * q], pk[2 * bx + i2][4 * q + 1],
+                                                        pk[2 * bx + i2][4 * q + 2], pk[2 * bx + i2][4 * q + 3]);
+                            const uint32_t piece = (uint32_t)(i2 * 4 + q);
+                            sts16(rowp + ((piece ^ (uint32_t)(row_in_tile & 7)) << 4), w4);
+                        }
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+                    if (store_thread) {
+                        tma_store_2d(&tmap_out, my_box,
+                                     (int)(rbase[0] - p.out_row0) + (hsel * (MINE / 2) + bx) * 64, mt * BM);
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
+                PROF_ADD(10, t_c);
+            } else {
+                for (int i = 0; i < MINE; i++) {
+                    const int ch = hsel * MINE + i;
+                    uint32_t r[32], r2[32];
+                    float v[32];
+                    tc_ld32(taddr + ch * 32, r);
+                    if (SWIGLU) tc_ld32(taddr + 128 + ch * 32, r2);
+                    tc_wait_ld();
+                    if (i == MINE - 1) release_acc();
+                    compute(ch, r, SWIGLU ? r2 : r, v);
+                    store_direct(ch, v);
                 }
             }
             acc_phase ^= 1u;
         }
         if (store_thread) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         PROF_ADD(6, t_all);
-        if (warp == 2 && lane == 0) {
+        if (warp == EPI_WARP0 && lane == 0) {
             PROF_OUT(5);
             PROF_OUT(6);
-            PROF_OUT(8);
-            PROF_OUT(9);
             PROF_OUT(10);
         }
-    } else if (KIND == KIND_MXF4 && warp == 6) {
+    } else if (KIND == KIND_MXF4 && warp == 2) {
         // ---------------- scale producer: whole 512-byte atoms, x then the two W halves ----------------
-        if (lane == 0) {
+        {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            const bool leader = elect_one();
+#ifdef VX_GEMM_PROFILE
+            if (p.dbg & (64 | 16384)) ok = false;
+#endif
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
                 const long long r0 = p.b_row0[0] + (long long)nt * p.b_tile_rows;
                 const long long r1 = p.b_row0[1] + (long long)nt * p.b_tile_rows;
                 const bool sf0 = r0 < p.b_rows_total[0], sf1 = r1 < p.b_rows_total[1];
                 for (int kb = 0; kb < p.k_blocks; kb++) {
-                    if (!mbar_wait(sf_empty(stage), phase ^ 1u, 100)) {
-                        atomicExch(p.status, ST_TIMEOUT_SF);
+                    if (!mbar_wait(sf_empty(stage), phase ^ 1u, 50)) {
+                        if (leader) atomicExch(p.status, ST_TIMEOUT_SF);
                         ok = false;
                         break;
                     }
                     const uint32_t bytes = (uint32_t)min(4, p.k_steps - 4 * kb) * 512u;
                     const uint32_t ssfa = sf_ring + stage * SF_STAGE_BYTES, ssfb = ssfa + SFA_BYTES;
-                    mbar_arrive_expect_tx(sf_full(stage), bytes * (1u + (sf0 ? 1u : 0u) + (sf1 ? 1u : 0u)));
                     const long long atom = 4LL * kb;
-                    bulk_load_1d(ssfa, p.sfa + ((long long)mt * p.k_tiles64 + atom) * 512, bytes, sf_full(stage));
-                    if (sf0)
-                        bulk_load_1d(ssfb, p.sfb[0] + ((r0 / 128) * p.k_tiles64 + atom) * 512, bytes, sf_full(stage));
-                    if (sf1)
-                        bulk_load_1d(ssfb + 4 * 512, p.sfb[1] + ((r1 / 128) * p.k_tiles64 + atom) * 512, bytes,
-                                     sf_full(stage));
+                    if (leader) {
+#ifdef VX_GEMM_PROFILE
+                        if (p.dbg & 256) {   // timing only: no scale copies
+                            mbar_arrive(sf_full(stage));
+                        } else
+#endif
+                        {
+                            mbar_arrive_expect_tx(sf_full(stage), bytes * (1u + (sf0 ? 1u : 0u) + (sf1 ? 1u : 0u)));
+                            bulk_load_1d(ssfa, p.sfa + ((long long)mt * p.k_tiles64 + atom) * 512, bytes,
+                                         sf_full(stage));
+                            if (sf0)
+                                bulk_load_1d(ssfb, p.sfb[0] + ((r0 / 128) * p.k_tiles64 + atom) * 512, bytes,
+                                             sf_full(stage));
+                            if (sf1)
+                                bulk_load_1d(ssfb + 4 * 512, p.sfb[1] + ((r1 / 128) * p.k_tiles64 + atom) * 512,
+                                             bytes, sf_full(stage));
+                        }
+                    }
                     if (++stage == SF_STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
             }
-            if (!ok) __nanosleep(200000);
+            if (!ok && !(p.dbg & (64 | 16384))) __nanosleep(200000);
         }
-    } else if (KIND == KIND_MXF4 && warp >= 8) {
+    } else if (KIND == KIND_MXF4 && warp >= MOVER_WARP0) {
         // ---------------- scale movers: shared memory -> tensor memory through registers ----------------
         // Lane i of the warp serving lane quadrant q writes rows i, i+32, i+64, i+96 of each
         // 128-row atom: the 16 bytes of atom row i are the four 32-bit columns of that atom,
@@ -716,6 +772,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
+#ifdef VX_GEMM_PROFILE
+        if (p.dbg & (64 | 16384)) ok = false;
+#endif
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             for (int kb = 0; kb < p.k_blocks; kb++) {
                 if (!mbar_wait(sf_full(stage), phase, 100)) {
@@ -744,8 +803,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 }
                 tc_fence_after();
                 const uint32_t tsf = tmem + ((uint32_t)(quad * 32) << 16) + TMEM_SF_COL + stage * TMEM_SF_SET;
-                tc_st16(tsf, ra);
-                tc_st32(tsf + 16, rb);
+#ifdef VX_GEMM_PROFILE
+                if (!(p.dbg & 128))
+#endif
+                {
+                    tc_st16(tsf, ra);
+                    tc_st32(tsf + 16, rb);
+                }
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
