@@ -30,6 +30,7 @@
 // No TMA load here uses cluster multicast; each CTA fetches its own tiles.
 //
 // Reference counterpart (SIMT f32): linear_tiled_kernel, crates/velox-cuda/kernels/portable_model.cu:349-398.
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
@@ -45,20 +46,27 @@ enum GemmKind { KIND_MXF4 = 0, KIND_F8 = 1, KIND_BF16 = 2 };
 constexpr int BM = 128;        // tokens per tile (MMA M)
 constexpr int BN = 256;        // weight rows per tile (MMA N): two 128-row halves
 constexpr int BK_BYTES = 128;  // bytes of K per row per stage: one swizzle row, four MMA k-steps
-constexpr int OP_STAGES = 3;   // operand ring (x tile + W tile)
 constexpr int SF_STAGES = 4;   // scale ring in shared memory and scale column sets in tensor memory
 constexpr int A_BYTES = BM * BK_BYTES;
 constexpr int B_HALF_BYTES = 128 * BK_BYTES;
-constexpr int B_BYTES = 2 * B_HALF_BYTES;
-constexpr int OP_STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int SFA_BYTES = 4 * 512;
 constexpr int SFB_BYTES = 2 * 4 * 512;
 constexpr int SF_STAGE_BYTES = SFA_BYTES + SFB_BYTES;
-constexpr int STAGING_BYTES = 2 * 16384;  // 128 tokens x 128 bf16 columns as two swizzled 64-column boxes
-constexpr int OFF_STAGING = OP_STAGES * OP_STAGE_BYTES;
-constexpr int OFF_SF = OFF_STAGING + STAGING_BYTES;
-constexpr int OFF_BARS = OFF_SF + SF_STAGES * SF_STAGE_BYTES;
-constexpr int SMEM_BYTES = OFF_BARS + 1024 + 512;
+constexpr int STAGING_BYTES = 2 * 16384;  // two swizzled boxes of 128 tokens x 64 bf16 columns, one per column half
+
+// Shared-memory plan for a CTA working alone (CG = 1: it loads both 128-row halves of the W tile)
+// or as one of a pair (CG = 2: it loads its own 128 tokens of x and one half of the W tile; the
+// pair's MMA reads the other half from the partner's shared memory).
+template <int CG>
+struct Plan {
+    static constexpr int B_BYTES = (CG == 2 ? 1 : 2) * B_HALF_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // 32 KB in a pair, 48 KB alone
+    static constexpr int STAGES = CG == 2 ? 5 : 3;          // operand ring
+    static constexpr int OFF_STAGING = STAGES * STAGE_BYTES;
+    static constexpr int OFF_SF = OFF_STAGING + STAGING_BYTES;
+    static constexpr int OFF_BARS = OFF_SF + SF_STAGES * SF_STAGE_BYTES;
+    static constexpr int SMEM_BYTES = OFF_BARS + 1024 + 512;
+};
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_SF_COL = 256;  // scale sets follow the accumulator
 constexpr int TMEM_SF_SET = 48;   // per set: 16 columns of x scales, 32 columns of W scales
@@ -93,7 +101,7 @@ struct GemmParams {
     long long ld, col;
     int tma_store;  // bf16-only output that a tensor map over yb + col describes
     int* status;
-    int dbg;        // profiling builds only: 1 no epilogue at all, 2 loads only, 4 no staging writes / stores, 8 no operand loads
+    int dbg;        // profiling builds only: 1 no epilogue at all, 2 loads only, 8 no operand loads, 16 no scale path, 32 no MMAs
 };
 
 __device__ int g_gemm_status = 0;
@@ -157,6 +165,38 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// ---- thread-block pairs ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// The address, in the cluster's shared window, of the same shared-memory offset in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    // default semantics, as measured: the .release.cluster form cost the arriving thread more than a
+    // thousand cycles per arrive on B200
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 __device__ __forceinline__ unsigned long long global_timer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -172,6 +212,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
     for (uint32_t spins = 1;; spins++) {
         if (backoff_ns) __nanosleep(backoff_ns);
         if (mbar_try_wait(bar, parity)) return true;
+        if ((spins & 255u) == 0 && global_timer_ns() - t0 > 2000000000ull) return false;
+    }
+}
+
+// The same for a barrier that the partner CTA of a pair arrives on.
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, uint32_t backoff_ns = 0) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const unsigned long long t0 = global_timer_ns();
+    for (uint32_t spins = 1;; spins++) {
+        if (backoff_ns) __nanosleep(backoff_ns);
+        if (mbar_try_wait_cluster(bar, parity)) return true;
         if ((spins & 255u) == 0 && global_timer_ns() - t0 > 2000000000ull) return false;
     }
 }
@@ -210,6 +261,14 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                  : "memory");
 }
 
+// Completion of this thread's MMAs, signalled on the barrier at the same offset in both CTAs of a pair.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"((uint16_t)3)
+        : "memory");
+}
+
 // Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes, groups of eight
 // rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
@@ -217,28 +276,35 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 
-template <int KIND>
+template <int KIND, int CG>
 __device__ __forceinline__ void tc_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc,
                                        uint32_t accumulate, uint32_t sfa, uint32_t sfb) {
-    if (KIND == KIND_MXF4) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-            ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
-            : "memory");
-    } else if (KIND == KIND_F8) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-            : "memory");
-    } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-            ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
-            : "memory");
+#define VX_MMA_ASM(GROUP)                                                                                      \
+    if (KIND == KIND_MXF4) {                                                                                   \
+        asm volatile(                                                                                          \
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                                  \
+            "tcgen05.mma.cta_group::" GROUP ".kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}" \
+            ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)                          \
+            : "memory");                                                                                       \
+    } else if (KIND == KIND_F8) {                                                                              \
+        asm volatile(                                                                                          \
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                                  \
+            "tcgen05.mma.cta_group::" GROUP ".kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"                           \
+            ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)                                              \
+            : "memory");                                                                                       \
+    } else {                                                                                                   \
+        asm volatile(                                                                                          \
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                                  \
+            "tcgen05.mma.cta_group::" GROUP ".kind::f16 [%0], %1, %2, %3, p;\n\t}"                              \
+            ::"r"(d), "l"(a), "l"(b), "r"(idesc), "r"(accumulate)                                              \
+            : "memory");                                                                                       \
     }
+    if (CG == 2) {
+        VX_MMA_ASM("2")
+    } else {
+        VX_MMA_ASM("1")
+    }
+#undef VX_MMA_ASM
 }
 
 // 32 lanes x 32 consecutive f32 columns of the accumulator.
@@ -300,10 +366,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Instruction descriptor: M = 128, N = 256, K-major operands, f32 accumulate.
-template <int KIND>
+// Instruction descriptor: M = 128 (256 across a pair), N = 256, K-major operands, f32 accumulate.
+template <int KIND, int CG>
 __device__ __forceinline__ constexpr uint32_t instr_desc() {
-    const uint32_t n = (uint32_t)(BN >> 3) << 17, m = (uint32_t)(BM >> 4) << 24;
+    const uint32_t n = (uint32_t)(BN >> 3) << 17, m = (uint32_t)((BM * CG) >> 4) << 24;
     if (KIND == KIND_MXF4) return (1u << 7) | (1u << 10) | n | m;         // E2M1 x E2M1, UE4M3 scales
     if (KIND == KIND_F8) return (1u << 4) | n | m;                        // E4M3 x E4M3 -> f32
     return (1u << 4) | (1u << 7) | (1u << 10) | n | m;                    // BF16 x BF16 -> f32
@@ -311,42 +377,61 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
 
 // ---- kernel ------------------------------------------------------------------------------------------
 
-template <int KIND, bool SWIGLU>
+template <int KIND, bool SWIGLU, int CG>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
             const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out,
             const GemmParams p) {
+    using PL = Plan<CG>;
+    constexpr int OP_STAGES = PL::STAGES;
+    constexpr int OP_STAGE_BYTES = PL::STAGE_BYTES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t staging = base + OFF_STAGING;
-    const uint32_t sf_ring = base + OFF_SF;
-    const uint32_t bars = base + OFF_BARS;
+    const uint32_t staging = base + PL::OFF_STAGING;
+    const uint32_t sf_ring = base + PL::OFF_SF;
+    const uint32_t bars = base + PL::OFF_BARS;
     auto op_full = [&](int s) { return bars + 8u * s; };
     auto op_empty = [&](int s) { return bars + 8u * (OP_STAGES + s); };
-    auto sf_full = [&](int s) { return bars + 8u * (2 * OP_STAGES + s); };
-    auto sf_empty = [&](int s) { return bars + 8u * (2 * OP_STAGES + SF_STAGES + s); };
-    auto tsf_full = [&](int s) { return bars + 8u * (2 * OP_STAGES + 2 * SF_STAGES + s); };
-    auto tsf_empty = [&](int s) { return bars + 8u * (2 * OP_STAGES + 3 * SF_STAGES + s); };
-    const uint32_t acc_full = bars + 8u * (2 * OP_STAGES + 4 * SF_STAGES);
+    auto peer_full = [&](int s) { return bars + 8u * (2 * OP_STAGES + s); };   // pairs: partner's stage landed
+    auto sf_full = [&](int s) { return bars + 8u * (3 * OP_STAGES + s); };
+    auto sf_empty = [&](int s) { return bars + 8u * (3 * OP_STAGES + SF_STAGES + s); };
+    auto tsf_full = [&](int s) { return bars + 8u * (3 * OP_STAGES + 2 * SF_STAGES + s); };
+    auto tsf_empty = [&](int s) { return bars + 8u * (3 * OP_STAGES + 3 * SF_STAGES + s); };
+    const uint32_t acc_full = bars + 8u * (3 * OP_STAGES + 4 * SF_STAGES);
     const uint32_t acc_empty = acc_full + 8u;
     const uint32_t tmem_slot = acc_full + 16u;
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    // In a pair, CTA 0 issues the MMAs for both and owns the barriers the other CTA reports to.
+    const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;
+    auto arrive_lead = [&](uint32_t bar) {
+        if (CG == 2)
+            mbar_arrive_cluster(map_to_cta(bar, 0));
+        else
+            mbar_arrive(bar);
+    };
+    auto commit = [&](uint32_t bar) {
+        if (CG == 2)
+            tc_commit_pair(bar);
+        else
+            tc_commit(bar);
+    };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < OP_STAGES; s++) {
             mbar_init(op_full(s), 1);
             mbar_init(op_empty(s), 1);
+            mbar_init(peer_full(s), 1);
         }
         for (int s = 0; s < SF_STAGES; s++) {
             mbar_init(sf_full(s), 1);
             mbar_init(sf_empty(s), 4);
-            mbar_init(tsf_full(s), 4);
+            mbar_init(tsf_full(s), 4 * CG);
             mbar_init(tsf_empty(s), 1);
         }
         mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 8);
+        mbar_init(acc_empty, 8 * CG);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b0) : "memory");
@@ -354,20 +439,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_out) : "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
-                     "r"((uint32_t)TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        // tensor memory: in a pair both CTAs' warp 1 take part and both get the same address
+        if (CG == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+                         "r"((uint32_t)TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+                         "r"((uint32_t)TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (CG == 2) cluster_sync_all();   // the partner's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem = *tmem_slot_ptr;
 
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    // Work units: tiles of 128 x CG tokens by 256 weight rows, walked by CTA (pair) number.
+    const int unit = CG == 2 ? (int)blockIdx.x / 2 : (int)blockIdx.x;
+    const int units = (int)gridDim.x / CG;
+    const int tiles_mu = (p.tiles_m + CG - 1) / CG;
+    const int num_tiles = tiles_mu * p.tiles_n;
 
     if (warp == 0) {
-        // ---------------- operand producer: x tile and the two W half tiles per k-block ----------------
+        // ---------------- operand producer: this CTA's x tile and W rows per k-block ----------------
         // (whole warp in the loop, one elected lane issuing, as in the MMA warp below)
         {
             int stage = 0;
@@ -376,11 +474,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const bool leader = elect_one();
             PROF_DECL;
             PROF_T0(t_all);
-#ifdef VX_GEMM_PROFILE
-            if (p.dbg & 64) ok = false;   // MMA-rate probe: nobody but the issuer and the epilogue runs
-#endif
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
+            for (int tile = unit; tile < num_tiles && ok; tile += units) {
+                const int mt = (tile % tiles_mu) * CG + (int)rank, nt = tile / tiles_mu;
                 const int r0 = (int)(p.b_row0[0] + (long long)nt * p.b_tile_rows);
                 const int r1 = (int)(p.b_row0[1] + (long long)nt * p.b_tile_rows);
                 for (int kb = 0; kb < p.k_blocks; kb++) {
@@ -401,11 +496,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         } else
 #endif
                         {
-                            mbar_arrive_expect_tx(op_full(stage), A_BYTES + B_BYTES);
+                            mbar_arrive_expect_tx(op_full(stage), A_BYTES + PL::B_BYTES);
                             tma_load_2d(sa, &tmap_a, op_full(stage), (kb % p.a_k_blocks) * p.k_elems_per_block,
                                         mt * BM);
-                            tma_load_2d(sb, &tmap_b0, op_full(stage), kx, r0);
-                            tma_load_2d(sb + B_HALF_BYTES, &tmap_b1, op_full(stage), kx, r1);
+                            if (CG == 2) {
+                                // one half of the W tile; the MMA reads the other from the partner
+                                if (rank)
+                                    tma_load_2d(sb, &tmap_b1, op_full(stage), kx, r1);
+                                else
+                                    tma_load_2d(sb, &tmap_b0, op_full(stage), kx, r0);
+                            } else {
+                                tma_load_2d(sb, &tmap_b0, op_full(stage), kx, r0);
+                                tma_load_2d(sb + B_HALF_BYTES, &tmap_b1, op_full(stage), kx, r1);
+                            }
                         }
                     }
                     if (++stage == OP_STAGES) {
@@ -414,11 +517,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
                 }
             }
-            if (!ok && !(p.dbg & 64)) __nanosleep(200000);  // let copies already in flight land before the CTA exits
+            if (!ok) __nanosleep(200000);  // let copies already in flight land before the CTA exits
             PROF_ADD(1, t_all);
             if (leader) {
                 PROF_OUT(0);
                 PROF_OUT(1);
+            }
+        }
+    } else if (warp == 1 && rank != 0) {
+        // ---------------- pair, second CTA: tell the MMA issuer when this CTA's operands have landed ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const bool leader = elect_one();
+        for (int tile = unit; tile < num_tiles && ok; tile += units) {
+            for (int kb = 0; kb < p.k_blocks; kb++) {
+                if (!mbar_wait(op_full(stage), phase)) {
+                    if (leader) atomicExch(p.status, ST_TIMEOUT_FULL);
+                    ok = false;
+                    break;
+                }
+                if (leader) mbar_arrive_cluster(map_to_cta(peer_full(stage), 0));
+                if (++stage == OP_STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
             }
         }
     } else if (warp == 1) {
@@ -430,45 +553,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             int stage = 0, sstage = 0;
             uint32_t phase = 0, sphase = 0, acc_phase = 0;
             bool ok = true;
-            const uint32_t idesc = instr_desc<KIND>();
+            const uint32_t idesc = instr_desc<KIND, CG>();
             const bool leader = elect_one();
             PROF_DECL;
             PROF_T0(t_all);
 #ifdef VX_GEMM_PROFILE
             const unsigned long long ns0 = global_timer_ns();
 #endif
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = unit; tile < num_tiles && ok; tile += units) {
                 PROF_T0(t_acc);
-                if (!mbar_wait(acc_empty, acc_phase ^ 1u)) {
+                if (!(CG == 2 ? mbar_wait_cluster(acc_empty, acc_phase ^ 1u) : mbar_wait(acc_empty, acc_phase ^ 1u))) {
                     if (leader) atomicExch(p.status, ST_TIMEOUT_ACC_EMPTY);
                     break;
                 }
                 PROF_ADD(3, t_acc);
                 for (int kb = 0; kb < p.k_blocks; kb++) {
-#ifdef VX_GEMM_PROFILE
-                    if (p.dbg & 64) {   // MMA-rate probe: back-to-back MMAs on whatever shared memory holds
-                        const uint32_t pb = (p.dbg & 4096) ? base + (kb % OP_STAGES) * OP_STAGE_BYTES : base;
-                        const uint64_t da = smem_desc_sw128(pb), db = smem_desc_sw128(pb + A_BYTES);
-                        if (leader) {
-                            for (int j = 0; j < 4; j++)
-                                tc_mma<KIND>(tmem, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u,
-                                             tmem + TMEM_SF_COL + 4 * j, tmem + TMEM_SF_COL + 16 + 8 * j);
-                            if (p.dbg & 1024) tc_commit(op_empty(kb % OP_STAGES));
-                        }
-                        if (p.dbg & 2048) { mbar_try_wait(op_full(0), 1); tc_fence_after(); }
-                        continue;
-                    }
-#endif
                     PROF_T0(t_w);
-                    if (!mbar_wait(op_full(stage), phase)) {
+                    if (!mbar_wait(op_full(stage), phase) ||
+                        (CG == 2 && !mbar_wait_cluster(peer_full(stage), phase))) {
                         if (leader) atomicExch(p.status, ST_TIMEOUT_FULL);
                         ok = false;
                         break;
                     }
                     PROF_ADD(2, t_w);
-                    if (KIND == KIND_MXF4 && !(p.dbg & 16384)) {
+                    if (KIND == KIND_MXF4 && !(p.dbg & 16)) {
                         PROF_T0(t_s);
-                        if (!mbar_wait(tsf_full(sstage), sphase)) {
+                        if (!(CG == 2 ? mbar_wait_cluster(tsf_full(sstage), sphase) : mbar_wait(tsf_full(sstage), sphase))) {
                             if (leader) atomicExch(p.status, ST_TIMEOUT_SF);
                             ok = false;
                             break;
@@ -482,20 +592,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
                     const uint32_t tsf = tmem + TMEM_SF_COL + sstage * TMEM_SF_SET;
                     PROF_T0(t_i);
+#ifdef VX_GEMM_PROFILE
+                    if (p.dbg & 32) {   // timing only: no MMAs, stages handed straight back (loads alone)
+                        if (leader) {
+                            mbar_arrive(op_empty(stage));
+                            if (CG == 2) mbar_arrive_cluster(map_to_cta(op_empty(stage), 1));
+                        }
+                    } else
+#endif
                     if (leader) {
                         // advancing 32 bytes along K inside the swizzle row: +2 in the address field
                         if (steps == 4) {
-                            tc_mma<KIND>(tmem, da, db, idesc, kb != 0 ? 1u : 0u, tsf, tsf + 16);
-                            tc_mma<KIND>(tmem, da + 2u, db + 2u, idesc, 1u, tsf + 4, tsf + 24);
-                            tc_mma<KIND>(tmem, da + 4u, db + 4u, idesc, 1u, tsf + 8, tsf + 32);
-                            tc_mma<KIND>(tmem, da + 6u, db + 6u, idesc, 1u, tsf + 12, tsf + 40);
+                            tc_mma<KIND, CG>(tmem, da, db, idesc, kb != 0 ? 1u : 0u, tsf, tsf + 16);
+                            tc_mma<KIND, CG>(tmem, da + 2u, db + 2u, idesc, 1u, tsf + 4, tsf + 24);
+                            tc_mma<KIND, CG>(tmem, da + 4u, db + 4u, idesc, 1u, tsf + 8, tsf + 32);
+                            tc_mma<KIND, CG>(tmem, da + 6u, db + 6u, idesc, 1u, tsf + 12, tsf + 40);
                         } else {
                             for (int j = 0; j < steps; j++)
-                                tc_mma<KIND>(tmem, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u,
-                                             tsf + 4 * j, tsf + 16 + 8 * j);
+                                tc_mma<KIND, CG>(tmem, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u,
+                                                 tsf + 4 * j, tsf + 16 + 8 * j);
                         }
-                        tc_commit(op_empty(stage));
-                        if (KIND == KIND_MXF4 && !(p.dbg & 16384)) tc_commit(tsf_empty(sstage));
+                        commit(op_empty(stage));
+                        if (KIND == KIND_MXF4 && !(p.dbg & 16)) commit(tsf_empty(sstage));
                     }
                     PROF_ADD(11, t_i);
                     if (++stage == OP_STAGES) {
@@ -509,7 +627,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         }
                     }
                 }
-                if (ok && leader) tc_commit(acc_full);
+                if (ok && leader) commit(acc_full);
                 acc_phase ^= 1u;
             }
             PROF_ADD(4, t_all);
@@ -544,8 +662,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         constexpr int MINE = CHUNKS / 2;         // ... of which this warp takes half
         PROF_DECL;
         PROF_T0(t_all);
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-            const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
+        for (int tile = unit; tile < num_tiles; tile += units) {
+            const int mt = (tile % tiles_mu) * CG + (int)rank, nt = tile / tiles_mu;
             PROF_T0(t_w);
             if (!mbar_wait(acc_full, acc_phase, 60)) {
                 if (lane == 0) atomicExch(p.status, ST_TIMEOUT_ACC_FULL);
@@ -563,6 +681,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             // Whole-tile bf16 output through shared memory and a tensor-map store: taken when the
             // tile does not start left of the output's first column.
             const bool staged = p.tma_store && rbase[0] >= p.out_row0;
+            const bool any_token = (long long)mt * BM < p.m;   // false only for a pair's second CTA past the end
             // chunk ch of the accumulator (and its partner in the up half) -> 32 finished values
             auto compute = [&](const int ch, const uint32_t (&r)[32], const uint32_t (&r2)[32], float (&v)[32]) {
                 const int half = SWIGLU ? 0 : ch / 4;
@@ -637,7 +756,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 // this warp's part of the accumulator is in registers: hand it back to the MMA issuer
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(acc_empty);
+                if (lane == 0) arrive_lead(acc_empty);
             };
 #ifdef VX_GEMM_PROFILE
             if (p.dbg & 1) {
@@ -684,7 +803,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-                    if (store_thread) {
+                    if (store_thread && any_token) {
                         tma_store_2d(&tmap_out, my_box,
                                      (int)(rbase[0] - p.out_row0) + (hsel * (MINE / 2) + bx) * 64, mt * BM);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -715,19 +834,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
     } else if (KIND == KIND_MXF4 && warp == 2) {
         // ---------------- scale producer: whole 512-byte atoms, x then the two W halves ----------------
+        // (in a pair each CTA needs the scales of its own tokens and of all 256 weight rows)
         {
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             const bool leader = elect_one();
-#ifdef VX_GEMM_PROFILE
-            if (p.dbg & (64 | 16384)) ok = false;
-#endif
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                const int mt = tile % p.tiles_m, nt = tile / p.tiles_m;
+            if (p.dbg & 16) ok = false;   // profiling builds, timing only: no scales at all
+            for (int tile = unit; tile < num_tiles && ok; tile += units) {
+                const int mt = (tile % tiles_mu) * CG + (int)rank, nt = tile / tiles_mu;
                 const long long r0 = p.b_row0[0] + (long long)nt * p.b_tile_rows;
                 const long long r1 = p.b_row0[1] + (long long)nt * p.b_tile_rows;
                 const bool sf0 = r0 < p.b_rows_total[0], sf1 = r1 < p.b_rows_total[1];
+                const bool sfx = mt < p.tiles_m;   // false only for a pair's second CTA past the last token tile
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!mbar_wait(sf_empty(stage), phase ^ 1u, 50)) {
                         if (leader) atomicExch(p.status, ST_TIMEOUT_SF);
@@ -738,15 +857,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t ssfa = sf_ring + stage * SF_STAGE_BYTES, ssfb = ssfa + SFA_BYTES;
                     const long long atom = 4LL * kb;
                     if (leader) {
-#ifdef VX_GEMM_PROFILE
-                        if (p.dbg & 256) {   // timing only: no scale copies
+                        const uint32_t parts = (sfx ? 1u : 0u) + (sf0 ? 1u : 0u) + (sf1 ? 1u : 0u);
+                        if (parts == 0) {
                             mbar_arrive(sf_full(stage));
-                        } else
-#endif
-                        {
-                            mbar_arrive_expect_tx(sf_full(stage), bytes * (1u + (sf0 ? 1u : 0u) + (sf1 ? 1u : 0u)));
-                            bulk_load_1d(ssfa, p.sfa + ((long long)mt * p.k_tiles64 + atom) * 512, bytes,
-                                         sf_full(stage));
+                        } else {
+                            mbar_arrive_expect_tx(sf_full(stage), bytes * parts);
+                            if (sfx)
+                                bulk_load_1d(ssfa, p.sfa + ((long long)mt * p.k_tiles64 + atom) * 512, bytes,
+                                             sf_full(stage));
                             if (sf0)
                                 bulk_load_1d(ssfb, p.sfb[0] + ((r0 / 128) * p.k_tiles64 + atom) * 512, bytes,
                                              sf_full(stage));
@@ -761,7 +879,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
                 }
             }
-            if (!ok && !(p.dbg & (64 | 16384))) __nanosleep(200000);
+            if (!ok && !(p.dbg & 16)) __nanosleep(200000);
         }
     } else if (KIND == KIND_MXF4 && warp >= MOVER_WARP0) {
         // ---------------- scale movers: shared memory -> tensor memory through registers ----------------
@@ -771,13 +889,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int quad = warp % 4;
         int stage = 0;
         uint32_t phase = 0;
-        bool ok = true;
-#ifdef VX_GEMM_PROFILE
-        if (p.dbg & (64 | 16384)) ok = false;
-#endif
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        bool ok = !(p.dbg & 16);
+        for (int tile = unit; tile < num_tiles && ok; tile += units) {
             for (int kb = 0; kb < p.k_blocks; kb++) {
-                if (!mbar_wait(sf_full(stage), phase, 100)) {
+                if (!mbar_wait(sf_full(stage), phase, 50)) {
                     if (lane == 0) atomicExch(p.status, ST_TIMEOUT_SF);
                     ok = false;
                     break;
@@ -796,24 +911,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sf_empty(stage));
                 // the MMAs that read this column set (SF_STAGES k-blocks ago) must have completed
-                if (!mbar_wait(tsf_empty(stage), phase ^ 1u, 100)) {
+                if (!mbar_wait(tsf_empty(stage), phase ^ 1u, 50)) {
                     if (lane == 0) atomicExch(p.status, ST_TIMEOUT_SF);
                     ok = false;
                     break;
                 }
                 tc_fence_after();
                 const uint32_t tsf = tmem + ((uint32_t)(quad * 32) << 16) + TMEM_SF_COL + stage * TMEM_SF_SET;
-#ifdef VX_GEMM_PROFILE
-                if (!(p.dbg & 128))
-#endif
-                {
-                    tc_st16(tsf, ra);
-                    tc_st32(tsf + 16, rb);
-                }
+                tc_st16(tsf, ra);
+                tc_st32(tsf + 16, rb);
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tsf_full(stage));
+                if (lane == 0) arrive_lead(tsf_full(stage));
                 if (++stage == SF_STAGES) {
                     stage = 0;
                     phase ^= 1u;
@@ -822,11 +932,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
     }
 
+    // Nobody leaves while the partner may still signal this CTA's barriers or read its shared memory.
     tc_fence_before();
     __syncthreads();
+    if (CG == 2) cluster_sync_all();
     if (warp == 1) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS)
-                     : "memory");
+        if (CG == 2)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS)
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS)
+                         : "memory");
     }
 }
 
@@ -895,6 +1011,49 @@ static void make_out_map(CUtensorMap* map, GemmParams& p, long long out_cols, lo
         p.tma_store = 1;
 }
 
+template <int KIND, bool SWIGLU, int CG>
+static int launch_cfg(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, const CUtensorMap& mo,
+                      const GemmParams& p, int sms) {
+    auto kern = gemm_kernel<KIND, SWIGLU, CG>;
+    constexpr int smem = Plan<CG>::SMEM_BYTES;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    const int tiles = ((p.tiles_m + CG - 1) / CG) * p.tiles_n;
+    cudaLaunchConfig_t cfg{};
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream();
+    cudaLaunchAttribute attr[1];
+    int units = sms / CG;
+    if (CG == 2) {
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        // pairs that can be resident at once (GPCs with an odd SM count leave one SM out)
+        static int max_pairs[2] = {0, 0};
+        int& mp = max_pairs[SWIGLU ? 1 : 0];
+        if (mp == 0) {
+            cfg.gridDim = dim3(2 * (sms / 2));
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) n = sms / 2;
+            cudaGetLastError();
+            mp = n;
+        }
+        units = mp < sms / 2 ? mp : sms / 2;
+    }
+    if (tiles < units) units = tiles;
+    cfg.gridDim = dim3(units * CG);
+#ifdef VX_GEMM_PROFILE
+    if (getenv("VX_GEMM_VERBOSE")) fprintf(stderr, "gemm launch: CG=%d units=%d tiles=%d smem=%d\n", CG, units, tiles, smem);
+#endif
+    e = cudaLaunchKernelEx(&cfg, kern, a, b0, b1, mo, p);
+    if (e != cudaSuccess) return (int)e;
+    return launch_status();
+}
+
 template <int KIND>
 static int launch(bool swiglu, const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1,
                   GemmParams& p, long long out_cols, long long first_row) {
@@ -907,22 +1066,11 @@ static int launch(bool swiglu, const CUtensorMap& a, const CUtensorMap& b0, cons
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
-    const int tiles = p.tiles_m * p.tiles_n;
-    const int grid = tiles < sms ? tiles : sms;
-    cudaError_t e;
     TimedRegion timed(KIND == KIND_MXF4 ? TIMED_GEMM_FP4 : KIND == KIND_F8 ? TIMED_GEMM_FP8 : TIMED_GEMM_BF16);
-    if (swiglu) {
-        auto kern = gemm_kernel<KIND, true>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream()>>>(a, b0, b1, mo, p);
-    } else {
-        auto kern = gemm_kernel<KIND, false>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        kern<<<grid, GEMM_THREADS, SMEM_BYTES, stream()>>>(a, b0, b1, mo, p);
-    }
-    return launch_status();
+    // More than one token tile: CTA pairs (256 tokens per unit, half the W traffic per CTA).
+    const bool pair = p.tiles_m > 1 && !getenv("VELOX_SM100_NO_PAIRS");
+    if (swiglu) return pair ? launch_cfg<KIND, true, 2>(a, b0, b1, mo, p, sms) : launch_cfg<KIND, true, 1>(a, b0, b1, mo, p, sms);
+    return pair ? launch_cfg<KIND, false, 2>(a, b0, b1, mo, p, sms) : launch_cfg<KIND, false, 1>(a, b0, b1, mo, p, sms);
 }
 
 static int* status_ptr() {
@@ -1206,9 +1354,9 @@ extern "C" int velox_sm100_linear_nvfp4_a4_static(const uint16_t* xb, const velo
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
     const int tiles = p.tiles_m * p.tiles_n;
-    auto kern = gemm_kernel<KIND_MXF4, false>;
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    auto kern = gemm_kernel<KIND_MXF4, false, 1>;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan<1>::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    kern<<<tiles < sms ? tiles : sms, GEMM_THREADS, SMEM_BYTES, stream()>>>(ma, mb, mb, mo, p);
+    kern<<<tiles < sms ? tiles : sms, GEMM_THREADS, Plan<1>::SMEM_BYTES, stream()>>>(ma, mb, mb, mo, p);
     return launch_status();
 }
