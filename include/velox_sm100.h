@@ -215,6 +215,20 @@ int velox_sm100_linear_swiglu_q4(const uint8_t* codes, const uint8_t* atoms, flo
                                  const velox_sm100_view* gate, const velox_sm100_view* up, int m, float* out,
                                  uint16_t* outb);
 
+/* The FP4 linears as producers of the next linear's FP4 input: the result, rounded to bf16, is
+ * quantised in the GEMM epilogue with `out_divisor` into out_codes [m, rows/2] and out_atoms (scale
+ * atoms over ceil(m/128)*128 rows, zero past m) - bit for bit what
+ * velox_sm100_quantize_act_nvfp4 makes of the bf16 output - and also stored as bf16 when yb / outb
+ * is not NULL. Same conditions as the _q4 entry points, and the view must start on a 128-row scale
+ * tile and hold a multiple of 64 rows; VELOX_ERR_UNSUPPORTED otherwise. */
+int velox_sm100_linear_q4_to_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                                const velox_sm100_view* view, int m, uint16_t* yb, uint8_t* out_codes,
+                                uint8_t* out_atoms, float out_divisor);
+int velox_sm100_linear_swiglu_q4_to_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                                       const velox_sm100_view* gate, const velox_sm100_view* up, int m,
+                                       uint16_t* outb, uint8_t* out_codes, uint8_t* out_atoms,
+                                       float out_divisor);
+
 /* The same with a bf16 addend (the all-reduced partial sums of a row-split projection): acc += xb,
  * then the norm. No counterpart in the reference, which has no tensor parallelism. */
 int velox_sm100_add_bf16_rms_norm_twin(float* acc, const uint16_t* xb, const float* weight, float* y,

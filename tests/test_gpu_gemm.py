@@ -270,3 +270,48 @@ def test_linear_q4_refuses_what_the_fp4_gemm_does_not_serve(b):
         b.linear_q4(q4, 256.0, make_view(b, payload, NV, n, k, 0, n, A16), y, 128)
     with pytest.raises(Unsupported):                     # decode sizes take the bf16 GEMV
         b.linear_q4(q4, 256.0, make_view(b, payload, NV, n, k, 0, n, ActPolicy.allow_a4(256.0)), y, 4)
+
+
+@pytest.mark.parametrize("n,k,m", [(256, 640, 37), (512, 1024, 300), (1024, 512, 513)])
+def test_linears_emit_the_next_linears_nvfp4_input(b, n, k, m):
+    """linear_q4_to_q4 / linear_swiglu_q4_to_q4: the bf16 result is unchanged, and the codes and
+    scale atoms written by the GEMM epilogue are bit for bit the stand-alone quantiser's output on
+    that bf16 result (which the oracle's quantiser pins in test_gpu_parity). m covers a lone CTA,
+    a CTA pair whose second half runs past the last token tile, and several pair tiles."""
+    r = O.Rng(47)
+    payload = r.random_weight(FMT_O[NV], n, k)
+    view = make_view(b, payload, NV, n, k, 0, n, ActPolicy.allow_a4(256.0))
+    acc = b.upload(r.vec(m * k, 1.0))
+    q4 = b.q4_blob(m, k)
+    b.add_rms_norm_q4(acc, None, b.upload(np.ones(k, np.float32)), None, q4, m, k, 1e-6, 256.0)
+    dev = acc.device
+    for out_div in (128.0, 16.0):
+        yb_ref = torch.zeros(m * n, dtype=torch.bfloat16, device=dev)
+        b.linear_q4(q4, 256.0, view, None, m, yb=yb_ref)
+        want_codes, want_atoms = b.quantize_act_nvfp4(yb_ref.float().reshape(m, n), out_div)
+        for with_bf16 in (True, False):
+            yb = torch.zeros(m * n, dtype=torch.bfloat16, device=dev) if with_bf16 else None
+            oq = b.q4_blob(m, n)
+            oq[0].fill_(0x5A)
+            oq[1].fill_(0x5A)
+            b.linear_q4_to_q4(q4, 256.0, view, m, oq, out_div, yb=yb)
+            assert b.lib.velox_sm100_debug_status() == 0
+            if with_bf16:
+                assert torch.equal(yb, yb_ref)
+            assert torch.equal(oq[0].reshape(m, n // 2), want_codes.reshape(m, n // 2))
+            assert torch.equal(oq[1], want_atoms.reshape(-1))
+    # SwiGLU producer
+    half = n // 2
+    g = make_view(b, payload, NV, n, k, 0, half, ActPolicy.allow_a4(256.0))
+    u = make_view(b, payload, NV, n, k, half, half, ActPolicy.allow_a4(256.0))
+    ob_ref = torch.zeros(m * half, dtype=torch.bfloat16, device=dev)
+    b.linear_swiglu_q4(q4, 256.0, g, u, None, ob_ref, m)
+    want_codes, want_atoms = b.quantize_act_nvfp4(ob_ref.float().reshape(m, half), 16.0)
+    oq = b.q4_blob(m, half)
+    oq[1].fill_(0x5A)
+    ob = torch.zeros_like(ob_ref)
+    b.linear_swiglu_q4_to_q4(q4, 256.0, g, u, m, oq, 16.0, outb=ob)
+    assert b.lib.velox_sm100_debug_status() == 0
+    assert torch.equal(ob, ob_ref)
+    assert torch.equal(oq[0].reshape(m, half // 2), want_codes.reshape(m, half // 2))
+    assert torch.equal(oq[1], want_atoms.reshape(-1))

@@ -53,6 +53,8 @@ SIGNATURES = {
     "velox_sm100_add_rms_norm_q4": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _F, _I, _F]),
     "velox_sm100_linear_q4": (_I, [_VP, _VP, _F, _PV, _I, _VP, _VP]),
     "velox_sm100_linear_swiglu_q4": (_I, [_VP, _VP, _F, _PV, _PV, _I, _VP, _VP]),
+    "velox_sm100_linear_q4_to_q4": (_I, [_VP, _VP, _F, _PV, _I, _VP, _VP, _VP, _F]),
+    "velox_sm100_linear_swiglu_q4_to_q4": (_I, [_VP, _VP, _F, _PV, _PV, _I, _VP, _VP, _VP, _F]),
     "velox_sm100_linear_act": (_I, [_PV, _I, C.POINTER(C.c_float)]),
     "velox_sm100_linear": (_I, [_VP, _VP, _I, _LL, _LL, _LL, _I, _I, _VP]),
     "velox_sm100_linear_view": (_I, [_VP, _PV, _I, _VP, _VP]),

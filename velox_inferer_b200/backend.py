@@ -267,6 +267,21 @@ class Sm100Backend:
                                                      C.byref(_view_struct(gate)), C.byref(_view_struct(up)), m,
                                                      _ptr(out), _ptr(outb)), "sm100 linear_swiglu_q4")
 
+    def linear_q4_to_q4(self, q4, divisor: float, w: WeightView, m: int, out_q4, out_divisor: float,
+                        yb: Optional[torch.Tensor] = None) -> None:
+        """linear_q4 whose result is (also) the next linear's NVFP4 input."""
+        self._bind()
+        status(self.lib.velox_sm100_linear_q4_to_q4(q4[0].data_ptr(), q4[1].data_ptr(), divisor,
+                                                    C.byref(_view_struct(w)), m, _ptr(yb), out_q4[0].data_ptr(),
+                                                    out_q4[1].data_ptr(), out_divisor), "sm100 linear_q4_to_q4")
+
+    def linear_swiglu_q4_to_q4(self, q4, divisor: float, gate: WeightView, up: WeightView, m: int, out_q4,
+                               out_divisor: float, outb: Optional[torch.Tensor] = None) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_linear_swiglu_q4_to_q4(
+            q4[0].data_ptr(), q4[1].data_ptr(), divisor, C.byref(_view_struct(gate)), C.byref(_view_struct(up)), m,
+            _ptr(outb), out_q4[0].data_ptr(), out_q4[1].data_ptr(), out_divisor), "sm100 linear_swiglu_q4_to_q4")
+
     def add_bf16(self, acc, xb, n) -> None:
         self._bind()
         status(self.lib.velox_sm100_add_bf16(acc.data_ptr(), xb.data_ptr(), n), "sm100 add_bf16")

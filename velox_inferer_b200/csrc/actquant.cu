@@ -3,9 +3,6 @@
 // performs on the host (crates/velox-core/src/quant.rs:63-96), so codes and scales agree bit for
 // bit; the final conversions are the hardware cvt.rn.satfinite the reference's converters restate
 // (quant.rs:9-59).
-#include <cuda_fp4.h>
-#include <cuda_fp8.h>
-
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -13,15 +10,6 @@ namespace vx {
 
 __device__ __forceinline__ float load_act(const float* x, const uint16_t* xb, long long i) {
     return xb ? bf16_bits_to_f32(xb[i]) : x[i];
-}
-
-__device__ __forceinline__ uint32_t f32_to_e4m3(float v) {
-    return (uint32_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
-}
-
-// Two values -> one byte of E2M1 codes, the first in the low nibble.
-__device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float lo, float hi) {
-    return (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
 }
 
 // Fp8Row: scale = amax / 448, inv = 1 / scale, code = e4m3(x * inv). One block per row.

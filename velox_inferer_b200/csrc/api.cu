@@ -163,8 +163,9 @@ static int run(const LinearArgs& a, const Plan& p) {
 
 static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_view* view, int m,
                          float* y, uint16_t* yb, long long ld, long long col,
-                         const uint8_t* q_codes = nullptr, const uint8_t* q_atoms = nullptr) {
-    if (m <= 0 || (!x && !xb && !q_codes) || (!y && !yb)) return VELOX_ERR_SHAPE;
+                         const uint8_t* q_codes = nullptr, const uint8_t* q_atoms = nullptr,
+                         uint8_t* qo_codes = nullptr, uint8_t* qo_atoms = nullptr, float qo_divisor = 0.0f) {
+    if (m <= 0 || (!x && !xb && !q_codes) || (!y && !yb && !qo_codes)) return VELOX_ERR_SHAPE;
     int rc = check_view(view);
     if (rc != 0) return rc;
     LinearArgs a{};
@@ -179,15 +180,19 @@ static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.col = col;
     a.q_codes = q_codes;
     a.q_atoms = q_atoms;
+    a.qo_codes = qo_codes;
+    a.qo_atoms = qo_atoms;
+    a.qo_divisor = qo_divisor;
     const Plan p = plan_for(*view, m);
-    if (q_codes && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;   // only the FP4 GEMM reads them
+    if ((q_codes || qo_codes) && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;   // FP4 GEMM only
     return run(a, p);
 }
 
 static int swiglu_common(const float* x, const uint16_t* xb, const velox_sm100_view* gate,
                          const velox_sm100_view* up, int m, float* out, uint16_t* outb,
-                         const uint8_t* q_codes = nullptr, const uint8_t* q_atoms = nullptr) {
-    if (m <= 0 || (!x && !xb && !q_codes) || (!out && !outb)) return VELOX_ERR_SHAPE;
+                         const uint8_t* q_codes = nullptr, const uint8_t* q_atoms = nullptr,
+                         uint8_t* qo_codes = nullptr, uint8_t* qo_atoms = nullptr, float qo_divisor = 0.0f) {
+    if (m <= 0 || (!x && !xb && !q_codes) || (!out && !outb && !qo_codes)) return VELOX_ERR_SHAPE;
     int rc = check_view(gate);
     if (rc != 0) return rc;
     rc = check_view(up);
@@ -215,8 +220,11 @@ static int swiglu_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.w.policy = a.up.policy = both.policy;
     a.q_codes = q_codes;
     a.q_atoms = q_atoms;
+    a.qo_codes = qo_codes;
+    a.qo_atoms = qo_atoms;
+    a.qo_divisor = qo_divisor;
     const Plan p = plan_swiglu(both, *gate, *up, m);
-    if (q_codes && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
+    if ((q_codes || qo_codes) && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
     return run(a, p);
 }
 
@@ -420,6 +428,27 @@ int velox_sm100_linear_swiglu_q4(const uint8_t* codes, const uint8_t* atoms, flo
         up->divisor != divisor)
         return VELOX_ERR_UNSUPPORTED;
     return swiglu_common(nullptr, nullptr, gate, up, m, out, outb, codes, atoms);
+}
+
+int velox_sm100_linear_q4_to_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                                const velox_sm100_view* view, int m, uint16_t* yb, uint8_t* out_codes,
+                                uint8_t* out_atoms, float out_divisor) {
+    if (!view || !codes || !atoms || !out_codes || !out_atoms) return VELOX_ERR_SHAPE;
+    if (view->policy != VELOX_POLICY_ALLOW_A4 || view->divisor != divisor) return VELOX_ERR_UNSUPPORTED;
+    return linear_common(nullptr, nullptr, view, m, nullptr, yb, view->rows, 0, codes, atoms, out_codes, out_atoms,
+                         out_divisor);
+}
+
+int velox_sm100_linear_swiglu_q4_to_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                                       const velox_sm100_view* gate, const velox_sm100_view* up, int m,
+                                       uint16_t* outb, uint8_t* out_codes, uint8_t* out_atoms,
+                                       float out_divisor) {
+    if (!gate || !up || !codes || !atoms || !out_codes || !out_atoms) return VELOX_ERR_SHAPE;
+    if (gate->policy != VELOX_POLICY_ALLOW_A4 || gate->divisor != divisor || up->policy != VELOX_POLICY_ALLOW_A4 ||
+        up->divisor != divisor)
+        return VELOX_ERR_UNSUPPORTED;
+    return swiglu_common(nullptr, nullptr, gate, up, m, nullptr, outb, codes, atoms, out_codes, out_atoms,
+                         out_divisor);
 }
 
 int velox_sm100_add_bf16(float* acc, const uint16_t* xb, long long len) {

@@ -4,6 +4,8 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -35,6 +37,15 @@ __host__ __device__ __forceinline__ long long nvfp4_scale_offset(long long row, 
     const long long row_tile = row / 128, row_inner = row % 128;
     return (row_tile * k_tiles + g / 4) * 512 + (row_inner % 32) * 16 + (row_inner / 32) * 4 +
            (g % 4);
+}
+
+// f32 -> E4M3 byte and two f32 -> one byte of E2M1 codes (the first in the low nibble): the
+// hardware's round-to-nearest-even, saturating conversions.
+__device__ __forceinline__ uint32_t f32_to_e4m3(float v) {
+    return (uint32_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float lo, float hi) {
+    return (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest);
 }
 
 // ---- exact scalar decoders --------------------------------------------------------------------

@@ -3,9 +3,6 @@
 // computes these in f64 (crates/velox-cpu/src/lib.rs:188-230, 688-707), results agree to f32
 // rounding. Reference kernels: crates/velox-cuda/kernels/portable.cu:109-115, 1519-1550;
 // portable_model.cu:2011-2022.
-#include <cuda_fp4.h>
-#include <cuda_fp8.h>
-
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -138,7 +135,7 @@ add_rms_norm_q4_kernel(float* __restrict__ acc, const float* __restrict__ x, con
             o[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             o[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         }
-        const uint32_t s = (uint32_t)__nv_cvt_float_to_fp8(__fdiv_rn(__fmul_rn(divisor, amax), 6.0f), __NV_SATFINITE, __NV_E4M3);
+        const uint32_t s = f32_to_e4m3(__fdiv_rn(__fmul_rn(divisor, amax), 6.0f));
         uint32_t out[2] = {0, 0};
         if (s != 0) {
             const float ds = e4m3_to_f32(s);
@@ -146,7 +143,7 @@ add_rms_norm_q4_kernel(float* __restrict__ acc, const float* __restrict__ x, con
             for (int i = 0; i < 8; i++) {
                 const float lo = __fdiv_rn(__fmul_rn(v[2 * i], divisor), ds);
                 const float hi = __fdiv_rn(__fmul_rn(v[2 * i + 1], divisor), ds);
-                out[i >> 2] |= (uint32_t)__nv_cvt_float2_to_fp4x2(make_float2(lo, hi), __NV_E2M1, cudaRoundNearest) << (8 * (i & 3));
+                out[i >> 2] |= f32x2_to_e2m1x2(lo, hi) << (8 * (i & 3));
             }
         }
         *reinterpret_cast<uint2*>(codes + (base + g * 16) / 2) = make_uint2(out[0], out[1]);

@@ -100,6 +100,10 @@ struct GemmParams {
     uint16_t* yb;
     long long ld, col;
     int tma_store;  // bf16-only output that a tensor map over yb + col describes
+    uint8_t* q_codes;   // optional: the output also (or only) as NVFP4 activations, codes [m, q_ld / 2] ...
+    uint8_t* q_atoms;   // ... and scale atoms over ceil(m / 128) * 128 rows
+    float q_divisor;
+    long long q_ld;     // columns of the quantised matrix (a multiple of 64)
     int* status;
     int dbg;        // profiling builds only: 1 no epilogue at all, 2 loads only, 8 no operand loads, 16 no scale path, 32 no MMAs
 };
@@ -765,7 +769,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 continue;
             }
 #endif
-            if (staged) {
+            const bool emit_q = p.q_codes != nullptr && mt < p.tiles_m;
+            if (staged || p.q_codes != nullptr) {
                 // Drain first: finish this warp's values and keep them as packed bf16 (16 registers
                 // per chunk), release tensor memory so the next tile's MMAs can start, and only then
                 // spend time on shared-memory staging and the tensor-map stores.
@@ -784,6 +789,60 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     for (int c = 0; c < 16; c++) pk[i][c] = pack_bf16(v[2 * c], v[2 * c + 1]);
                 }
                 PROF_T0(t_c);
+                if (emit_q) {
+                    // The output as the next linear's NVFP4 activations, quantised from the bf16
+                    // values exactly as the stand-alone quantiser does (quotients by the Markstein
+                    // sequence q0 = a*r, q = fma(fma(-q0, d, a), r, q0), which is the correctly
+                    // rounded a / d when r is the correctly rounded 1 / d).
+#pragma unroll
+                    for (int j = 0; j < MINE / 2; j++) {
+                        const long long col0 = (rbase[0] - p.out_row0) + (long long)(hsel * MINE + 2 * j) * 32;
+                        uint32_t sc = 0;
+                        uint32_t cw[8];
+#pragma unroll
+                        for (int g = 0; g < 4; g++) {
+                            float v[16];
+                            float amax = 0.0f;
+#pragma unroll
+                            for (int i = 0; i < 8; i++) {
+                                const uint32_t u = pk[2 * j + g / 2][(g % 2) * 8 + i];
+                                v[2 * i] = __uint_as_float(u << 16);
+                                v[2 * i + 1] = __uint_as_float(u & 0xffff0000u);
+                                amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
+                            }
+                            const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(p.q_divisor, amax), 6.0f));
+                            uint32_t o0 = 0, o1 = 0;
+                            if (sb != 0) {
+                                const float ds = e4m3_to_f32(sb);
+                                const float rc = __frcp_rn(ds);
+#pragma unroll
+                                for (int i = 0; i < 8; i++) {
+                                    const float a0 = __fmul_rn(v[2 * i], p.q_divisor);
+                                    const float a1 = __fmul_rn(v[2 * i + 1], p.q_divisor);
+                                    float q0 = __fmul_rn(a0, rc), q1 = __fmul_rn(a1, rc);
+                                    q0 = __fmaf_rn(__fmaf_rn(-q0, ds, a0), rc, q0);
+                                    q1 = __fmaf_rn(__fmaf_rn(-q1, ds, a1), rc, q1);
+                                    const uint32_t b = f32x2_to_e2m1x2(q0, q1) << (8 * (i & 3));
+                                    if (i < 4) o0 |= b; else o1 |= b;
+                                }
+                            }
+                            cw[2 * g] = o0;
+                            cw[2 * g + 1] = o1;
+                            sc |= sb << (8 * g);
+                        }
+                        if (col0 + 64 <= p.q_ld) {
+                            if (tok_ok) {
+                                uint4* dst = reinterpret_cast<uint4*>(p.q_codes + (token * p.q_ld + col0) / 2);
+                                dst[0] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
+                                dst[1] = make_uint4(cw[4], cw[5], cw[6], cw[7]);
+                            }
+                            // rows past m inside the last 128-row atom carry zero scales
+                            *reinterpret_cast<uint32_t*>(p.q_atoms + nvfp4_scale_offset(token, col0 / 16, p.q_ld)) =
+                                tok_ok ? sc : 0u;
+                        }
+                    }
+                }
+                if (staged) {
 #pragma unroll
                 for (int bx = 0; bx < MINE / 2; bx++) {
                     // the store that last read this half's 64-column box must be done with it
@@ -808,6 +867,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                                      (int)(rbase[0] - p.out_row0) + (hsel * (MINE / 2) + bx) * 64, mt * BM);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
+                }
                 }
                 PROF_ADD(10, t_c);
             } else {
@@ -1161,6 +1221,16 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
             p.tiles_n = (int)((w.row_begin + w.rows - base0 + 255) / 256);
         }
         p.out_row0 = w.row_begin;
+        if (a.qo_codes) {
+            // whole 64-column pieces of whole rows of the quantised matrix, starting at column 0
+            if (!a.qo_atoms || !(a.qo_divisor > 0.0f) || a.col != 0 || w.row_begin % 128 != 0 || w.rows % 64 != 0 ||
+                (a.y != nullptr))
+                return VELOX_ERR_UNSUPPORTED;
+            p.q_codes = a.qo_codes;
+            p.q_atoms = a.qo_atoms;
+            p.q_divisor = a.qo_divisor;
+            p.q_ld = w.rows;
+        }
         if ((rc = make_map(&ma, codes, false, a.m, k / 2)) != 0) return rc;
         if ((rc = make_map(&mb0, w.w, false, w.n, k / 2)) != 0) return rc;
         if ((rc = make_map(&mb1, w1.w, false, w1.n, k / 2)) != 0) return rc;

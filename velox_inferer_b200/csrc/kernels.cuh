@@ -20,6 +20,9 @@ struct LinearArgs {
     uint16_t* yb;            // bf16 twin of y, may be NULL
     const uint8_t* q_codes;  // activations already quantised to NVFP4 (codes [m, k/2]) ...
     const uint8_t* q_atoms;  // ... and their scale atoms; both NULL unless the caller has them
+    uint8_t* qo_codes;       // optional: the result also (or only) as NVFP4 activations for the
+    uint8_t* qo_atoms;       // next linear, quantised with qo_divisor (FP4 tensor-core path only)
+    float qo_divisor;
     long long ld;            // row stride of y / yb in elements
     long long col;           // first column written
 };

@@ -159,6 +159,8 @@ class LinearStack:
         self.outb = torch.zeros(m * s.hidden, dtype=bf, device=dev)
         self.a4 = a4
         self.hq = backend.q4_blob(m, s.hidden)                          # norm output as NVFP4
+        self.qq = backend.q4_blob(m, s.q_dim // world)                  # q projection as NVFP4 (o's input)
+        self.gq = backend.q4_blob(m, s.intermediate // world)           # silu(gate)*up as NVFP4 (down's input)
         self.weight_bytes = sum(v.buf.numel() for l in self.layers
                                 for v in (l.q, l.k, l.v, l.o, l.gate, l.up, l.down))
 
@@ -182,7 +184,8 @@ class LinearStack:
             if q4:
                 b.add_rms_norm_q4(self.x, None, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT,
                                   xb=None if first else self.pb)
-                b.linear_q4(self.hq, DIV_NORM_OUT, l.q, None, m, yb=self.qb)
+                # q feeds o directly (attention passthrough), so it is produced as o's FP4 input
+                b.linear_q4_to_q4(self.hq, DIV_NORM_OUT, l.q, m, self.qq, DIV_O_IN)
                 b.linear_q4(self.hq, DIV_NORM_OUT, l.k, None, m, yb=self.kb)
                 b.linear_q4(self.hq, DIV_NORM_OUT, l.v, None, m, yb=self.vb)
             else:
@@ -192,16 +195,20 @@ class LinearStack:
                 b.linear_bf16(self.hb, l.k, None, m, yb=self.kb)
                 b.linear_bf16(self.hb, l.v, None, m, yb=self.vb)
             first = False
-            b.linear_bf16(self.qb, l.o, None, m, yb=self.pb)       # attention passthrough: a = q
+            if q4:
+                b.linear_q4(self.qq, DIV_O_IN, l.o, None, m, yb=self.pb)
+            else:
+                b.linear_bf16(self.qb, l.o, None, m, yb=self.pb)   # attention passthrough: a = q
             self._all_reduce(self.pb[: m * h])
             if q4:
                 b.add_rms_norm_q4(self.x, None, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT,
                                   xb=self.pb)
-                b.linear_swiglu_q4(self.hq, DIV_NORM_OUT, l.gate, l.up, None, self.gb, m)
+                b.linear_swiglu_q4_to_q4(self.hq, DIV_NORM_OUT, l.gate, l.up, m, self.gq, DIV_DOWN_IN)
+                b.linear_q4(self.gq, DIV_DOWN_IN, l.down, None, m, yb=self.pb)
             else:
                 b.add_rms_norm_twin(self.x, None, self.norm_w, None, self.hb, m, h, s.norm_eps, xb=self.pb)
                 b.linear_swiglu_twin(self.hb, l.gate, l.up, None, self.gb, m)
-            b.linear_bf16(self.gb, l.down, None, m, yb=self.pb)
+                b.linear_bf16(self.gb, l.down, None, m, yb=self.pb)
             self._all_reduce(self.pb[: m * h])
         b.add_bf16(self.x, self.pb, m * h)
         out = b.bf16_twin_into(self.x, self.outb, m * h)
