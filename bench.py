@@ -182,7 +182,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-components", action="store_true", help="skip the single-linear GEMV / GEMM lines")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="decode: launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
 
@@ -229,22 +229,28 @@ def main():
         stack.forward(x_dev, m)
     barrier()
 
-    # Decode steps are hundreds of short launches: replay them as one CUDA graph, as the reference
-    # runs its step (crates/velox-cuda/src/lib.rs:2130-2204), unless --no-graph is given. Event
+    # A step is hundreds of launches (and, with several ranks, two all-reduces per layer): it is
+    # captured once and replayed as one CUDA graph, as the reference runs its step
+    # (crates/velox-cuda/src/lib.rs:2130-2204), unless --no-graph is given or capture fails. Event
     # timing of single kernels is not possible inside a graph, so the roofline pass runs eagerly.
     step = lambda: stack.forward(x_dev, m)
-    use_graph = (m <= 16) and not args.no_graph
+    use_graph = not args.no_graph
     if use_graph:
-        side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            stack.forward(x_dev, m)
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            stack.forward(x_dev, m)
-        step = graph.replay
-        for _ in range(3):
-            step()
+        try:
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                stack.forward(x_dev, m)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                stack.forward(x_dev, m)
+            step = graph.replay
+            for _ in range(3):
+                step()
+        except Exception as exc:  # capture not possible here: time eager launches instead
+            print(f"[bench] CUDA graph capture failed ({exc}); launching eagerly", file=sys.stderr, flush=True)
+            use_graph = False
+            step = lambda: stack.forward(x_dev, m)
         barrier()
     if b.lib.velox_sm100_debug_status() != 0:
         raise SystemExit("tensor-core kernel reported a timed-out wait")
@@ -299,9 +305,23 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
 
-    if rank != 0:
+    def shutdown():
+        # A captured graph holds the communicator's kernels: drop it and drain the device before the
+        # process group goes away, and never let teardown outlive the measurement by more than a
+        # few seconds (a rank stuck here would keep the whole launcher alive).
+        nonlocal step
         if world > 1:
+            threading.Timer(20.0, lambda: os._exit(0)).start()
+            step = None
+            if use_graph:
+                graph.reset()
+            torch.cuda.synchronize()
+            dist.barrier()
             dist.destroy_process_group()
+            os._exit(0)
+
+    if rank != 0:
+        shutdown()
         return
 
     # ---- roofline of the dominant kernel ----
@@ -347,8 +367,8 @@ def main():
     else:
         line["cpu_baseline"] = None
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    sys.stdout.flush()
+    shutdown()
 
 
 def components(b, peaks, graph=True):

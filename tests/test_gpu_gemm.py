@@ -268,8 +268,9 @@ def test_linear_q4_refuses_what_the_fp4_gemm_does_not_serve(b):
         b.linear_q4(q4, 128.0, make_view(b, payload, NV, n, k, 0, n, ActPolicy.allow_a4(256.0)), y, 128)
     with pytest.raises(Unsupported):                     # policy does not allow FP4 activations
         b.linear_q4(q4, 256.0, make_view(b, payload, NV, n, k, 0, n, A16), y, 128)
-    with pytest.raises(Unsupported):                     # decode sizes take the bf16 GEMV
-        b.linear_q4(q4, 256.0, make_view(b, payload, NV, n, k, 0, n, ActPolicy.allow_a4(256.0)), y, 4)
+    # decode sizes are served too (tensor-core decode path reads the same blob)
+    b.linear_q4(q4, 256.0, make_view(b, payload, NV, n, k, 0, n, ActPolicy.allow_a4(256.0)), y, 4)
+    assert b.lib.velox_sm100_debug_status() == 0
 
 
 @pytest.mark.parametrize("n,k,m", [(256, 640, 37), (512, 1024, 300), (1024, 512, 513)])

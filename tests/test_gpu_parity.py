@@ -139,6 +139,52 @@ def test_linear_decode_widths_match_oracle(b, fmt, n, k, begin, rows, m):
         assert np.array_equal(y2.cpu().numpy().view(np.uint32), got.reshape(-1).view(np.uint32))
 
 
+# ---- decode on the block-scaled tensor cores (views that admit NVFP4 activations) --------------
+
+@pytest.mark.parametrize("fmt,n,k,begin,rows,m", [c for c in GEMV_CASES if c[0] == NV] + [
+    (NV, 256, 8192, 0, 256, 4),       # few tiles, long K: K splits with the ordered fix-up
+    (NV, 1280, 256, 128, 1024, 16),   # one k-block per item
+])
+def test_linear_decode_nvfp4_activations_match_oracle(b, fmt, n, k, begin, rows, m):
+    r = O.Rng(11)
+    payload = r.random_weight(FMT_O[fmt], n, k)
+    x = r.vec(m * k, 1.0)
+    policy = ActPolicy.allow_a4(600.0)
+    view = make_view(b, payload, fmt, n, k, begin, rows, policy)
+    act = b.linear_act(view, m)
+    assert act == ActQuant(ActQuant.NVFP4, 600.0)     # the tensor-core decode path declares itself
+    want = oracle_linear(x, payload, fmt, n, k, begin, rows, m, act)
+    y = b.alloc(m * rows + 2)
+    yb = torch.zeros(m * rows, dtype=torch.bfloat16, device=y.device)
+    for _ in range(2):                                 # twice: the split counters return to zero
+        y.zero_()
+        b.linear(b.upload(x), view, y, m, yb=yb)
+        assert b.lib.velox_sm100_debug_status() == 0
+        got = y.cpu().numpy()
+        assert got[-2:].tolist() == [0.0, 0.0]
+        got = got[:-2].reshape(m, rows)
+        e_conf, e_rms = both_metrics(got, want)
+        assert e_conf <= LINEAR_TOL and e_rms <= RMS_TOL, (e_conf, e_rms)
+        assert np.array_equal(bf16_bits(yb).reshape(-1), f32_to_bf16_bits(got.reshape(-1)))
+
+
+@pytest.mark.parametrize("k,w,m,order", [(512, 256, 1, "gate_up"), (1024, 128, 16, "up_gate"), (5120, 128, 3, "gate_up")])
+def test_linear_swiglu_decode_nvfp4_activations(b, k, w, m, order):
+    r = O.Rng(0x5e2)
+    x = r.vec(m * k, 1.0)
+    p = r.random_weight(FMT_O[NV], 2 * w, k)
+    parent = WeightView.full(b.upload_bytes(p), NV, 2 * w, k).with_act(ActPolicy.allow_a4(600.0))
+    bg, bu = (0, w) if order == "gate_up" else (w, 0)
+    gate, up = parent.rows_view(bg, w), parent.rows_view(bu, w)
+    act = b.linear_swiglu_act(gate, up, m)
+    assert act == ActQuant(ActQuant.NVFP4, 600.0)
+    want = _swiglu_want(x, p, p, NV, 2 * w, 2 * w, k, bg, bu, w, m, act)
+    out = b.alloc(m * w)
+    b.linear_swiglu(b.upload(x), gate, up, out, m)
+    assert b.lib.velox_sm100_debug_status() == 0
+    assert O.max_err(out.cpu().numpy(), want) <= 5e-4
+
+
 def test_portable_signature_entry_point(b):
     # velox_sm100_linear has velox_portable_linear's signature (portable.rs:81-91)
     n, k, m = 256, 512, 4

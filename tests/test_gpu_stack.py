@@ -6,6 +6,7 @@ import pytest
 import torch
 
 from oracle import oracle as O
+from velox_inferer_b200 import ActQuant
 from velox_inferer_b200.stack import DIV_DOWN_IN, DIV_NORM_OUT, DIV_O_IN, LinearStack, StackSpec
 
 from .gpu_util import backend
@@ -17,12 +18,16 @@ def _bf16(a):
     return O.quantize_activations(np.asarray(a, dtype=np.float32).reshape(-1), 1, O.ACT_BF16).reshape(np.shape(a))
 
 
-def _oracle_stack(stack, spec, x, m, prefill):
+def _oracle_stack(b, stack, spec, x, m):
     def lin(inp, view, div):
         n, k = view.parent_rows, view.k
         payload = view.buf.cpu().numpy()
-        act = (O.ACT_NVFP4, div) if prefill else (O.ACT_BF16, 0.0)
-        return O.linear(inp, payload, O.FMT_NVFP4, n, k, 0, n, m, act=act[0], divisor=act[1])
+        act = b.linear_act(view, m)                       # the rounding the backend declares
+        assert act.kind in (ActQuant.NVFP4, ActQuant.BF16)
+        if act.kind == ActQuant.NVFP4:
+            assert act.divisor == div
+            return O.linear(inp, payload, O.FMT_NVFP4, n, k, 0, n, m, act=O.ACT_NVFP4, divisor=div)
+        return O.linear(inp, payload, O.FMT_NVFP4, n, k, 0, n, m, act=O.ACT_BF16, divisor=0.0)
 
     ones = np.ones(spec.hidden, dtype=np.float32)
     x = _bf16(x).astype(np.float32)
@@ -52,7 +57,7 @@ def test_stack_matches_oracle_sequence(m):
     torch.cuda.synchronize()
     assert b.lib.velox_sm100_debug_status() == 0
     got = out[: m * spec.hidden].float().cpu().numpy().reshape(m, spec.hidden)
-    want = _oracle_stack(stack, spec, xb.float().cpu().numpy(), m, prefill=m > 16)
+    want = _oracle_stack(b, stack, spec, xb.float().cpu().numpy(), m)
     # every stage rounds to bf16 (2^-9 relative); two layers of it stay within a few bf16 ulps
     err = O.max_abs_diff(got, want) / O.rms(want)
     assert err <= 2e-2, err

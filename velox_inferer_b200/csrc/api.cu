@@ -2,6 +2,7 @@
 // checks as the reference's check::linear (crates/velox-core/src/check.rs:100-131), kernel
 // selection by (format, policy, m, k), and the launch-stream / scratch state the launchers share.
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 
@@ -88,7 +89,7 @@ int check_view(const velox_sm100_view* v) {
     return 0;
 }
 
-enum Path { PATH_GEMV, PATH_GEMM_A4, PATH_GEMM_A8, PATH_GEMM_BF16, PATH_GENERIC };
+enum Path { PATH_GEMV, PATH_GEMV_TC, PATH_GEMM_A4, PATH_GEMM_A8, PATH_GEMM_BF16, PATH_GENERIC };
 
 struct Plan {
     Path path;
@@ -103,6 +104,15 @@ static Plan plan_for(const velox_sm100_view& v, int m) {
     Plan p{PATH_GENERIC, VELOX_ACT_EXACT, 0.0f};
     if (v.k % 64 != 0) return p;
     if (m <= 16) {
+        // Decode. Where the view admits NVFP4 activations the stored bytes go to the block-scaled
+        // tensor cores as they are; otherwise bf16 activations and the unpacking GEMV.
+        if (v.format == VELOX_FMT_NVFP4 && v.policy == VELOX_POLICY_ALLOW_A4 && v.divisor > 0.0f && gemm_available() &&
+            !getenv("VELOX_SM100_DECODE_BF16")) {
+            p.path = PATH_GEMV_TC;
+            p.act = VELOX_ACT_NVFP4;
+            p.divisor = v.divisor;
+            return p;
+        }
         p.path = PATH_GEMV;
         p.act = VELOX_ACT_BF16;
         return p;
@@ -130,8 +140,8 @@ static Plan plan_for(const velox_sm100_view& v, int m) {
 static Plan plan_swiglu(const velox_sm100_view& both, const velox_sm100_view& gate,
                         const velox_sm100_view& up, int m) {
     Plan p = plan_for(both, m);
-    if (p.path == PATH_GEMM_A4 && (gate.row_begin - up.row_begin) % 128 != 0) {
-        p.path = PATH_GEMM_BF16;
+    if ((p.path == PATH_GEMM_A4 || p.path == PATH_GEMV_TC) && (gate.row_begin - up.row_begin) % 128 != 0) {
+        p.path = p.path == PATH_GEMV_TC ? PATH_GEMV : PATH_GEMM_BF16;
         p.act = VELOX_ACT_BF16;
         p.divisor = 0.0f;
     }
@@ -143,6 +153,9 @@ static int run(const LinearArgs& a, const Plan& p) {
     switch (p.path) {
         case PATH_GEMV:
             rc = gemv(a);
+            break;
+        case PATH_GEMV_TC:
+            rc = gemv_nvfp4_tc(a, p.divisor);
             break;
         case PATH_GEMM_A4:
         case PATH_GEMM_A8:
@@ -184,7 +197,9 @@ static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.qo_atoms = qo_atoms;
     a.qo_divisor = qo_divisor;
     const Plan p = plan_for(*view, m);
-    if ((q_codes || qo_codes) && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;   // FP4 GEMM only
+    // pre-quantised input: the FP4 tensor-core paths only; quantised output: the prefill GEMM only
+    if (q_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
+    if (qo_codes && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
     return run(a, p);
 }
 
@@ -224,7 +239,8 @@ static int swiglu_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.qo_atoms = qo_atoms;
     a.qo_divisor = qo_divisor;
     const Plan p = plan_swiglu(both, *gate, *up, m);
-    if ((q_codes || qo_codes) && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
+    if (q_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
+    if (qo_codes && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
     return run(a, p);
 }
 
@@ -270,7 +286,9 @@ int velox_sm100_linear_swiglu_act(const velox_sm100_view* gate, const velox_sm10
 
 int velox_sm100_debug_status(void) {
     const int a = gemm_status_sync();
-    return a != 0 ? a : gemv_status_sync();
+    if (a != 0) return a;
+    const int b = gemv_status_sync();
+    return b != 0 ? b : gemv_tc_status_sync();
 }
 
 long long velox_sm100_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

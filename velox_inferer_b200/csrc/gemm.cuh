@@ -1,6 +1,8 @@
 // Tensor-core (tcgen05) prefill GEMM entry points used by the dispatcher.
 #pragma once
 
+#include <cuda.h>  // CUtensorMap
+
 #include "kernels.cuh"
 
 namespace vx {
@@ -13,6 +15,14 @@ bool gemm_available();
 // (VELOX_ACT_NVFP4 with `divisor`, VELOX_ACT_FP8_ROW, or VELOX_ACT_BF16). Handles the fused
 // SwiGLU form. Returns VELOX_ERR_UNSUPPORTED for shapes it does not take.
 int gemm_linear(const LinearArgs& a, int act, float divisor);
+
+// 2-D tensor map over a row-major byte matrix [rows, row_bytes]: boxes of 128 bytes x box_rows rows,
+// 128-byte swizzle.
+int gemm_make_map_u8(CUtensorMap* map, const void* ptr, long long rows, long long row_bytes, int box_rows);
+
+// NVFP4 decode linear (m <= 16) on the block-scaled tensor cores, activations quantised to NVFP4
+// with `divisor` (or taken from a.q_codes / a.q_atoms). VELOX_ERR_UNSUPPORTED for other shapes.
+int gemv_nvfp4_tc(const LinearArgs& a, float divisor);
 
 // Synchronises the device and returns the tensor-core kernels' status word: 0, or the code of the
 // first bounded wait that gave up.

@@ -1,0 +1,520 @@
+// NVFP4 decode linear (m <= 16 tokens) on the block-scaled tensor cores.
+//
+// Decode is a byte stream: 0.5625 B per weight, every byte once. The SIMT/mma.sync GEMV spends
+// about 1.6 issue slots per weight on unpacking (E2M1 -> f16, times the block scale) and is bound
+// by instruction issue near half the copy rate. Here nothing is unpacked: a persistent CTA per SM
+// streams 128-row x 256-k tiles of the stored codes (16 KB, one tensor-map box) and their four
+// 512-byte scale atoms into shared memory, and tcgen05.mma kind::mxf4nvf4 consumes them as they
+// are - weight rows are the MMA M operand (128), the tokens the N operand (16, zero padded), the
+// activations NVFP4 with the view's per-tensor divisor (ActQuant::Nvfp4, which the view's AllowA4
+// policy admits at any m). An MMA of this shape takes a few tens of cycles, so a CTA is idle
+// unless bytes arrive: the ring (eight 18 KB stages) is what sets the speed.
+//
+// Work items are (128-row tile, K split); splits park f32 partial sums and the CTA that arrives
+// last at a tile adds them in split order, so the result does not depend on arrival order. Roles:
+//   warp 0      operand producer (TMA: W codes box + the x codes box, 16 rows);
+//   warp 1      MMA issuer (one elected lane), accumulators double-buffered in tensor memory;
+//   warp 2      scale producer (bulk copies of whole atoms, W then x);
+//   warps 4-7   epilogue: tcgen05.ld, K-split fix-up, per-tensor factors, optional silu(gate)*up;
+//   warps 8-11  scale movers: shared memory -> tensor memory (tcgen05.st), one per lane quadrant.
+// Every mbarrier wait is bounded; a wait that gives up records a code in the status word.
+//
+// Reference counterpart: linear_gemv_vec_kernel, crates/velox-cuda/kernels/portable_model.cu:1448-1626.
+#include <cstdlib>
+
+#include "common.cuh"
+#include "gemm.cuh"
+#include "kernels.cuh"
+#include "tcgen.cuh"
+
+namespace vx {
+
+constexpr int DT_STAGES = 8;
+constexpr int DT_W_BYTES = 128 * 128;   // 128 weight rows x 128 bytes (256 k)
+constexpr int DT_X_BYTES = 16 * 128;    // 16 token rows x 128 bytes
+constexpr int DT_STAGE_BYTES = DT_W_BYTES + DT_X_BYTES;
+constexpr int DT_SF_STAGE_BYTES = 2048 + 2048;   // four W atoms, four x atoms
+constexpr int DT_OFF_SF = DT_STAGES * DT_STAGE_BYTES;
+constexpr int DT_OFF_BARS = DT_OFF_SF + DT_STAGES * DT_SF_STAGE_BYTES;
+constexpr int DT_SMEM_BYTES = DT_OFF_BARS + 1024 + 512;
+constexpr int DT_THREADS = 384;
+constexpr int DT_TMEM_COLS = 512;
+constexpr int DT_ACC_COLS = 32;      // per buffer: 16 token columns for each of up to two passes
+constexpr int DT_SF_COL = 64;        // scale sets follow the two accumulator buffers
+constexpr int DT_SF_SET = 32;        // per set: 16 columns of W scales, 16 of x scales
+
+struct DtParams {
+    int m;
+    int k_blocks, k_steps;
+    long long k_tiles64;
+    long long tile0[2];          // first 128-row tile (parent coordinates) of each pass
+    int tiles, splits;
+    const uint8_t* sfw[2];
+    const uint8_t* sfx;
+    const float* wdiv[2];
+    float alpha;                 // 1 / activation divisor
+    long long valid_begin, valid_end;   // rows of the view, pass-0 parent coordinates
+    float* y;
+    uint16_t* yb;
+    long long ld, col;
+    float* partial;              // [items][V][128][16] when splits > 1
+    int* tickets;                // [tiles], zero between launches
+    int* status;
+};
+
+__device__ int g_gemv_tc_status = 0;
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(DT_THREADS, 1)
+gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
+                     const __grid_constant__ CUtensorMap map_x, const DtParams p) {
+    constexpr int V = SWIGLU ? 2 : 1;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t sf_ring = base + DT_OFF_SF;
+    const uint32_t bars = base + DT_OFF_BARS;
+    auto op_full = [&](int s) { return bars + 8u * s; };
+    auto op_empty = [&](int s) { return bars + 8u * (DT_STAGES + s); };
+    auto sf_full = [&](int s) { return bars + 8u * (2 * DT_STAGES + s); };
+    auto sf_empty = [&](int s) { return bars + 8u * (3 * DT_STAGES + s); };
+    auto tsf_full = [&](int s) { return bars + 8u * (4 * DT_STAGES + s); };
+    auto tsf_empty = [&](int s) { return bars + 8u * (5 * DT_STAGES + s); };
+    auto acc_full = [&](int b) { return bars + 8u * (6 * DT_STAGES + b); };
+    auto acc_empty = [&](int b) { return bars + 8u * (6 * DT_STAGES + 2 + b); };
+    const uint32_t tmem_slot = bars + 8u * (6 * DT_STAGES + 4);
+    const uint32_t flag_slot = tmem_slot + 8u;   // "this CTA finishes the tile", shared by the epilogue warps
+    uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+    volatile uint32_t* flag_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (flag_slot - smem_u32(smem_raw)));
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < DT_STAGES; s++) {
+            mbar_init(op_full(s), 1);
+            mbar_init(op_empty(s), 1);
+            mbar_init(sf_full(s), 1);
+            mbar_init(sf_empty(s), 4);
+            mbar_init(tsf_full(s), 4);
+            mbar_init(tsf_empty(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full(b), 1);
+            mbar_init(acc_empty(b), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w0) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w1) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot),
+                     "r"((uint32_t)DT_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot_ptr;
+
+    const int items = p.tiles * p.splits;
+    auto kb_begin = [&](int split) { return (int)((long long)split * p.k_blocks / p.splits); };
+
+    if (warp == 0) {
+        // ---------------- operand producer ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const bool leader = elect_one();
+        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+            const int tile = item / p.splits, split = item % p.splits;
+            const int kb0 = kb_begin(split), kb1 = kb_begin(split + 1);
+            for (int v = 0; v < V && ok; v++) {
+                const int row0 = (int)((p.tile0[v] + tile) * 128);
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(op_empty(stage), phase ^ 1u, 20)) {
+                        if (leader) atomicExch(p.status, 21);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t sw = base + stage * DT_STAGE_BYTES;
+                    if (leader) {
+                        mbar_arrive_expect_tx(op_full(stage), DT_STAGE_BYTES);
+                        tma_load_2d(sw, v ? &map_w1 : &map_w0, op_full(stage), kb * 128, row0);
+                        tma_load_2d(sw + DT_W_BYTES, &map_x, op_full(stage), kb * 128, 0);
+                    }
+                    if (++stage == DT_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        if (!ok) __nanosleep(200000);   // let copies already in flight land before the CTA exits
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const bool leader = elect_one();
+        // M = 128, N = 16, E2M1 x E2M1 with UE4M3 block scales, K-major operands, f32 accumulate
+        const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        int n = 0;
+        for (int item = blockIdx.x; item < items && ok; item += gridDim.x, n++) {
+            const int split = item % p.splits;
+            const int kb0 = kb_begin(split), kb1 = kb_begin(split + 1);
+            const int buf = n & 1;
+            if (!mbar_wait(acc_empty(buf), ((uint32_t)(n >> 1) & 1u) ^ 1u)) {
+                if (leader) atomicExch(p.status, 22);
+                break;
+            }
+            for (int v = 0; v < V && ok; v++) {
+                const uint32_t d = tmem + buf * DT_ACC_COLS + v * 16;
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(op_full(stage), phase) || !mbar_wait(tsf_full(stage), phase)) {
+                        if (leader) atomicExch(p.status, 23);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const int steps = min(4, p.k_steps - 4 * kb);
+                    const uint32_t sw = base + stage * DT_STAGE_BYTES;
+                    const uint64_t da = smem_desc_sw128(sw), db = smem_desc_sw128(sw + DT_W_BYTES);
+                    const uint32_t tsf = tmem + DT_SF_COL + stage * DT_SF_SET;
+                    if (leader) {
+                        for (int j = 0; j < steps; j++)
+                            tc_mma<KIND_MXF4, 1>(d, da + 2u * j, db + 2u * j, idesc, (kb != kb0 || j != 0) ? 1u : 0u,
+                                                 tsf + 4 * j, tsf + 16 + 4 * j);
+                        tc_commit(op_empty(stage));
+                        tc_commit(tsf_empty(stage));
+                    }
+                    if (++stage == DT_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            if (ok && leader) tc_commit(acc_full(buf));
+        }
+    } else if (warp == 2) {
+        // ---------------- scale producer ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        const bool leader = elect_one();
+        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+            const int tile = item / p.splits, split = item % p.splits;
+            const int kb0 = kb_begin(split), kb1 = kb_begin(split + 1);
+            for (int v = 0; v < V && ok; v++) {
+                const uint8_t* wsf = p.sfw[v] + (p.tile0[v] + tile) * p.k_tiles64 * 512;
+                for (int kb = kb0; kb < kb1; kb++) {
+                    if (!mbar_wait(sf_empty(stage), phase ^ 1u, 50)) {
+                        if (leader) atomicExch(p.status, 24);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bytes = (uint32_t)min(4, p.k_steps - 4 * kb) * 512u;
+                    const uint32_t dst = sf_ring + stage * DT_SF_STAGE_BYTES;
+                    if (leader) {
+                        mbar_arrive_expect_tx(sf_full(stage), 2 * bytes);
+                        bulk_load_1d(dst, wsf + 4LL * kb * 512, bytes, sf_full(stage));
+                        bulk_load_1d(dst + 2048, p.sfx + 4LL * kb * 512, bytes, sf_full(stage));
+                    }
+                    if (++stage == DT_STAGES) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        if (!ok) __nanosleep(200000);
+    } else if (warp >= 8) {
+        // ---------------- scale movers ----------------
+        // Lane i of the warp serving lane quadrant q writes atom rows i, i+32, i+64, i+96: the 16
+        // bytes of atom row i are that atom's four 32-bit columns, replicated in every quadrant.
+        const int quad = warp % 4;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+            const int split = item % p.splits;
+            const int count = (kb_begin(split + 1) - kb_begin(split)) * V;
+            for (int i = 0; i < count; i++) {
+                if (!mbar_wait(sf_full(stage), phase, 50)) {
+                    if (lane == 0) atomicExch(p.status, 25);
+                    ok = false;
+                    break;
+                }
+                const uint32_t src = sf_ring + stage * DT_SF_STAGE_BYTES + (uint32_t)lane * 16u;
+                uint32_t ra[16], rb[16];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const uint4 a = lds16(src + 512 * j);
+                    const uint4 b = lds16(src + 2048 + 512 * j);
+                    ra[4 * j] = a.x; ra[4 * j + 1] = a.y; ra[4 * j + 2] = a.z; ra[4 * j + 3] = a.w;
+                    rb[4 * j] = b.x; rb[4 * j + 1] = b.y; rb[4 * j + 2] = b.z; rb[4 * j + 3] = b.w;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sf_empty(stage));
+                // the MMAs that read this column set one ring pass ago must have completed
+                if (!mbar_wait(tsf_empty(stage), phase ^ 1u, 50)) {
+                    if (lane == 0) atomicExch(p.status, 26);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tsf = tmem + ((uint32_t)(quad * 32) << 16) + DT_SF_COL + stage * DT_SF_SET;
+                tc_st16(tsf, ra);
+                tc_st16(tsf + 16, rb);
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tsf_full(stage));
+                if (++stage == DT_STAGES) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------- epilogue ----------------
+        const int quad = warp % 4;
+        const int row_in_tile = quad * 32 + lane;
+        const float f0 = p.alpha / *p.wdiv[0];
+        const float f1 = SWIGLU ? p.alpha / *p.wdiv[1] : 0.0f;
+        int n = 0;
+        for (int item = blockIdx.x; item < items; item += gridDim.x, n++) {
+            const int tile = item / p.splits;
+            const int buf = n & 1;
+            if (!mbar_wait(acc_full(buf), (uint32_t)(n >> 1) & 1u, 60)) {
+                if (lane == 0) atomicExch(p.status, 27);
+                break;
+            }
+            tc_fence_after();
+            uint32_t r[V][16];
+            const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + buf * DT_ACC_COLS;
+#pragma unroll
+            for (int v = 0; v < V; v++) tc_ld16(taddr + v * 16, r[v]);
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(buf));
+            float acc[V][16];
+#pragma unroll
+            for (int v = 0; v < V; v++)
+#pragma unroll
+                for (int j = 0; j < 16; j++) acc[v][j] = __uint_as_float(r[v][j]);
+
+            bool finish = true;
+            if (p.splits > 1) {
+                // park this item's partial sums; the CTA that arrives last at the tile adds all
+                // splits in index order and finishes
+                float4* mine = reinterpret_cast<float4*>(p.partial + ((size_t)item * V * 128 + row_in_tile) * 16);
+#pragma unroll
+                for (int v = 0; v < V; v++)
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        mine[(size_t)v * 128 * 4 + q] =
+                            make_float4(acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2], acc[v][4 * q + 3]);
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 4 && lane == 0) {
+                    const int prev = atomicAdd(p.tickets + tile, 1);
+                    const bool last = prev == p.splits - 1;
+                    if (last) p.tickets[tile] = 0;   // back to zero for the next launch
+                    *flag_ptr = last ? 1u : 0u;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                finish = *flag_ptr != 0u;
+                asm volatile("bar.sync 1, 128;" ::: "memory");   // the flag is read before it is rewritten
+                if (finish) {
+                    __threadfence();
+#pragma unroll
+                    for (int v = 0; v < V; v++)
+#pragma unroll
+                        for (int j = 0; j < 16; j++) acc[v][j] = 0.0f;
+                    for (int s = 0; s < p.splits; s++) {
+                        const float4* theirs = reinterpret_cast<const float4*>(
+                            p.partial + ((size_t)(tile * p.splits + s) * V * 128 + row_in_tile) * 16);
+#pragma unroll
+                        for (int v = 0; v < V; v++)
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                const float4 t = __ldcg(theirs + (size_t)v * 128 * 4 + q);
+                                acc[v][4 * q] += t.x;
+                                acc[v][4 * q + 1] += t.y;
+                                acc[v][4 * q + 2] += t.z;
+                                acc[v][4 * q + 3] += t.w;
+                            }
+                    }
+                }
+            }
+            if (finish) {
+                const long long row = (p.tile0[0] + tile) * 128 + row_in_tile;
+                if (row >= p.valid_begin && row < p.valid_end) {
+                    const long long o0 = p.col + (row - p.valid_begin);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        if (j < p.m) {
+                            float val = acc[0][j] * f0;
+                            if (SWIGLU) {
+                                const float u = acc[V - 1][j] * f1;
+                                val = val / (1.0f + __expf(-val)) * u;
+                            }
+                            if (p.y) p.y[(long long)j * p.ld + o0] = val;
+                            if (p.yb) p.yb[(long long)j * p.ld + o0] = bf16_bits(val);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)DT_TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// ---- host side ----
+
+static int* gemv_tc_status_ptr() {
+    static int* ptrs[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptrs[dev]) cudaGetSymbolAddress(reinterpret_cast<void**>(&ptrs[dev]), g_gemv_tc_status);
+    return ptrs[dev];
+}
+
+// Arrival counters of the K-split fix-up: zeroed when (re)allocated, returned to zero by the kernel.
+static int* gemv_tc_tickets(size_t count) {
+    static int* ptrs[64] = {};
+    static size_t caps[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (count > caps[dev]) {
+        const size_t n = count < 4096 ? 4096 : count * 2;
+        int* q = nullptr;
+        if (cudaMalloc(&q, n * sizeof(int)) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        if (cudaMemsetAsync(q, 0, n * sizeof(int), stream()) != cudaSuccess) return nullptr;
+        ptrs[dev] = q;   // the old block stays allocated: queued work may still use it
+        caps[dev] = n;
+    }
+    return ptrs[dev];
+}
+
+int gemv_tc_status_sync() {
+    int v = -1;
+    if (cudaMemcpyFromSymbol(&v, g_gemv_tc_status, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}
+
+int gemv_nvfp4_tc(const LinearArgs& a, float divisor) {
+    if (!gemm_available()) return VELOX_ERR_UNSUPPORTED;
+    const velox_sm100_view& w = a.w;
+    const bool sw = a.swiglu != 0;
+    const velox_sm100_view& u = sw ? a.up : a.w;
+    if (w.format != VELOX_FMT_NVFP4 || a.m < 1 || a.m > 16 || w.k % 64 != 0 || !(divisor > 0.0f))
+        return VELOX_ERR_UNSUPPORTED;
+    if (sw && ((w.row_begin - u.row_begin) % 128 != 0 || u.format != VELOX_FMT_NVFP4)) return VELOX_ERR_UNSUPPORTED;
+    if (reinterpret_cast<uintptr_t>(w.w) & 15) return VELOX_ERR_UNSUPPORTED;
+    const long long k = w.k;
+
+    const uint8_t* codes = a.q_codes;
+    const uint8_t* atoms = a.q_atoms;
+    int rc;
+    if (!codes || !atoms) {
+        uint8_t* c = static_cast<uint8_t*>(scratch(SCRATCH_ACT_CODES, (size_t)a.m * k / 2));
+        uint8_t* s = static_cast<uint8_t*>(scratch(SCRATCH_ACT_SCALES, (size_t)128 * k / 16));
+        if (!c || !s) return (int)cudaErrorMemoryAllocation;
+        if ((rc = quantize_act_nvfp4(a.x, a.xb, a.m, k, divisor, c, s)) != 0) return rc;
+        codes = c;
+        atoms = s;
+    }
+
+    DtParams p{};
+    p.m = a.m;
+    p.k_steps = (int)(k / 64);
+    p.k_blocks = (p.k_steps + 3) / 4;
+    p.k_tiles64 = k / 64;
+    p.tile0[0] = w.row_begin / 128;
+    p.tile0[1] = u.row_begin / 128;
+    p.tiles = (int)((w.row_begin + w.rows - 1) / 128 - w.row_begin / 128 + 1);
+    p.sfw[0] = w.w + align256(w.n * k / 2);
+    p.sfw[1] = u.w + align256(u.n * k / 2);
+    p.wdiv[0] = reinterpret_cast<const float*>(p.sfw[0] + w.n * k / 16);
+    p.wdiv[1] = reinterpret_cast<const float*>(p.sfw[1] + u.n * k / 16);
+    p.sfx = atoms;
+    p.alpha = 1.0f / divisor;
+    p.valid_begin = w.row_begin;
+    p.valid_end = w.row_begin + w.rows;
+    p.y = a.y;
+    p.yb = a.yb;
+    p.ld = a.ld;
+    p.col = a.col;
+    p.status = gemv_tc_status_ptr();
+    if (!p.status) return VELOX_ERR_UNSUPPORTED;
+
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    // K splits: the fewest that keep the SMs' last round of items at least 85% full (else the
+    // fullest), each split at least four k-blocks long
+    {
+        int best = 1;
+        double best_eff = 0.0;
+        const int max_splits = p.k_blocks / 4 < 1 ? 1 : (p.k_blocks / 4 > 16 ? 16 : p.k_blocks / 4);
+        for (int s = 1; s <= max_splits; s++) {
+            const long long items = (long long)p.tiles * s;
+            const long long rounds = (items + sms - 1) / sms;
+            const double eff = (double)items / (double)(rounds * sms);
+            if (eff > best_eff + 0.02) {
+                best_eff = eff;
+                best = s;
+            }
+            if (eff >= 0.85) break;
+        }
+        p.splits = best;
+        if (const char* e = getenv("VELOX_SM100_DECODE_SPLITS")) p.splits = atoi(e) > 0 ? atoi(e) : p.splits;
+        if (p.splits > p.k_blocks) p.splits = p.k_blocks;
+    }
+    if (p.splits > 1) {
+        const size_t per_item = (size_t)(sw ? 2 : 1) * 128 * 16 * sizeof(float);
+        p.partial = static_cast<float*>(scratch(SCRATCH_Y_F32, (size_t)p.tiles * p.splits * per_item));
+        p.tickets = gemv_tc_tickets((size_t)p.tiles);
+        if (!p.partial || !p.tickets) return (int)cudaErrorMemoryAllocation;
+    }
+
+    CUtensorMap mw0, mw1, mx;
+    if ((rc = gemm_make_map_u8(&mw0, w.w, w.n, k / 2, 128)) != 0) return rc;
+    if ((rc = gemm_make_map_u8(&mw1, u.w, u.n, k / 2, 128)) != 0) return rc;
+    if ((rc = gemm_make_map_u8(&mx, codes, a.m, k / 2, 16)) != 0) return rc;
+
+    const long long items = (long long)p.tiles * p.splits;
+    const int grid = (int)(items < sms ? items : sms);
+    cudaError_t e;
+    TimedRegion timed(TIMED_GEMV);
+    if (sw) {
+        auto kern = gemv_nvfp4_tc_kernel<true>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, DT_THREADS, DT_SMEM_BYTES, stream()>>>(mw0, mw1, mx, p);
+    } else {
+        auto kern = gemv_nvfp4_tc_kernel<false>;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        kern<<<grid, DT_THREADS, DT_SMEM_BYTES, stream()>>>(mw0, mw1, mx, p);
+    }
+    return launch_status();
+}
+
+}  // namespace vx

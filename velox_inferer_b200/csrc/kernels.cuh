@@ -38,6 +38,8 @@ int gemv_nvfp4_mma(const LinearArgs& a);
 // NVFP4 only: TMA-staged weight stream + mma.sync; k % 128 == 0. The preferred decode kernel.
 int gemv_nvfp4_tma(const LinearArgs& a);
 int gemv_status_sync();
+int gemv_tc_status_sync();
+int gemv_tc_status_sync();
 // Any shape, any m: one warp per output row, per-element decode. Slow but total.
 int linear_generic(const LinearArgs& a);
 

@@ -26,7 +26,7 @@ from typing import List, Optional
 import torch
 
 from .backend import Sm100Backend
-from .weights import ActPolicy, WeightFormat, WeightView, align256
+from .weights import ActPolicy, ActQuant, WeightFormat, WeightView, align256
 
 NV = WeightFormat.NVFP4
 
@@ -177,15 +177,20 @@ class LinearStack:
         launches0 = b.launch_count()
         self.x[: m * h].copy_(xb_in.reshape(-1)[: m * h])
         first = True
-        # at prefill sizes the norm hands the FP4 linears their quantised input directly
-        q4 = self.a4 and m > 16
+        # the norm hands the FP4 linears their quantised input directly; at prefill sizes the
+        # linears that feed another linear also emit its FP4 input from their epilogue
+        q4 = self.a4 and b.linear_act(self.layers[0].q, m).kind == ActQuant.NVFP4
+        emit = q4 and m > 16
         for l in self.layers:
             # x (+= previous down partial), h = rms_norm(x)
             if q4:
                 b.add_rms_norm_q4(self.x, None, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT,
                                   xb=None if first else self.pb)
                 # q feeds o directly (attention passthrough), so it is produced as o's FP4 input
-                b.linear_q4_to_q4(self.hq, DIV_NORM_OUT, l.q, m, self.qq, DIV_O_IN)
+                if emit:
+                    b.linear_q4_to_q4(self.hq, DIV_NORM_OUT, l.q, m, self.qq, DIV_O_IN)
+                else:
+                    b.linear_q4(self.hq, DIV_NORM_OUT, l.q, None, m, yb=self.qb)
                 b.linear_q4(self.hq, DIV_NORM_OUT, l.k, None, m, yb=self.kb)
                 b.linear_q4(self.hq, DIV_NORM_OUT, l.v, None, m, yb=self.vb)
             else:
@@ -195,7 +200,7 @@ class LinearStack:
                 b.linear_bf16(self.hb, l.k, None, m, yb=self.kb)
                 b.linear_bf16(self.hb, l.v, None, m, yb=self.vb)
             first = False
-            if q4:
+            if emit:
                 b.linear_q4(self.qq, DIV_O_IN, l.o, None, m, yb=self.pb)
             else:
                 b.linear_bf16(self.qb, l.o, None, m, yb=self.pb)   # attention passthrough: a = q
@@ -203,8 +208,12 @@ class LinearStack:
             if q4:
                 b.add_rms_norm_q4(self.x, None, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT,
                                   xb=self.pb)
-                b.linear_swiglu_q4_to_q4(self.hq, DIV_NORM_OUT, l.gate, l.up, m, self.gq, DIV_DOWN_IN)
-                b.linear_q4(self.gq, DIV_DOWN_IN, l.down, None, m, yb=self.pb)
+                if emit:
+                    b.linear_swiglu_q4_to_q4(self.hq, DIV_NORM_OUT, l.gate, l.up, m, self.gq, DIV_DOWN_IN)
+                    b.linear_q4(self.gq, DIV_DOWN_IN, l.down, None, m, yb=self.pb)
+                else:
+                    b.linear_swiglu_q4(self.hq, DIV_NORM_OUT, l.gate, l.up, None, self.gb, m)
+                    b.linear_bf16(self.gb, l.down, None, m, yb=self.pb)
             else:
                 b.add_rms_norm_twin(self.x, None, self.norm_w, None, self.hb, m, h, s.norm_eps, xb=self.pb)
                 b.linear_swiglu_twin(self.hb, l.gate, l.up, None, self.gb, m)
