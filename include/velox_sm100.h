@@ -204,8 +204,9 @@ int velox_sm100_add_rms_norm_twin(float* acc, const float* x, const float* weigh
  * dim/2] and E4M3 scale atoms over ceil(rows/128)*128 rows, quantised from the bf16-rounded values
  * with `divisor` exactly as quant::quantize_activations(Nvfp4{divisor}) does - so the projections
  * that follow run without a quantisation pass. velox_sm100_linear_q4 / _swiglu_q4 take that blob
- * in place of x; they serve NVFP4 views whose policy is AllowA4 with the same divisor at m > 16
- * and return VELOX_ERR_UNSUPPORTED otherwise (use the bf16 entry points then). */
+ * in place of x; they serve NVFP4 views whose policy is AllowA4 with the same divisor, at any m
+ * (prefill GEMM above 16 tokens, tensor-core decode kernel up to 16), and return
+ * VELOX_ERR_UNSUPPORTED otherwise (use the bf16 entry points then). */
 int velox_sm100_add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float* weight,
                                 uint16_t* yb, uint8_t* codes, uint8_t* atoms, int rows, int dim, float eps,
                                 int offset, float divisor);
@@ -216,9 +217,10 @@ int velox_sm100_linear_swiglu_q4(const uint8_t* codes, const uint8_t* atoms, flo
                                  uint16_t* outb);
 
 /* The FP4 linears as producers of the next linear's FP4 input: the result, rounded to bf16, is
- * quantised in the GEMM epilogue with `out_divisor` into out_codes [m, rows/2] and out_atoms (scale
- * atoms over ceil(m/128)*128 rows, zero past m) - bit for bit what
- * velox_sm100_quantize_act_nvfp4 makes of the bf16 output - and also stored as bf16 when yb / outb
+ * quantised in the kernel's epilogue with `out_divisor` into out_codes [m, rows/2] and out_atoms
+ * (scale atoms over ceil(m/128)*128 rows; the scales of rows past m are zero after a prefill call
+ * and left as they were after a decode call, whose consumers do not read them) - for rows < m bit
+ * for bit what velox_sm100_quantize_act_nvfp4 makes of the bf16 output - and also stored as bf16 when yb / outb
  * is not NULL. Same conditions as the _q4 entry points, and the view must start on a 128-row scale
  * tile and hold a multiple of 64 rows; VELOX_ERR_UNSUPPORTED otherwise. */
 int velox_sm100_linear_q4_to_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,

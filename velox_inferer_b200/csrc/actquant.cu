@@ -43,6 +43,7 @@ quantize_nvfp4_kernel(const float* __restrict__ x, const uint16_t* __restrict__ 
                       uint8_t* __restrict__ scale_atoms) {
     const long long groups = k / 16;
     const long long total = (long long)rows_padded * groups;
+    if (threadIdx.x == 0) grid_launch_dependents();   // the linear behind this may start fetching weights
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long row = idx / groups, g = idx % groups;

@@ -197,9 +197,9 @@ static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.qo_atoms = qo_atoms;
     a.qo_divisor = qo_divisor;
     const Plan p = plan_for(*view, m);
-    // pre-quantised input: the FP4 tensor-core paths only; quantised output: the prefill GEMM only
+    // pre-quantised input: the FP4 tensor-core paths only; and quantised output: the FP4 tensor-core paths only
     if (q_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
-    if (qo_codes && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
+    if (qo_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
     return run(a, p);
 }
 
@@ -240,7 +240,7 @@ static int swiglu_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.qo_divisor = qo_divisor;
     const Plan p = plan_swiglu(both, *gate, *up, m);
     if (q_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
-    if (qo_codes && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
+    if (qo_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
     return run(a, p);
 }
 

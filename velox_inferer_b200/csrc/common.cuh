@@ -39,6 +39,17 @@ __host__ __device__ __forceinline__ long long nvfp4_scale_offset(long long row, 
            (g % 4);
 }
 
+// ---- early start of the next kernel in the stream (programmatic dependent launch) ----
+// Returns once every kernel this launch depends on has completed and its writes are visible; at
+// once if the launch was not allowed to start early.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+// Lets a dependent launch that allows it start once all CTAs of this grid have said so or exited.
+__device__ __forceinline__ void grid_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // f32 -> E4M3 byte and two f32 -> one byte of E2M1 codes (the first in the low nibble): the
 // hardware's round-to-nearest-even, saturating conversions.
 __device__ __forceinline__ uint32_t f32_to_e4m3(float v) {

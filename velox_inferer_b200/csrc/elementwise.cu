@@ -93,6 +93,7 @@ add_rms_norm_q4_kernel(float* __restrict__ acc, const float* __restrict__ x, con
     __shared__ float red[8];
     const long long row = blockIdx.x;
     const int groups = dim / 16;
+    if (threadIdx.x == 0) grid_launch_dependents();   // a decode linear behind this may start fetching weights
     if (row >= rows) {
         for (int g = threadIdx.x; g < groups; g += blockDim.x) atoms[nvfp4_scale_offset(row, g, dim)] = 0;
         return;

@@ -10,8 +10,10 @@
 // policy admits at any m). An MMA of this shape takes a few tens of cycles, so a CTA is idle
 // unless bytes arrive: the ring (eight 18 KB stages) is what sets the speed.
 //
-// Work items are (128-row tile, K split); splits park f32 partial sums and the CTA that arrives
-// last at a tile adds them in split order, so the result does not depend on arrival order. Roles:
+// Work is cut by bytes, not by tiles: the (tile, k-block) steps of the whole matrix are laid end to
+// end and every CTA takes an equal contiguous run of them, so a run starts and ends inside tiles.
+// A CTA that holds only part of a tile's K parks f32 partial sums; the CTA that arrives last at
+// the tile adds the parts in K order, so the result does not depend on arrival order. Roles:
 //   warp 0      operand producer (TMA: W codes box + the x codes box, 16 rows);
 //   warp 1      MMA issuer (one elected lane), accumulators double-buffered in tensor memory;
 //   warp 2      scale producer (bulk copies of whole atoms, W then x);
@@ -48,7 +50,8 @@ struct DtParams {
     int k_blocks, k_steps;
     long long k_tiles64;
     long long tile0[2];          // first 128-row tile (parent coordinates) of each pass
-    int tiles, splits;
+    int tiles;
+    long long per_cta;           // (tile, k-block) steps per CTA; CTA c takes steps [c * per_cta, (c + 1) * per_cta)
     const uint8_t* sfw[2];
     const uint8_t* sfx;
     const float* wdiv[2];
@@ -57,7 +60,11 @@ struct DtParams {
     float* y;
     uint16_t* yb;
     long long ld, col;
-    float* partial;              // [items][V][128][16] when splits > 1
+    uint8_t* q_codes;            // optional: the result also (or only) as NVFP4 activations [m, q_ld / 2] ...
+    uint8_t* q_atoms;            // ... with their scale atoms, for the next linear
+    float q_divisor;
+    long long q_ld;
+    float* partial;              // [CTAs][2][V][128][16]: a CTA's first and last run can be partial tiles
     int* tickets;                // [tiles], zero between launches
     int* status;
 };
@@ -88,6 +95,9 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
 
+    // A kernel launched after this one with early start allowed may begin as CTAs here retire.
+    if (threadIdx.x == 0) grid_launch_dependents();
+
     if (threadIdx.x == 0) {
         for (int s = 0; s < DT_STAGES; s++) {
             mbar_init(op_full(s), 1);
@@ -117,8 +127,19 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
     tc_fence_after();
     const uint32_t tmem = *tmem_slot_ptr;
 
-    const int items = p.tiles * p.splits;
-    auto kb_begin = [&](int split) { return (int)((long long)split * p.k_blocks / p.splits); };
+    // This CTA's run of steps, walked tile by tile: each piece is (tile, k-blocks [kb0, kb1)).
+    const long long total_steps = (long long)p.tiles * p.k_blocks;
+    const long long u_begin = (long long)blockIdx.x * p.per_cta;
+    const long long u_end = u_begin + p.per_cta < total_steps ? u_begin + p.per_cta : total_steps;
+    struct Piece { int tile, kb0, kb1; };
+    auto piece_at = [&](long long u) {
+        Piece q;
+        q.tile = (int)(u / p.k_blocks);
+        q.kb0 = (int)(u % p.k_blocks);
+        const long long left = u_end - u;
+        q.kb1 = q.kb0 + left < p.k_blocks ? (int)(q.kb0 + left) : p.k_blocks;
+        return q;
+    };
 
     if (warp == 0) {
         // ---------------- operand producer ----------------
@@ -126,12 +147,26 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         uint32_t phase = 0;
         bool ok = true;
         const bool leader = elect_one();
-        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-            const int tile = item / p.splits, split = item % p.splits;
-            const int kb0 = kb_begin(split), kb1 = kb_begin(split + 1);
+        // The weights do not depend on the kernel before this one, the activations do: the first
+        // ring pass requests its weight boxes at once, then waits for the preceding grid (a
+        // no-op unless this launch was allowed to start early) and adds the activation boxes.
+        int issued = 0, pend_kb[DT_STAGES];
+        bool waited = false;
+        auto after_dependency = [&]() {
+            grid_dependency_wait();
+            if (leader)
+                for (int i = 0; i < issued; i++)
+                    tma_load_2d(base + i * DT_STAGE_BYTES + DT_W_BYTES, &map_x, op_full(i), pend_kb[i] * 128, 0);
+            waited = true;
+        };
+        for (long long u = u_begin; u < u_end && ok;) {
+            const Piece pc = piece_at(u);
+            const int tile = pc.tile, kb0 = pc.kb0, kb1 = pc.kb1;
+            u += kb1 - kb0;
             for (int v = 0; v < V && ok; v++) {
                 const int row0 = (int)((p.tile0[v] + tile) * 128);
                 for (int kb = kb0; kb < kb1; kb++) {
+                    if (!waited && issued == DT_STAGES) after_dependency();
                     if (!mbar_wait(op_empty(stage), phase ^ 1u, 20)) {
                         if (leader) atomicExch(p.status, 21);
                         ok = false;
@@ -141,8 +176,9 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                     if (leader) {
                         mbar_arrive_expect_tx(op_full(stage), DT_STAGE_BYTES);
                         tma_load_2d(sw, v ? &map_w1 : &map_w0, op_full(stage), kb * 128, row0);
-                        tma_load_2d(sw + DT_W_BYTES, &map_x, op_full(stage), kb * 128, 0);
+                        if (waited) tma_load_2d(sw + DT_W_BYTES, &map_x, op_full(stage), kb * 128, 0);
                     }
+                    if (!waited) pend_kb[issued++] = kb;
                     if (++stage == DT_STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -150,6 +186,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                 }
             }
         }
+        if (!waited) after_dependency();
         if (!ok) __nanosleep(200000);   // let copies already in flight land before the CTA exits
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
@@ -160,9 +197,10 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         // M = 128, N = 16, E2M1 x E2M1 with UE4M3 block scales, K-major operands, f32 accumulate
         const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
         int n = 0;
-        for (int item = blockIdx.x; item < items && ok; item += gridDim.x, n++) {
-            const int split = item % p.splits;
-            const int kb0 = kb_begin(split), kb1 = kb_begin(split + 1);
+        for (long long u = u_begin; u < u_end && ok; n++) {
+            const Piece pc = piece_at(u);
+            const int kb0 = pc.kb0, kb1 = pc.kb1;
+            u += kb1 - kb0;
             const int buf = n & 1;
             if (!mbar_wait(acc_empty(buf), ((uint32_t)(n >> 1) & 1u) ^ 1u)) {
                 if (leader) atomicExch(p.status, 22);
@@ -198,16 +236,31 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         }
     } else if (warp == 2) {
         // ---------------- scale producer ----------------
+        // (weight atoms at once, activation atoms after the preceding grid, as the operand producer)
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
         const bool leader = elect_one();
-        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-            const int tile = item / p.splits, split = item % p.splits;
-            const int kb0 = kb_begin(split), kb1 = kb_begin(split + 1);
+        int issued = 0, pend_kb[DT_STAGES];
+        bool waited = false;
+        auto x_atoms = [&](int st, int kb) {
+            const uint32_t bytes = (uint32_t)min(4, p.k_steps - 4 * kb) * 512u;
+            bulk_load_1d(sf_ring + st * DT_SF_STAGE_BYTES + 2048, p.sfx + 4LL * kb * 512, bytes, sf_full(st));
+        };
+        auto after_dependency = [&]() {
+            grid_dependency_wait();
+            if (leader)
+                for (int i = 0; i < issued; i++) x_atoms(i, pend_kb[i]);
+            waited = true;
+        };
+        for (long long u = u_begin; u < u_end && ok;) {
+            const Piece pc = piece_at(u);
+            const int tile = pc.tile, kb0 = pc.kb0, kb1 = pc.kb1;
+            u += kb1 - kb0;
             for (int v = 0; v < V && ok; v++) {
                 const uint8_t* wsf = p.sfw[v] + (p.tile0[v] + tile) * p.k_tiles64 * 512;
                 for (int kb = kb0; kb < kb1; kb++) {
+                    if (!waited && issued == DT_STAGES) after_dependency();
                     if (!mbar_wait(sf_empty(stage), phase ^ 1u, 50)) {
                         if (leader) atomicExch(p.status, 24);
                         ok = false;
@@ -218,8 +271,9 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                     if (leader) {
                         mbar_arrive_expect_tx(sf_full(stage), 2 * bytes);
                         bulk_load_1d(dst, wsf + 4LL * kb * 512, bytes, sf_full(stage));
-                        bulk_load_1d(dst + 2048, p.sfx + 4LL * kb * 512, bytes, sf_full(stage));
+                        if (waited) x_atoms(stage, kb);
                     }
+                    if (!waited) pend_kb[issued++] = kb;
                     if (++stage == DT_STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -227,6 +281,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                 }
             }
         }
+        if (!waited) after_dependency();
         if (!ok) __nanosleep(200000);
     } else if (warp >= 8) {
         // ---------------- scale movers ----------------
@@ -236,10 +291,10 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
-            const int split = item % p.splits;
-            const int count = (kb_begin(split + 1) - kb_begin(split)) * V;
-            for (int i = 0; i < count; i++) {
+        {
+            // one pass over this CTA's steps: the ring does not care where tiles begin
+            const long long count = (u_end > u_begin ? u_end - u_begin : 0) * V;
+            for (long long i = 0; i < count; i++) {
                 if (!mbar_wait(sf_full(stage), phase, 50)) {
                     if (lane == 0) atomicExch(p.status, 25);
                     ok = false;
@@ -283,8 +338,12 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         const float f0 = p.alpha / *p.wdiv[0];
         const float f1 = SWIGLU ? p.alpha / *p.wdiv[1] : 0.0f;
         int n = 0;
-        for (int item = blockIdx.x; item < items; item += gridDim.x, n++) {
-            const int tile = item / p.splits;
+        for (long long u = u_begin; u < u_end; n++) {
+            const Piece pc = piece_at(u);
+            const int tile = pc.tile;
+            const bool whole = pc.kb0 == 0 && pc.kb1 == p.k_blocks;
+            const bool first_piece = u == u_begin;
+            u += pc.kb1 - pc.kb0;
             const int buf = n & 1;
             if (!mbar_wait(acc_full(buf), (uint32_t)(n >> 1) & 1u, 60)) {
                 if (lane == 0) atomicExch(p.status, 27);
@@ -306,10 +365,15 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                 for (int j = 0; j < 16; j++) acc[v][j] = __uint_as_float(r[v][j]);
 
             bool finish = true;
-            if (p.splits > 1) {
-                // park this item's partial sums; the CTA that arrives last at the tile adds all
-                // splits in index order and finishes
-                float4* mine = reinterpret_cast<float4*>(p.partial + ((size_t)item * V * 128 + row_in_tile) * 16);
+            if (!whole) {
+                // park this piece's partial sums; the CTA that arrives last at the tile adds the
+                // pieces in K order (which is CTA order) and finishes. The tile's pieces belong to
+                // CTAs c_first .. c_last; a CTA's piece of a tile is its first piece exactly when its
+                // run starts inside that tile, otherwise it is its last.
+                const long long t0 = (long long)tile * p.k_blocks, t1 = t0 + p.k_blocks;
+                const int c_first = (int)(t0 / p.per_cta), c_last = (int)((t1 - 1) / p.per_cta);
+                float4* mine = reinterpret_cast<float4*>(
+                    p.partial + (((size_t)blockIdx.x * 2 + (first_piece ? 0 : 1)) * V * 128 + row_in_tile) * 16);
 #pragma unroll
                 for (int v = 0; v < V; v++)
 #pragma unroll
@@ -320,7 +384,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (warp == 4 && lane == 0) {
                     const int prev = atomicAdd(p.tickets + tile, 1);
-                    const bool last = prev == p.splits - 1;
+                    const bool last = prev == c_last - c_first;
                     if (last) p.tickets[tile] = 0;   // back to zero for the next launch
                     *flag_ptr = last ? 1u : 0u;
                 }
@@ -333,9 +397,10 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                     for (int v = 0; v < V; v++)
 #pragma unroll
                         for (int j = 0; j < 16; j++) acc[v][j] = 0.0f;
-                    for (int s = 0; s < p.splits; s++) {
+                    for (int c = c_first; c <= c_last; c++) {
+                        const int slot = (long long)c * p.per_cta >= t0 ? 0 : 1;
                         const float4* theirs = reinterpret_cast<const float4*>(
-                            p.partial + ((size_t)(tile * p.splits + s) * V * 128 + row_in_tile) * 16);
+                            p.partial + (((size_t)c * 2 + slot) * V * 128 + row_in_tile) * 16);
 #pragma unroll
                         for (int v = 0; v < V; v++)
 #pragma unroll
@@ -351,18 +416,38 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
             }
             if (finish) {
                 const long long row = (p.tile0[0] + tile) * 128 + row_in_tile;
-                if (row >= p.valid_begin && row < p.valid_end) {
-                    const long long o0 = p.col + (row - p.valid_begin);
+                const bool row_ok = row >= p.valid_begin && row < p.valid_end;
+                const long long o0 = p.col + (row - p.valid_begin);
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        if (j < p.m) {
-                            float val = acc[0][j] * f0;
-                            if (SWIGLU) {
-                                const float u = acc[V - 1][j] * f1;
-                                val = val / (1.0f + __expf(-val)) * u;
-                            }
+                for (int j = 0; j < 16; j++) {
+                    if (j < p.m) {   // uniform across the warp
+                        float val = acc[0][j] * f0;
+                        if (SWIGLU) {
+                            const float u = acc[V - 1][j] * f1;
+                            val = val / (1.0f + __expf(-val)) * u;
+                        }
+                        if (row_ok) {
                             if (p.y) p.y[(long long)j * p.ld + o0] = val;
                             if (p.yb) p.yb[(long long)j * p.ld + o0] = bf16_bits(val);
+                        }
+                        if (p.q_codes) {
+                            // The same value as the next linear's NVFP4 input: sixteen consecutive
+                            // outputs of a token sit in sixteen consecutive lanes (the host side only
+                            // allows views that start on a scale tile and hold whole groups).
+                            const float vb = row_ok ? round_bf16(val) : 0.0f;
+                            float amax = fabsf(vb);
+#pragma unroll
+                            for (int off = 8; off >= 1; off >>= 1)
+                                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+                            const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(p.q_divisor, amax), 6.0f));
+                            const float q = sb ? __fdiv_rn(__fmul_rn(vb, p.q_divisor), e4m3_to_f32(sb)) : 0.0f;
+                            const float qn = __shfl_down_sync(0xffffffffu, q, 1);
+                            if (row_ok) {
+                                if ((lane & 1) == 0)
+                                    p.q_codes[((long long)j * p.q_ld + o0) / 2] = (uint8_t)f32x2_to_e2m1x2(q, qn);
+                                if ((lane & 15) == 0)
+                                    p.q_atoms[nvfp4_scale_offset(j, o0 / 16, p.q_ld)] = (uint8_t)sb;
+                            }
                         }
                     }
                 }
@@ -459,6 +544,15 @@ int gemv_nvfp4_tc(const LinearArgs& a, float divisor) {
     p.col = a.col;
     p.status = gemv_tc_status_ptr();
     if (!p.status) return VELOX_ERR_UNSUPPORTED;
+    if (a.qo_codes) {
+        // whole 16-wide groups of whole rows of the quantised matrix, starting at column 0
+        if (!a.qo_atoms || !(a.qo_divisor > 0.0f) || a.col != 0 || w.row_begin % 128 != 0 || w.rows % 64 != 0 || a.y)
+            return VELOX_ERR_UNSUPPORTED;
+        p.q_codes = a.qo_codes;
+        p.q_atoms = a.qo_atoms;
+        p.q_divisor = a.qo_divisor;
+        p.q_ld = w.rows;
+    }
 
     static int sms = 0;
     if (sms == 0) {
@@ -467,29 +561,15 @@ int gemv_nvfp4_tc(const LinearArgs& a, float divisor) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
-    // K splits: the fewest that keep the SMs' last round of items at least 85% full (else the
-    // fullest), each split at least four k-blocks long
+    // Equal runs of (tile, k-block) steps per CTA, at least two steps each.
+    const long long total_steps = (long long)p.tiles * p.k_blocks;
+    long long grid_l = total_steps / 2 < 1 ? 1 : total_steps / 2;
+    if (grid_l > sms) grid_l = sms;
+    p.per_cta = (total_steps + grid_l - 1) / grid_l;
+    const int grid = (int)((total_steps + p.per_cta - 1) / p.per_cta);
     {
-        int best = 1;
-        double best_eff = 0.0;
-        const int max_splits = p.k_blocks / 4 < 1 ? 1 : (p.k_blocks / 4 > 16 ? 16 : p.k_blocks / 4);
-        for (int s = 1; s <= max_splits; s++) {
-            const long long items = (long long)p.tiles * s;
-            const long long rounds = (items + sms - 1) / sms;
-            const double eff = (double)items / (double)(rounds * sms);
-            if (eff > best_eff + 0.02) {
-                best_eff = eff;
-                best = s;
-            }
-            if (eff >= 0.85) break;
-        }
-        p.splits = best;
-        if (const char* e = getenv("VELOX_SM100_DECODE_SPLITS")) p.splits = atoi(e) > 0 ? atoi(e) : p.splits;
-        if (p.splits > p.k_blocks) p.splits = p.k_blocks;
-    }
-    if (p.splits > 1) {
-        const size_t per_item = (size_t)(sw ? 2 : 1) * 128 * 16 * sizeof(float);
-        p.partial = static_cast<float*>(scratch(SCRATCH_Y_F32, (size_t)p.tiles * p.splits * per_item));
+        const size_t per_slot = (size_t)(sw ? 2 : 1) * 128 * 16 * sizeof(float);
+        p.partial = static_cast<float*>(scratch(SCRATCH_Y_F32, (size_t)grid * 2 * per_slot));
         p.tickets = gemv_tc_tickets((size_t)p.tiles);
         if (!p.partial || !p.tickets) return (int)cudaErrorMemoryAllocation;
     }
@@ -499,21 +579,34 @@ int gemv_nvfp4_tc(const LinearArgs& a, float divisor) {
     if ((rc = gemm_make_map_u8(&mw1, u.w, u.n, k / 2, 128)) != 0) return rc;
     if ((rc = gemm_make_map_u8(&mx, codes, a.m, k / 2, 16)) != 0) return rc;
 
-    const long long items = (long long)p.tiles * p.splits;
-    const int grid = (int)(items < sms ? items : sms);
     cudaError_t e;
     TimedRegion timed(TIMED_GEMV);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(DT_THREADS);
+    cfg.dynamicSmemBytes = DT_SMEM_BYTES;
+    cfg.stream = stream();
+    // Early start: this kernel's CTAs may become resident while the kernel before it in the
+    // stream is still finishing; they fetch weights, and wait for that kernel before touching
+    // anything it wrote (grid_dependency_wait in the producers).
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
+    cfg.attrs = attr;
+    cfg.numAttrs = early ? 1 : 0;
     if (sw) {
         auto kern = gemv_nvfp4_tc_kernel<true>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, DT_THREADS, DT_SMEM_BYTES, stream()>>>(mw0, mw1, mx, p);
+        e = cudaLaunchKernelEx(&cfg, kern, mw0, mw1, mx, p);
     } else {
         auto kern = gemv_nvfp4_tc_kernel<false>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, DT_THREADS, DT_SMEM_BYTES, stream()>>>(mw0, mw1, mx, p);
+        e = cudaLaunchKernelEx(&cfg, kern, mw0, mw1, mx, p);
     }
+    if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
 

@@ -177,10 +177,10 @@ class LinearStack:
         launches0 = b.launch_count()
         self.x[: m * h].copy_(xb_in.reshape(-1)[: m * h])
         first = True
-        # the norm hands the FP4 linears their quantised input directly; at prefill sizes the
-        # linears that feed another linear also emit its FP4 input from their epilogue
+        # the norm hands the FP4 linears their quantised input directly, and the linears that feed
+        # another linear emit its FP4 input from their epilogue
         q4 = self.a4 and b.linear_act(self.layers[0].q, m).kind == ActQuant.NVFP4
-        emit = q4 and m > 16
+        emit = q4
         for l in self.layers:
             # x (+= previous down partial), h = rms_norm(x)
             if q4:
