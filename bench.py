@@ -341,7 +341,7 @@ def main():
     else:
         k_ms, k_n = timed["gemv"]
         achieved = per_rank_bytes * args.steps / (k_ms * 1e-3) / 1e9 if k_ms > 0 else 0.0
-        roofline = {"bound": "hbm", "kernel": "gemv_kernel<nvfp4>", "achieved": achieved,
+        roofline = {"bound": "hbm", "kernel": "gemv_nvfp4_tc_kernel (tcgen05 block-scaled decode)", "achieved": achieved,
                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                     "peak_source": f"{peaks['source']} copy bandwidth",
                     "frac_of_nominal_hbm": achieved / NOMINAL_HBM_GBS,
@@ -350,7 +350,7 @@ def main():
     line = {
         "metric": METRIC, "value": m / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 accumulate (bf16 in/out)" if m > 16 else "nvfp4 x bf16 -> f32",
+        "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 accumulate (bf16 in/out)",
         "data": "synthetic", "config": workload_config(args, spec, m),
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
@@ -389,19 +389,27 @@ def components(b, peaks, graph=True):
     out = {}
     payload = WeightFormat.NVFP4.payload_bytes(n, k)
     stream = torch.cuda.Stream()
-    for m in (1, 2048):
+    for m, twin in ((1, False), (1, True), (2048, False)):
         xb = torch.randn(m, k, device=b.device).to(torch.bfloat16)
         yb = torch.empty(m, n, dtype=torch.bfloat16, device=b.device)
         rounds = 5 if m == 1 else 2
+        if twin:
+            # the FP4 activation twin a norm or a producing linear hands over: no quantiser launch
+            q4 = b.q4_blob(m, k)
+            b.add_rms_norm_q4(xb.float().reshape(-1).contiguous(), None, torch.ones(k, device=b.device), None, q4,
+                              m, k, 1e-6, 256.0)
+            call = lambda v: b.linear_q4(q4, 256.0, v, None, m, yb=yb)
+        else:
+            call = lambda v: b.linear_bf16(xb, v, None, m, yb=yb)
         with torch.cuda.stream(stream):
             for v in views:
-                b.linear_bf16(xb, v, None, m, yb=yb)
+                call(v)
         torch.cuda.synchronize()
         # replayed as one CUDA graph so that host launch latency is not in the measurement
         def burst():
             for _ in range(rounds):
                 for v in views:
-                    b.linear_bf16(xb, v, None, m, yb=yb)
+                    call(v)
         replay = burst
         if graph:
             g = torch.cuda.CUDAGraph()
@@ -420,10 +428,13 @@ def components(b, peaks, graph=True):
         if m == 1:
             byts = payload + 2 * m * k + 2 * m * n
             gbs = byts / (us * 1e-6) / 1e9
-            out["decode_gemv_m1"] = {"us_per_launch": us, "GB/s": gbs, "bytes": byts,
-                                     "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                                     "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
-                                     "timing": "CUDA-graph replay of 30 launches over 6 rotated weight copies"}
+            out["decode_gemv_m1_fp4_twin_in" if twin else "decode_gemv_m1"] = {
+                "us_per_launch": us, "GB/s": gbs, "bytes": byts,
+                "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS,
+                "timing": "CUDA-graph replay of 30 launches over 6 rotated weight copies"
+                          + ("; input is the NVFP4 blob a producer wrote" if twin
+                             else "; bf16 input, includes the activation quantiser launch")}
         else:
             tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
             out["prefill_gemm_m2048"] = {"us_per_launch": us, "TFLOP/s": tf,

@@ -221,7 +221,12 @@ def test_norm_emits_the_nvfp4_blob_the_quantiser_would(b, m, dim, addend):
     b.add_rms_norm_q4(acc, x, b.upload(w), yb, q4, m, dim, 1e-6, div, xb=xb)
     b.add_rms_norm_twin(acc_ref, x, b.upload(w), None, yb_ref, m, dim, 1e-6, xb=xb)
     assert torch.equal(acc, acc_ref)
-    assert np.array_equal(bf16_bits(yb), bf16_bits(yb_ref))
+    # the two kernels add the squares in different orders: the norm may differ in the last f32 bit,
+    # the bf16 twin by at most one unit in the last place
+    d = np.abs(bf16_bits(yb).astype(np.int32) - bf16_bits(yb_ref).astype(np.int32))
+    assert d.max() <= 1 and np.mean(d != 0) < 0.01
+    want = O.rms_norm(acc.cpu().numpy().reshape(m, dim), w, 1e-6)
+    assert O.max_err(yb.float().cpu().numpy(), want) <= 2.0 ** -8
     twin = yb.float().cpu().numpy().reshape(m, dim)
     wc, ws = O.act_codes_nvfp4(twin, div)
     assert np.array_equal(q4[0].cpu().numpy().reshape(m, dim // 2), wc)

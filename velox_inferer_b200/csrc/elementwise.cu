@@ -152,12 +152,113 @@ add_rms_norm_q4_kernel(float* __restrict__ acc, const float* __restrict__ x, con
     }
 }
 
+// The same for rows of at most ITERS * 1024 values, kept in registers between the two passes: a
+// thread owns four consecutive values per 1024-wide slice (coalesced 128-bit accesses), four
+// neighbouring lanes own a 16-wide scale group, and the quotients use the Markstein sequence
+// (q0 = a*r, q = fma(fma(-q0, d, a), r, q0), the correctly rounded a / d for r = rn(1 / d)), so the
+// bytes written are those of the kernel above.
+template <int ITERS>
+__global__ void __launch_bounds__(256)
+add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x, const uint16_t* __restrict__ xb,
+                            const float* __restrict__ weight, uint16_t* __restrict__ yb,
+                            uint8_t* __restrict__ codes, uint8_t* __restrict__ atoms, int rows, int dim, float eps,
+                            float offset, float divisor) {
+    __shared__ float red[8];
+    const long long row = blockIdx.x;
+    if (threadIdx.x == 0) grid_launch_dependents();   // a decode linear behind this may start fetching weights
+    if (row >= rows) {
+        for (int g = threadIdx.x; g < dim / 16; g += blockDim.x) atoms[nvfp4_scale_offset(row, g, dim)] = 0;
+        return;
+    }
+    const long long base = row * dim;
+    float4 v[ITERS];
+    float ss = 0.0f;
+#pragma unroll
+    for (int it = 0; it < ITERS; it++) {
+        const int c = (it * 256 + (int)threadIdx.x) * 4;
+        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (c < dim) {
+            a = *reinterpret_cast<const float4*>(acc + base + c);
+            if (x) {
+                const float4 b = *reinterpret_cast<const float4*>(x + base + c);
+                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+                *reinterpret_cast<float4*>(acc + base + c) = a;
+            } else if (xb) {
+                const uint2 b = *reinterpret_cast<const uint2*>(xb + base + c);
+                a.x += __uint_as_float(b.x << 16); a.y += __uint_as_float(b.x & 0xffff0000u);
+                a.z += __uint_as_float(b.y << 16); a.w += __uint_as_float(b.y & 0xffff0000u);
+                *reinterpret_cast<float4*>(acc + base + c) = a;
+            }
+        }
+        v[it] = a;
+        // the order of the reference's running sum does not survive any parallel reduction; this
+        // one matches add_rms_norm_twin's up to the f32 rounding of the partial sums
+        ss = fmaf(a.x, a.x, ss); ss = fmaf(a.y, a.y, ss); ss = fmaf(a.z, a.z, ss); ss = fmaf(a.w, a.w, ss);
+    }
+    ss = warp_sum(ss);
+    if (threadIdx.x % VX_WARP == 0) red[threadIdx.x / VX_WARP] = ss;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += red[i];
+    const float inv = 1.0f / sqrtf(total / (float)dim + eps);
+#pragma unroll
+    for (int it = 0; it < ITERS; it++) {
+        const int c = (it * 256 + (int)threadIdx.x) * 4;
+        const bool in = c < dim;
+        float n[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (in) {
+            const float4 w = *reinterpret_cast<const float4*>(weight + c);
+            n[0] = round_bf16(v[it].x * inv * (offset + w.x));
+            n[1] = round_bf16(v[it].y * inv * (offset + w.y));
+            n[2] = round_bf16(v[it].z * inv * (offset + w.z));
+            n[3] = round_bf16(v[it].w * inv * (offset + w.w));
+            if (yb)
+                *reinterpret_cast<uint2*>(yb + base + c) =
+                    make_uint2((__float_as_uint(n[0]) >> 16) | (__float_as_uint(n[1]) & 0xffff0000u),
+                               (__float_as_uint(n[2]) >> 16) | (__float_as_uint(n[3]) & 0xffff0000u));
+        }
+        float amax = fmaxf(fmaxf(fabsf(n[0]), fabsf(n[1])), fmaxf(fabsf(n[2]), fabsf(n[3])));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(divisor, amax), 6.0f));
+        uint32_t out = 0;
+        if (sb != 0) {
+            const float ds = e4m3_to_f32(sb);
+            const float rc = __frcp_rn(ds);
+            float q[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float a = __fmul_rn(n[i], divisor);
+                const float q0 = __fmul_rn(a, rc);
+                q[i] = __fmaf_rn(__fmaf_rn(-q0, ds, a), rc, q0);
+            }
+            out = f32x2_to_e2m1x2(q[0], q[1]) | (f32x2_to_e2m1x2(q[2], q[3]) << 8);
+        }
+        if (in) {
+            *reinterpret_cast<uint16_t*>(codes + (base + c) / 2) = (uint16_t)out;
+            if ((threadIdx.x & 3) == 0) atoms[nvfp4_scale_offset(row, c / 16, dim)] = (uint8_t)sb;
+        }
+    }
+}
+
 int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float* weight, uint16_t* yb,
                     uint8_t* codes, uint8_t* atoms, int rows, int dim, float eps, int offset, float divisor) {
     if (rows < 1 || dim < 64 || dim % 64 != 0 || !(divisor > 0.0f)) return VELOX_ERR_SHAPE;
     const int rows_padded = (rows + 127) / 128 * 128;
-    add_rms_norm_q4_kernel<<<(unsigned)rows_padded, 256, 0, stream()>>>(acc, x, xb, weight, yb, codes, atoms, rows,
-                                                                         dim, eps, offset ? 1.0f : 0.0f, divisor);
+    const float off = offset ? 1.0f : 0.0f;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(x) |
+                           reinterpret_cast<uintptr_t>(weight)) & 15) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(xb) | reinterpret_cast<uintptr_t>(yb)) & 7) == 0;
+    if (aligned && dim <= 2048)
+        add_rms_norm_q4_rows_kernel<2><<<(unsigned)rows_padded, 256, 0, stream()>>>(acc, x, xb, weight, yb, codes, atoms,
+                                                                                    rows, dim, eps, off, divisor);
+    else if (aligned && dim <= 8192)
+        add_rms_norm_q4_rows_kernel<8><<<(unsigned)rows_padded, 256, 0, stream()>>>(acc, x, xb, weight, yb, codes, atoms,
+                                                                                    rows, dim, eps, off, divisor);
+    else
+        add_rms_norm_q4_kernel<<<(unsigned)rows_padded, 256, 0, stream()>>>(acc, x, xb, weight, yb, codes, atoms, rows,
+                                                                             dim, eps, off, divisor);
     return launch_status();
 }
 
