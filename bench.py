@@ -152,20 +152,23 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * m / tok_s,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64 accumulate over NVFP4",
         "data": "synthetic",
-        "config": workload_config(args, spec, m),
+        "config": workload_config(args, spec, m, args.gpus > 1 and args.tp == "fused"),
         "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(args, spec, m):
+def workload_config(args, spec, m, fused_tp=False):
     return {"workload": f"{spec.layers}-layer NVFP4 linear stack (hidden {spec.hidden}, q {spec.q_dim}, kv {spec.kv_dim}, "
                         f"intermediate {spec.intermediate}), M={m}, attention = passthrough of q",
             "tokens_per_step": m, "layers": spec.layers,
-            "parallelism": f"tp{args.gpus}: column-split q/k/v/gate/up, row-split o/down, bf16 all-reduce after o and down",
-            "activations": "bf16 in HBM; NVFP4 tensor-core operands (ActQuant::Nvfp4, per-use divisors 256/128/16)"
-                           if m > 16 else "bf16 (ActQuant::Bf16)",
+            "parallelism": f"tp{args.gpus}: column-split q/k/v/gate/up, row-split o/down, "
+                           + ("bf16 partial tiles stored into the owning rank's rows by the GEMM epilogue over NVLink "
+                              "(reduce-scatter), NVFP4 norm output stored into every rank (all-gather), "
+                              "signal-pad barriers" if fused_tp else "bf16 all-reduce (NCCL) after o and down"),
+            "activations": "NVFP4 tensor-core operands written by the producing kernels (ActQuant::Nvfp4, "
+                           "per-use divisors 256/128/16); f32 residual stream; bf16 step input and output",
             "l2": "each step streams the layers' distinct weights, far larger than the 126 MB L2"}
 
 
@@ -182,6 +185,9 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-components", action="store_true", help="skip the single-linear GEMV / GEMM lines")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp", choices=("fused", "nccl"), default="nccl",
+                    help="N > 1: communication fused into the GEMM epilogue and the norm over symmetric memory, "
+                         "or one NCCL all-reduce after o and down")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
@@ -225,32 +231,40 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    fused_tp = False
+    if world > 1 and args.tp == "fused":
+        try:
+            fused_tp = stack.enable_fused_tp(m)
+        except Exception as exc:  # symmetric memory not available here: the NCCL step still is
+            print(f"[bench] fused tensor parallelism not available ({exc}); using NCCL all-reduce",
+                  file=sys.stderr, flush=True)
+    forward = (lambda: stack.forward_fused_tp(x_dev)) if fused_tp else (lambda: stack.forward(x_dev, m))
     for _ in range(max(args.warmup, 3)):
-        stack.forward(x_dev, m)
+        forward()
     barrier()
 
     # A step is hundreds of launches (and, with several ranks, two all-reduces per layer): it is
     # captured once and replayed as one CUDA graph, as the reference runs its step
     # (crates/velox-cuda/src/lib.rs:2130-2204), unless --no-graph is given or capture fails. Event
     # timing of single kernels is not possible inside a graph, so the roofline pass runs eagerly.
-    step = lambda: stack.forward(x_dev, m)
+    step = forward
     use_graph = not args.no_graph
     if use_graph:
         try:
             side = torch.cuda.Stream()
             with torch.cuda.stream(side):
-                stack.forward(x_dev, m)
+                forward()
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
-                stack.forward(x_dev, m)
+                forward()
             step = graph.replay
             for _ in range(3):
                 step()
         except Exception as exc:  # capture not possible here: time eager launches instead
             print(f"[bench] CUDA graph capture failed ({exc}); launching eagerly", file=sys.stderr, flush=True)
             use_graph = False
-            step = lambda: stack.forward(x_dev, m)
+            step = forward
         barrier()
     if b.lib.velox_sm100_debug_status() != 0:
         raise SystemExit("tensor-core kernel reported a timed-out wait")
@@ -281,7 +295,7 @@ def main():
     b.timing_enable(True)
     barrier()
     for _ in range(args.steps):
-        stack.forward(x_dev, m)
+        forward()
     barrier()
     timed = b.timing_collect()
     b.timing_enable(False)
@@ -294,9 +308,9 @@ def main():
         x_dev.copy_(x_host, non_blocking=True)
         if use_graph:
             step()
-            out = stack.outb
+            out = stack.fabric.out if fused_tp else stack.outb
         else:
-            out = stack.forward(x_dev, m)
+            out = forward()
         y_host.copy_(out[: m * spec.hidden].view(m, spec.hidden), non_blocking=True)
     e1.record()
     barrier()
@@ -351,7 +365,7 @@ def main():
         "metric": METRIC, "value": m / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 accumulate (bf16 in/out)",
-        "data": "synthetic", "config": workload_config(args, spec, m),
+        "data": "synthetic", "config": workload_config(args, spec, m, fused_tp),
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
         "gpu_launches": int(launches), "cuda_graph": bool(use_graph), "clocks": clocks, "roofline": roofline,

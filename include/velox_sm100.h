@@ -231,6 +231,30 @@ int velox_sm100_linear_swiglu_q4_to_q4(const uint8_t* codes, const uint8_t* atom
                                        uint16_t* outb, uint8_t* out_codes, uint8_t* out_atoms,
                                        float out_divisor);
 
+/* Tensor parallelism over one node (no counterpart in the reference, which is single-device).
+ * Token rows are owned by ranks in equal blocks of `rows_per_owner` (a multiple of 128). Buffers
+ * named "_ptrs" are arrays, one entry per rank, of device addresses valid on the calling GPU
+ * (peer mappings of symmetric allocations); the caller orders the phases with its own barriers.
+ *  - velox_sm100_tp_make_maps: output maps for a row-split linear. slot_ptrs[o] is this rank's
+ *    [rows_per_owner, cols] bf16 slot in rank o's memory; maps_dev receives n x 128 bytes.
+ *  - velox_sm100_tp_linear_q4_scatter: linear_q4 whose bf16 result tiles are stored by the GEMM
+ *    epilogue straight into the owners' slots (the reduce-scatter's data movement, fused into the
+ *    linear). The view must be a whole parent with a multiple of 256 rows, m a multiple of
+ *    rows_per_owner, m > 16.
+ *  - velox_sm100_tp_norm_q4: acc (this rank's rows, f32) += the nslots slots in order; rms norm;
+ *    the result as NVFP4 codes and scale atoms at rows row0.. of every rank's blob (the
+ *    all-gather, fused into the norm). nslots = 0: no addend.
+ *  - velox_sm100_tp_finish: acc += the slots; acc as bf16 at rows row0.. of every rank's output. */
+int velox_sm100_tp_make_maps(void* maps_dev, const unsigned long long* slot_ptrs, int n, int rows_per_owner,
+                             long long cols);
+int velox_sm100_tp_linear_q4_scatter(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                                     const velox_sm100_view* view, int m, const void* maps_dev, int rows_per_owner);
+int velox_sm100_tp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
+                           const unsigned long long* codes_ptrs, const unsigned long long* atoms_ptrs, int ndst,
+                           long long row0, int rows, int dim, float eps, int offset, float divisor);
+int velox_sm100_tp_finish(float* acc, const uint16_t* slots, int nslots, long long slot_stride,
+                          const unsigned long long* out_ptrs, int ndst, long long row0, int rows, int dim);
+
 /* The same with a bf16 addend (the all-reduced partial sums of a row-split projection): acc += xb,
  * then the norm. No counterpart in the reference, which has no tensor parallelism. */
 int velox_sm100_add_bf16_rms_norm_twin(float* acc, const uint16_t* xb, const float* weight, float* y,

@@ -53,6 +53,10 @@ SIGNATURES = {
     "velox_sm100_add_rms_norm_q4": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _F, _I, _F]),
     "velox_sm100_linear_q4": (_I, [_VP, _VP, _F, _PV, _I, _VP, _VP]),
     "velox_sm100_linear_swiglu_q4": (_I, [_VP, _VP, _F, _PV, _PV, _I, _VP, _VP]),
+    "velox_sm100_tp_make_maps": (_I, [_VP, _VP, _I, _I, _LL]),
+    "velox_sm100_tp_linear_q4_scatter": (_I, [_VP, _VP, _F, _PV, _I, _VP, _I]),
+    "velox_sm100_tp_norm_q4": (_I, [_VP, _VP, _I, _LL, _VP, _VP, _VP, _I, _LL, _I, _I, _F, _I, _F]),
+    "velox_sm100_tp_finish": (_I, [_VP, _VP, _I, _LL, _VP, _I, _LL, _I, _I]),
     "velox_sm100_linear_q4_to_q4": (_I, [_VP, _VP, _F, _PV, _I, _VP, _VP, _VP, _F]),
     "velox_sm100_linear_swiglu_q4_to_q4": (_I, [_VP, _VP, _F, _PV, _PV, _I, _VP, _VP, _VP, _F]),
     "velox_sm100_linear_act": (_I, [_PV, _I, C.POINTER(C.c_float)]),

@@ -282,6 +282,34 @@ class Sm100Backend:
             q4[0].data_ptr(), q4[1].data_ptr(), divisor, C.byref(_view_struct(gate)), C.byref(_view_struct(up)), m,
             _ptr(outb), out_q4[0].data_ptr(), out_q4[1].data_ptr(), out_divisor), "sm100 linear_swiglu_q4_to_q4")
 
+    # -- tensor parallelism: reduce-scatter fused into the row-split linear, all-gather into the norm
+    def tp_make_maps(self, maps_dev: torch.Tensor, slot_ptrs, rows_per_owner: int, cols: int) -> None:
+        self._bind()
+        arr = (C.c_uint64 * len(slot_ptrs))(*slot_ptrs)
+        status(self.lib.velox_sm100_tp_make_maps(maps_dev.data_ptr(), arr, len(slot_ptrs), rows_per_owner, cols),
+               "sm100 tp_make_maps")
+
+    def tp_linear_q4_scatter(self, q4, divisor: float, w: WeightView, m: int, maps_dev: torch.Tensor,
+                             rows_per_owner: int) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_tp_linear_q4_scatter(q4[0].data_ptr(), q4[1].data_ptr(), divisor,
+                                                         C.byref(_view_struct(w)), m, maps_dev.data_ptr(),
+                                                         rows_per_owner), "sm100 tp_linear_q4_scatter")
+
+    def tp_norm_q4(self, acc, slots, nslots: int, slot_stride: int, weight, codes_ptrs, atoms_ptrs, row0: int,
+                   rows: int, dim: int, eps: float, divisor: float, offset=False) -> None:
+        self._bind()
+        n = len(codes_ptrs)
+        status(self.lib.velox_sm100_tp_norm_q4(acc.data_ptr(), _ptr(slots), nslots, slot_stride, weight.data_ptr(),
+                                               (C.c_uint64 * n)(*codes_ptrs), (C.c_uint64 * n)(*atoms_ptrs), n, row0,
+                                               rows, dim, eps, 1 if offset else 0, divisor), "sm100 tp_norm_q4")
+
+    def tp_finish(self, acc, slots, nslots: int, slot_stride: int, out_ptrs, row0: int, rows: int, dim: int) -> None:
+        self._bind()
+        n = len(out_ptrs)
+        status(self.lib.velox_sm100_tp_finish(acc.data_ptr(), slots.data_ptr(), nslots, slot_stride,
+                                              (C.c_uint64 * n)(*out_ptrs), n, row0, rows, dim), "sm100 tp_finish")
+
     def add_bf16(self, acc, xb, n) -> None:
         self._bind()
         status(self.lib.velox_sm100_add_bf16(acc.data_ptr(), xb.data_ptr(), n), "sm100 add_bf16")

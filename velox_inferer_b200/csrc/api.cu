@@ -177,8 +177,9 @@ static int run(const LinearArgs& a, const Plan& p) {
 static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_view* view, int m,
                          float* y, uint16_t* yb, long long ld, long long col,
                          const uint8_t* q_codes = nullptr, const uint8_t* q_atoms = nullptr,
-                         uint8_t* qo_codes = nullptr, uint8_t* qo_atoms = nullptr, float qo_divisor = 0.0f) {
-    if (m <= 0 || (!x && !xb && !q_codes) || (!y && !yb && !qo_codes)) return VELOX_ERR_SHAPE;
+                         uint8_t* qo_codes = nullptr, uint8_t* qo_atoms = nullptr, float qo_divisor = 0.0f,
+                         const void* rs_maps = nullptr, int rs_rows = 0) {
+    if (m <= 0 || (!x && !xb && !q_codes) || (!y && !yb && !qo_codes && !rs_maps)) return VELOX_ERR_SHAPE;
     int rc = check_view(view);
     if (rc != 0) return rc;
     LinearArgs a{};
@@ -196,7 +197,10 @@ static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.qo_codes = qo_codes;
     a.qo_atoms = qo_atoms;
     a.qo_divisor = qo_divisor;
+    a.rs_maps = rs_maps;
+    a.rs_rows_per_owner = rs_rows;
     const Plan p = plan_for(*view, m);
+    if (rs_maps && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
     // pre-quantised input: the FP4 tensor-core paths only; and quantised output: the FP4 tensor-core paths only
     if (q_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
     if (qo_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
@@ -467,6 +471,44 @@ int velox_sm100_linear_swiglu_q4_to_q4(const uint8_t* codes, const uint8_t* atom
         return VELOX_ERR_UNSUPPORTED;
     return swiglu_common(nullptr, nullptr, gate, up, m, nullptr, outb, codes, atoms, out_codes, out_atoms,
                          out_divisor);
+}
+
+int velox_sm100_tp_make_maps(void* maps_dev, const unsigned long long* slot_ptrs, int n, int rows_per_owner,
+                             long long cols) {
+    return gemm_make_rs_maps(maps_dev, slot_ptrs, n, rows_per_owner, cols);
+}
+
+int velox_sm100_tp_linear_q4_scatter(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                                     const velox_sm100_view* view, int m, const void* maps_dev, int rows_per_owner) {
+    if (!view || !codes || !atoms || !maps_dev) return VELOX_ERR_SHAPE;
+    if (view->policy != VELOX_POLICY_ALLOW_A4 || view->divisor != divisor) return VELOX_ERR_UNSUPPORTED;
+    return linear_common(nullptr, nullptr, view, m, nullptr, nullptr, view->rows, 0, codes, atoms, nullptr, nullptr,
+                         0.0f, maps_dev, rows_per_owner);
+}
+
+int velox_sm100_tp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
+                           const unsigned long long* codes_ptrs, const unsigned long long* atoms_ptrs, int ndst,
+                           long long row0, int rows, int dim, float eps, int offset, float divisor) {
+    if (!acc || !weight || !codes_ptrs || !atoms_ptrs || ndst < 1 || ndst > VX_MAX_PEERS) return VELOX_ERR_SHAPE;
+    uint8_t* c[VX_MAX_PEERS];
+    uint8_t* s[VX_MAX_PEERS];
+    for (int d = 0; d < ndst; d++) {
+        c[d] = reinterpret_cast<uint8_t*>(codes_ptrs[d]);
+        s[d] = reinterpret_cast<uint8_t*>(atoms_ptrs[d]);
+        if (!c[d] || !s[d]) return VELOX_ERR_SHAPE;
+    }
+    return sp_norm_q4(acc, slots, nslots, slot_stride, weight, c, s, ndst, row0, rows, dim, eps, offset, divisor);
+}
+
+int velox_sm100_tp_finish(float* acc, const uint16_t* slots, int nslots, long long slot_stride,
+                          const unsigned long long* out_ptrs, int ndst, long long row0, int rows, int dim) {
+    if (!acc || !slots || !out_ptrs || ndst < 1 || ndst > VX_MAX_PEERS) return VELOX_ERR_SHAPE;
+    uint16_t* o[VX_MAX_PEERS];
+    for (int d = 0; d < ndst; d++) {
+        o[d] = reinterpret_cast<uint16_t*>(out_ptrs[d]);
+        if (!o[d]) return VELOX_ERR_SHAPE;
+    }
+    return sp_finish(acc, slots, nslots, slot_stride, o, ndst, row0, rows, dim);
 }
 
 int velox_sm100_add_bf16(float* acc, const uint16_t* xb, long long len) {

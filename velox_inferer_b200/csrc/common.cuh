@@ -50,6 +50,8 @@ __device__ __forceinline__ void grid_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+constexpr int VX_MAX_PEERS = 8;   // ranks of a tensor-parallel group one kernel can store to
+
 // f32 -> E4M3 byte and two f32 -> one byte of E2M1 codes (the first in the low nibble): the
 // hardware's round-to-nearest-even, saturating conversions.
 __device__ __forceinline__ uint32_t f32_to_e4m3(float v) {

@@ -152,22 +152,35 @@ add_rms_norm_q4_kernel(float* __restrict__ acc, const float* __restrict__ x, con
     }
 }
 
+// Where the norm's NVFP4 output goes: one blob, or the same rows of the blob on every rank of a
+// tensor-parallel group (peer pointers into symmetric memory; plain stores over NVLink).
+struct Q4Dest {
+    uint8_t* codes[VX_MAX_PEERS];
+    uint8_t* atoms[VX_MAX_PEERS];
+    int n;
+};
+
 // The same for rows of at most ITERS * 1024 values, kept in registers between the two passes: a
 // thread owns four consecutive values per 1024-wide slice (coalesced 128-bit accesses), four
 // neighbouring lanes own a 16-wide scale group, and the quotients use the Markstein sequence
 // (q0 = a*r, q = fma(fma(-q0, d, a), r, q0), the correctly rounded a / d for r = rn(1 / d)), so the
 // bytes written are those of the kernel above.
+//
+// Sequence-parallel form: `acc` holds only this rank's rows; the addend is the sum, in slot order,
+// of `nslots` bf16 partial-sum slots (one per source rank, `slot_stride` values apart), and the
+// output row lands at row `row0 + row` of every destination blob.
 template <int ITERS>
 __global__ void __launch_bounds__(256)
 add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x, const uint16_t* __restrict__ xb,
-                            const float* __restrict__ weight, uint16_t* __restrict__ yb,
-                            uint8_t* __restrict__ codes, uint8_t* __restrict__ atoms, int rows, int dim, float eps,
-                            float offset, float divisor) {
+                            int nslots, long long slot_stride, const float* __restrict__ weight,
+                            uint16_t* __restrict__ yb, const Q4Dest dst, long long row0, int rows, int dim,
+                            float eps, float offset, float divisor) {
     __shared__ float red[8];
     const long long row = blockIdx.x;
     if (threadIdx.x == 0) grid_launch_dependents();   // a decode linear behind this may start fetching weights
     if (row >= rows) {
-        for (int g = threadIdx.x; g < dim / 16; g += blockDim.x) atoms[nvfp4_scale_offset(row, g, dim)] = 0;
+        for (int g = threadIdx.x; g < dim / 16; g += blockDim.x)
+            for (int d = 0; d < dst.n; d++) dst.atoms[d][nvfp4_scale_offset(row0 + row, g, dim)] = 0;
         return;
     }
     const long long base = row * dim;
@@ -184,9 +197,13 @@ add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x
                 a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
                 *reinterpret_cast<float4*>(acc + base + c) = a;
             } else if (xb) {
-                const uint2 b = *reinterpret_cast<const uint2*>(xb + base + c);
-                a.x += __uint_as_float(b.x << 16); a.y += __uint_as_float(b.x & 0xffff0000u);
-                a.z += __uint_as_float(b.y << 16); a.w += __uint_as_float(b.y & 0xffff0000u);
+                float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int sl = 0; sl < nslots; sl++) {
+                    const uint2 b = *reinterpret_cast<const uint2*>(xb + sl * slot_stride + base + c);
+                    t.x += __uint_as_float(b.x << 16); t.y += __uint_as_float(b.x & 0xffff0000u);
+                    t.z += __uint_as_float(b.y << 16); t.w += __uint_as_float(b.y & 0xffff0000u);
+                }
+                a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
                 *reinterpret_cast<float4*>(acc + base + c) = a;
             }
         }
@@ -202,6 +219,7 @@ add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x
 #pragma unroll
     for (int i = 0; i < 8; i++) total += red[i];
     const float inv = 1.0f / sqrtf(total / (float)dim + eps);
+    const long long obase = (row0 + row) * dim;
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
         const int c = (it * 256 + (int)threadIdx.x) * 4;
@@ -235,30 +253,101 @@ add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x
             }
             out = f32x2_to_e2m1x2(q[0], q[1]) | (f32x2_to_e2m1x2(q[2], q[3]) << 8);
         }
-        if (in) {
-            *reinterpret_cast<uint16_t*>(codes + (base + c) / 2) = (uint16_t)out;
-            if ((threadIdx.x & 3) == 0) atoms[nvfp4_scale_offset(row, c / 16, dim)] = (uint8_t)sb;
+        // two more shuffles gather a lane quad's four code bytes pairs so that one lane stores 8 bytes
+        const uint32_t o1 = __shfl_down_sync(0xffffffffu, out, 1);
+        const uint32_t o2 = __shfl_down_sync(0xffffffffu, out, 2);
+        const uint32_t o3 = __shfl_down_sync(0xffffffffu, out, 3);
+        if (in && (threadIdx.x & 3) == 0) {
+            const uint2 pk = make_uint2((out & 0xffffu) | (o1 << 16), (o2 & 0xffffu) | (o3 << 16));
+            const long long soff = nvfp4_scale_offset(row0 + row, c / 16, dim);
+            for (int d = 0; d < dst.n; d++) {
+                *reinterpret_cast<uint2*>(dst.codes[d] + (obase + c) / 2) = pk;
+                dst.atoms[d][soff] = (uint8_t)sb;
+            }
         }
     }
+}
+
+// x_own += sum of the slots, then the rows as bf16 to every destination (the last step of a
+// sequence-parallel stack: residual add and all-gather of the result in one pass).
+__global__ void __launch_bounds__(256)
+sp_finish_kernel(float* __restrict__ acc, const uint16_t* __restrict__ slots, int nslots, long long slot_stride,
+                 const Q4Dest dst, long long row0, long long len, int dim) {
+    for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < len;
+         i += (long long)gridDim.x * blockDim.x * 4) {
+        float4 a = *reinterpret_cast<const float4*>(acc + i);
+        float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int sl = 0; sl < nslots; sl++) {
+            const uint2 b = *reinterpret_cast<const uint2*>(slots + sl * slot_stride + i);
+            t.x += __uint_as_float(b.x << 16); t.y += __uint_as_float(b.x & 0xffff0000u);
+            t.z += __uint_as_float(b.y << 16); t.w += __uint_as_float(b.y & 0xffff0000u);
+        }
+        a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
+        *reinterpret_cast<float4*>(acc + i) = a;
+        const uint2 pk = make_uint2((uint32_t)bf16_bits(a.x) | ((uint32_t)bf16_bits(a.y) << 16),
+                                    (uint32_t)bf16_bits(a.z) | ((uint32_t)bf16_bits(a.w) << 16));
+        for (int d = 0; d < dst.n; d++)
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(dst.codes[d]) + row0 * dim + i) = pk;
+    }
+}
+
+static int launch_norm_q4(float* acc, const float* x, const uint16_t* xb, int nslots, long long slot_stride,
+                          const float* weight, uint16_t* yb, const Q4Dest& dst, long long row0, int rows,
+                          int rows_padded, int dim, float eps, int offset, float divisor) {
+    const float off = offset ? 1.0f : 0.0f;
+    if (dim <= 2048)
+        add_rms_norm_q4_rows_kernel<2><<<(unsigned)rows_padded, 256, 0, stream()>>>(
+            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor);
+    else
+        add_rms_norm_q4_rows_kernel<8><<<(unsigned)rows_padded, 256, 0, stream()>>>(
+            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor);
+    return launch_status();
 }
 
 int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float* weight, uint16_t* yb,
                     uint8_t* codes, uint8_t* atoms, int rows, int dim, float eps, int offset, float divisor) {
     if (rows < 1 || dim < 64 || dim % 64 != 0 || !(divisor > 0.0f)) return VELOX_ERR_SHAPE;
     const int rows_padded = (rows + 127) / 128 * 128;
-    const float off = offset ? 1.0f : 0.0f;
     const bool aligned = ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(x) |
                            reinterpret_cast<uintptr_t>(weight)) & 15) == 0 &&
-                         ((reinterpret_cast<uintptr_t>(xb) | reinterpret_cast<uintptr_t>(yb)) & 7) == 0;
-    if (aligned && dim <= 2048)
-        add_rms_norm_q4_rows_kernel<2><<<(unsigned)rows_padded, 256, 0, stream()>>>(acc, x, xb, weight, yb, codes, atoms,
-                                                                                    rows, dim, eps, off, divisor);
-    else if (aligned && dim <= 8192)
-        add_rms_norm_q4_rows_kernel<8><<<(unsigned)rows_padded, 256, 0, stream()>>>(acc, x, xb, weight, yb, codes, atoms,
-                                                                                    rows, dim, eps, off, divisor);
-    else
-        add_rms_norm_q4_kernel<<<(unsigned)rows_padded, 256, 0, stream()>>>(acc, x, xb, weight, yb, codes, atoms, rows,
-                                                                             dim, eps, off, divisor);
+                         ((reinterpret_cast<uintptr_t>(xb) | reinterpret_cast<uintptr_t>(yb) |
+                           reinterpret_cast<uintptr_t>(codes)) & 7) == 0;
+    if (aligned && dim <= 8192) {
+        Q4Dest dst{};
+        dst.codes[0] = codes;
+        dst.atoms[0] = atoms;
+        dst.n = 1;
+        return launch_norm_q4(acc, x, xb, 1, 0, weight, yb, dst, 0, rows, rows_padded, dim, eps, offset, divisor);
+    }
+    add_rms_norm_q4_kernel<<<(unsigned)rows_padded, 256, 0, stream()>>>(acc, x, xb, weight, yb, codes, atoms, rows,
+                                                                         dim, eps, offset ? 1.0f : 0.0f, divisor);
+    return launch_status();
+}
+
+int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
+               uint8_t* const* codes, uint8_t* const* atoms, int ndst, long long row0, int rows, int dim, float eps,
+               int offset, float divisor) {
+    if (rows < 1 || rows % 128 != 0 || row0 % 128 != 0 || dim < 64 || dim % 64 != 0 || dim > 8192 ||
+        !(divisor > 0.0f) || ndst < 1 || ndst > VX_MAX_PEERS || nslots < 0 || (nslots > 0 && !slots))
+        return VELOX_ERR_SHAPE;
+    Q4Dest dst{};
+    for (int d = 0; d < ndst; d++) {
+        dst.codes[d] = codes[d];
+        dst.atoms[d] = atoms[d];
+    }
+    dst.n = ndst;
+    return launch_norm_q4(acc, nullptr, nslots > 0 ? slots : nullptr, nslots, slot_stride, weight, nullptr, dst, row0,
+                          rows, rows, dim, eps, offset, divisor);
+}
+
+int sp_finish(float* acc, const uint16_t* slots, int nslots, long long slot_stride, uint16_t* const* out, int ndst,
+              long long row0, int rows, int dim) {
+    if (rows < 1 || dim % 4 != 0 || ndst < 1 || ndst > VX_MAX_PEERS || nslots < 1 || !slots) return VELOX_ERR_SHAPE;
+    Q4Dest dst{};
+    for (int d = 0; d < ndst; d++) dst.codes[d] = reinterpret_cast<uint8_t*>(out[d]);
+    dst.n = ndst;
+    const long long len = (long long)rows * dim;
+    sp_finish_kernel<<<grid_1d(len / 4, 256), 256, 0, stream()>>>(acc, slots, nslots, slot_stride, dst, row0, len, dim);
     return launch_status();
 }
 

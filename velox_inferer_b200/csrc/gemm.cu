@@ -100,6 +100,8 @@ struct GemmParams {
     uint16_t* yb;
     long long ld, col;
     int tma_store;  // bf16-only output that a tensor map over yb + col describes
+    const CUtensorMap* out_maps;   // optional (tensor parallel): one output map per owning rank, in global memory;
+    int rows_per_owner;            // token rows [o * rows_per_owner, (o + 1) * rows_per_owner) go to out_maps[o]
     uint8_t* q_codes;   // optional: the output also (or only) as NVFP4 activations, codes [m, q_ld / 2] ...
     uint8_t* q_atoms;   // ... and scale atoms over ceil(m / 128) * 128 rows
     float q_divisor;
@@ -620,8 +622,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
                     if (store_thread && any_token) {
-                        tma_store_2d(&tmap_out, my_box,
-                                     (int)(rbase[0] - p.out_row0) + (hsel * (MINE / 2) + bx) * 64, mt * BM);
+                        // tensor parallel: the tile goes straight into the buffer of the rank that owns
+                        // these token rows (a store over NVLink when that is not this rank)
+                        const CUtensorMap* omap = &tmap_out;
+                        int orow = mt * BM;
+                        if (p.out_maps) {
+                            const int owner = orow / p.rows_per_owner;
+                            omap = p.out_maps + owner;
+                            orow -= owner * p.rows_per_owner;
+                        }
+                        tma_store_2d(omap, my_box, (int)(rbase[0] - p.out_row0) + (hsel * (MINE / 2) + bx) * 64, orow);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 }
@@ -823,6 +833,28 @@ int gemm_make_map_u8(CUtensorMap* map, const void* ptr, long long rows, long lon
     return r == CUDA_SUCCESS ? 0 : VELOX_ERR_UNSUPPORTED;
 }
 
+// Output maps of a tensor-parallel row-split linear: map o covers the [rows_per_owner, cols] bf16
+// buffer at ptrs[o] (this rank's slot in rank o's memory). Encoded here, copied to `maps_dev`
+// (n x 128 bytes of device memory, 64-byte aligned) on the current stream.
+int gemm_make_rs_maps(void* maps_dev, const unsigned long long* ptrs, int n, int rows_per_owner, long long cols) {
+    if (!encode_fn() || n < 1 || n > VX_MAX_PEERS || !maps_dev || (reinterpret_cast<uintptr_t>(maps_dev) & 63))
+        return VELOX_ERR_UNSUPPORTED;
+    CUtensorMap maps[VX_MAX_PEERS];
+    for (int o = 0; o < n; o++) {
+        const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows_per_owner};
+        const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+        const cuuint32_t box[2] = {64u, 128u};
+        const cuuint32_t estr[2] = {1, 1};
+        if (encode_fn()(&maps[o], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, reinterpret_cast<void*>(ptrs[o]), dims, strides,
+                        box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return VELOX_ERR_UNSUPPORTED;
+    }
+    // pageable source: the copy has read `maps` by the time the call returns
+    cudaError_t e = cudaMemcpyAsync(maps_dev, maps, sizeof(CUtensorMap) * n, cudaMemcpyHostToDevice, stream());
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
 // Tensor map over the bf16 output columns [col, col + out_cols) of yb, for whole-tile stores.
 // Leaves p.tma_store at 0 when the output is not bf16-only or not 16-byte friendly.
 static void make_out_map(CUtensorMap* map, GemmParams& p, long long out_cols, long long first_row) {
@@ -887,7 +919,10 @@ template <int KIND>
 static int launch(bool swiglu, const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1,
                   GemmParams& p, long long out_cols, long long first_row) {
     CUtensorMap mo = a;
-    make_out_map(&mo, p, out_cols, first_row);
+    if (p.out_maps)
+        p.tma_store = 1;   // every tile is stored through the owner's map
+    else
+        make_out_map(&mo, p, out_cols, first_row);
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -990,6 +1025,14 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
             p.tiles_n = (int)((w.row_begin + w.rows - base0 + 255) / 256);
         }
         p.out_row0 = w.row_begin;
+        if (a.rs_maps) {
+            // whole tiles of whole rows into per-owner buffers: nothing ragged
+            if (a.y || a.yb || a.qo_codes || a.col != 0 || w.row_begin != 0 || w.rows % 256 != 0 ||
+                a.rs_rows_per_owner < 128 || a.rs_rows_per_owner % 128 != 0 || a.m % a.rs_rows_per_owner != 0)
+                return VELOX_ERR_UNSUPPORTED;
+            p.out_maps = static_cast<const CUtensorMap*>(a.rs_maps);
+            p.rows_per_owner = a.rs_rows_per_owner;
+        }
         if (a.qo_codes) {
             // whole 64-column pieces of whole rows of the quantised matrix, starting at column 0
             if (!a.qo_atoms || !(a.qo_divisor > 0.0f) || a.col != 0 || w.row_begin % 128 != 0 || w.rows % 64 != 0 ||

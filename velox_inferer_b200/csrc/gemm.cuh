@@ -20,6 +20,8 @@ int gemm_linear(const LinearArgs& a, int act, float divisor);
 // 128-byte swizzle.
 int gemm_make_map_u8(CUtensorMap* map, const void* ptr, long long rows, long long row_bytes, int box_rows);
 
+int gemm_make_rs_maps(void* maps_dev, const unsigned long long* ptrs, int n, int rows_per_owner, long long cols);
+
 // NVFP4 decode linear (m <= 16) on the block-scaled tensor cores, activations quantised to NVFP4
 // with `divisor` (or taken from a.q_codes / a.q_atoms). VELOX_ERR_UNSUPPORTED for other shapes.
 int gemv_nvfp4_tc(const LinearArgs& a, float divisor);

@@ -23,6 +23,8 @@ struct LinearArgs {
     uint8_t* qo_codes;       // optional: the result also (or only) as NVFP4 activations for the
     uint8_t* qo_atoms;       // next linear, quantised with qo_divisor (FP4 tensor-core path only)
     float qo_divisor;
+    const void* rs_maps;     // optional (tensor parallel): per-owner output maps in device memory, and
+    int rs_rows_per_owner;   // the token rows each owner holds; replaces y / yb
     long long ld;            // row stride of y / yb in elements
     long long col;           // first column written
 };
@@ -59,6 +61,11 @@ int add_bf16(float* acc, const uint16_t* xb, long long len);
 int add_rms_norm_twin(float* acc, const float* x, const uint16_t* xb, const float* weight, float* y,
                       uint16_t* yb, int rows, int dim, float eps, int offset);
 int bf16_twin(const float* x, uint16_t* xb, long long len);
+int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
+               uint8_t* const* codes, uint8_t* const* atoms, int ndst, long long row0, int rows, int dim, float eps,
+               int offset, float divisor);
+int sp_finish(float* acc, const uint16_t* slots, int nslots, long long slot_stride, uint16_t* const* out, int ndst,
+              long long row0, int rows, int dim);
 int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float* weight, uint16_t* yb,
                     uint8_t* codes, uint8_t* atoms, int rows, int dim, float eps, int offset, float divisor);
 

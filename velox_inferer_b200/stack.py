@@ -97,6 +97,47 @@ def slice_k_nvfp4(payload: torch.Tensor, n: int, k: int, k_begin: int, k_len: in
     return out
 
 
+class TpFabric:
+    """Symmetric memory of a tensor-parallel group for the fused scatter / gather path: on every
+    rank, one slot per source rank for bf16 partial sums of the rows this rank owns, the norm's
+    NVFP4 blob for all rows, and the final output. Peers' copies are mapped into this process
+    (torch symmetric memory: cuMem allocations exchanged once at set-up), so kernels store into
+    them with ordinary addresses; phases are separated by signal-pad barriers on the stream."""
+
+    def __init__(self, backend: Sm100Backend, group, rank: int, world: int, m: int, hidden: int):
+        import torch.distributed._symmetric_memory as symm
+
+        assert m % (world * 128) == 0
+        self.rank, self.world, self.m, self.hidden = rank, world, m, hidden
+        self.rows = m // world                               # token rows each rank owns
+        slots_b, codes_b = world * self.rows * hidden * 2, m * hidden // 2
+        atoms_b, out_b = m * hidden // 16, m * hidden * 2
+        self.off_slots, self.off_codes = 0, align256(slots_b)
+        self.off_atoms = self.off_codes + align256(codes_b)
+        self.off_out = self.off_atoms + align256(atoms_b)
+        total = self.off_out + align256(out_b)
+        self.buf = symm.empty(total, dtype=torch.uint8, device=backend.device)
+        self.buf.zero_()
+        self.hdl = symm.rendezvous(self.buf, group)
+        base = [int(p) for p in self.hdl.buffer_ptrs]
+        self.codes_ptrs = [p + self.off_codes for p in base]
+        self.atoms_ptrs = [p + self.off_atoms for p in base]
+        self.out_ptrs = [p + self.off_out for p in base]
+        # this rank's slot in every owner's memory
+        self.slot_ptrs = [p + self.off_slots + rank * self.rows * hidden * 2 for p in base]
+        self.slots = self.buf[self.off_slots:self.off_slots + slots_b].view(torch.bfloat16)
+        self.codes = self.buf[self.off_codes:self.off_codes + codes_b]
+        self.atoms = self.buf[self.off_atoms:self.off_atoms + atoms_b]
+        self.out = self.buf[self.off_out:self.off_out + out_b].view(torch.bfloat16)
+        self.maps = torch.zeros(world * 128, dtype=torch.uint8, device=backend.device)
+        backend.tp_make_maps(self.maps, self.slot_ptrs, self.rows, hidden)
+        torch.cuda.synchronize()
+        self.hdl.barrier(channel=0)
+
+    def barrier(self) -> None:
+        self.hdl.barrier(channel=0)
+
+
 @dataclass
 class LayerWeights:
     q: WeightView
@@ -161,12 +202,57 @@ class LinearStack:
         self.hq = backend.q4_blob(m, s.hidden)                          # norm output as NVFP4
         self.qq = backend.q4_blob(m, s.q_dim // world)                  # q projection as NVFP4 (o's input)
         self.gq = backend.q4_blob(m, s.intermediate // world)           # silu(gate)*up as NVFP4 (down's input)
+        self.fabric: Optional[TpFabric] = None
         self.weight_bytes = sum(v.buf.numel() for l in self.layers
                                 for v in (l.q, l.k, l.v, l.o, l.gate, l.up, l.down))
 
     def _all_reduce(self, t: torch.Tensor) -> None:
         if self.world > 1:
             torch.distributed.all_reduce(t, group=self.group)
+
+    def enable_fused_tp(self, m: int) -> bool:
+        """Set up the symmetric buffers of the fused scatter / gather path for steps of m tokens.
+        False (and nothing changed) where it does not apply."""
+        if self.world == 1 or not self.a4 or m <= 16 or m % (self.world * 128) != 0 or m > self.max_tokens:
+            return False
+        self.fabric = TpFabric(self.b, self.group if self.group is not None else torch.distributed.group.WORLD,
+                               self.rank, self.world, m, self.spec.hidden)
+        return True
+
+    def forward_fused_tp(self, xb_in: torch.Tensor) -> torch.Tensor:
+        """The step with communication fused into the kernels on either side of it. Token rows
+        are owned by ranks in equal blocks. o and down store their bf16 partial tiles straight into
+        the owning rank's slots (GEMM epilogue, TMA stores over NVLink); the norm adds the slots to
+        its own rows of the f32 residual, normalises them, and writes the NVFP4 result into every
+        rank's blob. Four stream barriers per layer keep the phases apart."""
+        b, s, f = self.b, self.spec, self.fabric
+        h, m, rows, world = s.hidden, f.m, f.rows, self.world
+        r0 = self.rank * rows
+        launches0 = b.launch_count()
+        x_own = self.x[: rows * h]
+        x_own.copy_(xb_in.reshape(-1)[r0 * h:(r0 + rows) * h])
+        hq = (f.codes, f.atoms)
+        nslots = 0
+        for l in self.layers:
+            b.tp_norm_q4(x_own, f.slots, nslots, rows * h, self.norm_w, f.codes_ptrs, f.atoms_ptrs, r0, rows, h,
+                         s.norm_eps, DIV_NORM_OUT)
+            nslots = world
+            f.barrier()                                   # every rank's rows of the blob are in place
+            b.linear_q4_to_q4(hq, DIV_NORM_OUT, l.q, m, self.qq, DIV_O_IN)
+            b.linear_q4(hq, DIV_NORM_OUT, l.k, None, m, yb=self.kb)
+            b.linear_q4(hq, DIV_NORM_OUT, l.v, None, m, yb=self.vb)
+            b.tp_linear_q4_scatter(self.qq, DIV_O_IN, l.o, m, f.maps, rows)
+            f.barrier()                                   # all partial sums of o have landed
+            b.tp_norm_q4(x_own, f.slots, world, rows * h, self.norm_w, f.codes_ptrs, f.atoms_ptrs, r0, rows, h,
+                         s.norm_eps, DIV_NORM_OUT)
+            f.barrier()
+            b.linear_swiglu_q4_to_q4(hq, DIV_NORM_OUT, l.gate, l.up, m, self.gq, DIV_DOWN_IN)
+            b.tp_linear_q4_scatter(self.gq, DIV_DOWN_IN, l.down, m, f.maps, rows)
+            f.barrier()
+        b.tp_finish(x_own, f.slots, world, rows * h, f.out_ptrs, r0, rows, h)
+        f.barrier()
+        self.launches_per_step = b.launch_count() - launches0
+        return f.out
 
     def forward(self, xb_in: torch.Tensor, m: int) -> torch.Tensor:
         """One step over m tokens: xb_in is bf16 [m, hidden] on the device; returns the final
