@@ -231,6 +231,20 @@ int velox_sm100_linear_swiglu_q4_to_q4(const uint8_t* codes, const uint8_t* atom
                                        uint16_t* outb, uint8_t* out_codes, uint8_t* out_atoms,
                                        float out_divisor);
 
+/* Several views of one width reading the same FP4 activations, each with its own destination: the
+ * q4 form of Backend::linears (backend.rs:1001-1048). yb may be NULL when out_codes is given (the
+ * result then exists only as the next linear's FP4 input). At decode sizes up to three views run
+ * as one launch; otherwise one launch per view. */
+typedef struct {
+    velox_sm100_view view;
+    uint16_t* yb;          /* [m, view.rows] bf16, or NULL */
+    uint8_t* out_codes;    /* optional: see velox_sm100_linear_q4_to_q4 */
+    uint8_t* out_atoms;
+    float out_divisor;
+} velox_sm100_part_q4;
+int velox_sm100_linears_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                           const velox_sm100_part_q4* parts, int nparts, int m);
+
 /* Tensor parallelism over one node (no counterpart in the reference, which is single-device).
  * Token rows are owned by ranks in equal blocks of `rows_per_owner` (a multiple of 128). Buffers
  * named "_ptrs" are arrays, one entry per rank, of device addresses valid on the calling GPU

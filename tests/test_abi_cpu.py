@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
 def test_view_struct_layout_matches_header():
     import ctypes as C
     # 8 + 4 + 4 + 8 + 8 + 8 + 4 + 4
-    assert C.sizeof(_lib.View) == 48 and C.sizeof(_lib.Part) == 72
+    assert C.sizeof(_lib.View) == 48 and C.sizeof(_lib.Part) == 72 and C.sizeof(_lib.PartQ4) == 80
     assert _lib.View.rows.offset == 40 and _lib.View.divisor.offset == 44
 
 

@@ -334,3 +334,33 @@ def test_linears_emit_the_next_linears_nvfp4_input(b, n, k, m):
     assert torch.equal(ob, ob_ref)
     assert torch.equal(oq[0].reshape(m, half // 2), want_codes.reshape(m, half // 2))
     _assert_atoms_equal(oq[1], want_atoms, m, half)
+
+
+@pytest.mark.parametrize("m", [1, 8, 40])
+def test_linears_q4_equals_separate_calls(b, m):
+    """q, k and v of one input through linears_q4 (one launch at decode sizes) give the bits the
+    per-view entry points give, including the FP4 hand-over of the first view."""
+    r = O.Rng(53)
+    k = 1024
+    shapes = (512, 128, 256)
+    payloads = [r.random_weight(FMT_O[NV], n, k) for n in shapes]
+    views = [make_view(b, p, NV, n, k, 0, n, ActPolicy.allow_a4(256.0)) for p, n in zip(payloads, shapes)]
+    acc = b.upload(r.vec(m * k, 1.0))
+    q4 = b.q4_blob(m, k)
+    b.add_rms_norm_q4(acc, None, b.upload(np.ones(k, np.float32)), None, q4, m, k, 1e-6, 256.0)
+    dev = acc.device
+    want = []
+    for v, n in zip(views, shapes):
+        yb = torch.zeros(m * n, dtype=torch.bfloat16, device=dev)
+        b.linear_q4(q4, 256.0, v, None, m, yb=yb)
+        want.append(yb)
+    oq_ref = b.q4_blob(m, shapes[0])
+    b.linear_q4_to_q4(q4, 256.0, views[0], m, oq_ref, 128.0)
+    oq = b.q4_blob(m, shapes[0])
+    got = [torch.zeros_like(w) for w in want]
+    b.linears_q4(q4, 256.0, [(views[0], got[0], oq, 128.0), (views[1], got[1], None, 0.0), (views[2], got[2], None, 0.0)], m)
+    assert b.lib.velox_sm100_debug_status() == 0
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    assert torch.equal(oq[0], oq_ref[0])
+    _assert_atoms_equal(oq[1], oq_ref[1], m, shapes[0])

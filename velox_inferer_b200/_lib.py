@@ -32,6 +32,12 @@ class View(C.Structure):
     ]
 
 
+class PartQ4(C.Structure):
+    """velox_sm100_part_q4."""
+    _fields_ = [("view", View), ("yb", C.c_void_p), ("out_codes", C.c_void_p), ("out_atoms", C.c_void_p),
+                ("out_divisor", C.c_float)]
+
+
 class Part(C.Structure):
     """``velox_sm100_part`` (include/velox_sm100.h)."""
 
@@ -53,6 +59,7 @@ SIGNATURES = {
     "velox_sm100_add_rms_norm_q4": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _F, _I, _F]),
     "velox_sm100_linear_q4": (_I, [_VP, _VP, _F, _PV, _I, _VP, _VP]),
     "velox_sm100_linear_swiglu_q4": (_I, [_VP, _VP, _F, _PV, _PV, _I, _VP, _VP]),
+    "velox_sm100_linears_q4": (_I, [_VP, _VP, _F, _VP, _I, _I]),
     "velox_sm100_tp_make_maps": (_I, [_VP, _VP, _I, _I, _LL]),
     "velox_sm100_tp_linear_q4_scatter": (_I, [_VP, _VP, _F, _PV, _I, _VP, _I]),
     "velox_sm100_tp_norm_q4": (_I, [_VP, _VP, _I, _LL, _VP, _VP, _VP, _I, _LL, _I, _I, _F, _I, _F]),

@@ -282,6 +282,16 @@ class Sm100Backend:
             q4[0].data_ptr(), q4[1].data_ptr(), divisor, C.byref(_view_struct(gate)), C.byref(_view_struct(up)), m,
             _ptr(outb), out_q4[0].data_ptr(), out_q4[1].data_ptr(), out_divisor), "sm100 linear_swiglu_q4_to_q4")
 
+    def linears_q4(self, q4, divisor: float, parts, m: int) -> None:
+        """parts: (view, yb or None, out_q4 or None, out_divisor) per projection of the same input."""
+        self._bind()
+        arr = (_lib.PartQ4 * len(parts))()
+        for i, (w, yb, oq, od) in enumerate(parts):
+            arr[i] = _lib.PartQ4(_view_struct(w), _ptr(yb), None if oq is None else oq[0].data_ptr(),
+                                 None if oq is None else oq[1].data_ptr(), od)
+        status(self.lib.velox_sm100_linears_q4(q4[0].data_ptr(), q4[1].data_ptr(), divisor, arr, len(parts), m),
+               "sm100 linears_q4")
+
     # -- tensor parallelism: reduce-scatter fused into the row-split linear, all-gather into the norm
     def tp_make_maps(self, maps_dev: torch.Tensor, slot_ptrs, rows_per_owner: int, cols: int) -> None:
         self._bind()

@@ -473,6 +473,47 @@ int velox_sm100_linear_swiglu_q4_to_q4(const uint8_t* codes, const uint8_t* atom
                          out_divisor);
 }
 
+int velox_sm100_linears_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                           const velox_sm100_part_q4* parts, int nparts, int m) {
+    if (!codes || !atoms || !parts || nparts < 1 || m <= 0) return VELOX_ERR_SHAPE;
+    for (int i = 0; i < nparts; i++) {
+        const velox_sm100_part_q4& q = parts[i];
+        int rc = check_view(&q.view);
+        if (rc != 0) return rc;
+        if (!q.yb && !q.out_codes) return VELOX_ERR_SHAPE;
+        if (q.view.policy != VELOX_POLICY_ALLOW_A4 || q.view.divisor != divisor || q.view.k != parts[0].view.k)
+            return VELOX_ERR_UNSUPPORTED;
+    }
+    auto args_of = [&](const velox_sm100_part_q4& q) {
+        LinearArgs l{};
+        l.w = q.view;
+        l.m = m;
+        l.yb = q.yb;
+        l.ld = q.view.rows;
+        l.col = 0;
+        l.q_codes = codes;
+        l.q_atoms = atoms;
+        l.qo_codes = q.out_codes;
+        l.qo_atoms = q.out_atoms;
+        l.qo_divisor = q.out_divisor;
+        return l;
+    };
+    // decode: one launch for up to three views; otherwise one launch per view
+    if (nparts <= 3 && plan_for(parts[0].view, m).path == PATH_GEMV_TC) {
+        LinearArgs l[3];
+        for (int i = 0; i < nparts; i++) l[i] = args_of(parts[i]);
+        const int rc = gemv_nvfp4_tc_parts(l, nparts, divisor);
+        if (rc != VELOX_ERR_UNSUPPORTED) return rc;
+    }
+    for (int i = 0; i < nparts; i++) {
+        const Plan p = plan_for(parts[i].view, m);
+        if (p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
+        const int rc = run(args_of(parts[i]), p);
+        if (rc != 0) return rc;
+    }
+    return 0;
+}
+
 int velox_sm100_tp_make_maps(void* maps_dev, const unsigned long long* slot_ptrs, int n, int rows_per_owner,
                              long long cols) {
     return gemm_make_rs_maps(maps_dev, slot_ptrs, n, rows_per_owner, cols);

@@ -25,6 +25,8 @@ int gemm_make_rs_maps(void* maps_dev, const unsigned long long* ptrs, int n, int
 // NVFP4 decode linear (m <= 16) on the block-scaled tensor cores, activations quantised to NVFP4
 // with `divisor` (or taken from a.q_codes / a.q_atoms). VELOX_ERR_UNSUPPORTED for other shapes.
 int gemv_nvfp4_tc(const LinearArgs& a, float divisor);
+// The same for up to three views of one width that share the activations, in one launch.
+int gemv_nvfp4_tc_parts(const LinearArgs* parts, int n, float divisor);
 
 // Synchronises the device and returns the tensor-core kernels' status word: 0, or the code of the
 // first bounded wait that gave up.

@@ -45,18 +45,11 @@ constexpr int DT_ACC_COLS = 32;      // per buffer: 16 token columns for each of
 constexpr int DT_SF_COL = 64;        // scale sets follow the two accumulator buffers
 constexpr int DT_SF_SET = 32;        // per set: 16 columns of W scales, 16 of x scales
 
-struct DtParams {
-    int m;
-    int k_blocks, k_steps;
-    long long k_tiles64;
-    long long tile0[2];          // first 128-row tile (parent coordinates) of each pass
-    int tiles;
-    long long per_cta;           // (tile, k-block) steps per CTA; CTA c takes steps [c * per_cta, (c + 1) * per_cta)
-    const uint8_t* sfw[2];
-    const uint8_t* sfx;
-    const float* wdiv[2];
-    float alpha;                 // 1 / activation divisor
-    long long valid_begin, valid_end;   // rows of the view, pass-0 parent coordinates
+constexpr int DT_MAX_PARTS = 3;   // views served by one launch (q, k, v of one input)
+
+// Where one view's results go.
+struct DtOut {
+    long long valid_begin, valid_end;   // rows of the view, parent coordinates
     float* y;
     uint16_t* yb;
     long long ld, col;
@@ -64,6 +57,25 @@ struct DtParams {
     uint8_t* q_atoms;            // ... with their scale atoms, for the next linear
     float q_divisor;
     long long q_ld;
+};
+
+struct DtParams {
+    int m;
+    int k_blocks, k_steps;
+    long long k_tiles64;
+    // Plain form: up to three views of the same width sharing the activations, their 128-row tiles
+    // numbered one view after the other. SwiGLU form: entries 0 and 1 are gate and up of one
+    // output (out[0]), walked as two passes over the same tile index.
+    int nparts;
+    int part_tiles[DT_MAX_PARTS];
+    long long tile0[DT_MAX_PARTS];      // first 128-row tile (parent coordinates)
+    const uint8_t* sfw[DT_MAX_PARTS];
+    const float* wdiv[DT_MAX_PARTS];
+    DtOut out[DT_MAX_PARTS];
+    int tiles;                   // all parts together
+    long long per_cta;           // (tile, k-block) steps per CTA; CTA c takes steps [c * per_cta, (c + 1) * per_cta)
+    const uint8_t* sfx;
+    float alpha;                 // 1 / activation divisor
     float* partial;              // [CTAs][2][V][128][16]: a CTA's first and last run can be partial tiles
     int* tickets;                // [tiles], zero between launches
     int* status;
@@ -74,7 +86,8 @@ __device__ int g_gemv_tc_status = 0;
 template <bool SWIGLU>
 __global__ void __launch_bounds__(DT_THREADS, 1)
 gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
-                     const __grid_constant__ CUtensorMap map_x, const DtParams p) {
+                     const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_x,
+                     const DtParams p) {
     constexpr int V = SWIGLU ? 2 : 1;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -114,6 +127,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w0) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w1) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w2) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
     }
     if (warp == 1) {
@@ -141,6 +155,17 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         return q;
     };
 
+    // which view a tile belongs to, and its index among that view's tiles (plain form)
+    auto part_of = [&](int tile, int& local) {
+        int part = 0;
+        local = tile;
+        while (part + 1 < p.nparts && local >= p.part_tiles[part]) {
+            local -= p.part_tiles[part];
+            part++;
+        }
+        return part;
+    };
+
     if (warp == 0) {
         // ---------------- operand producer ----------------
         int stage = 0;
@@ -164,7 +189,10 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
             const int tile = pc.tile, kb0 = pc.kb0, kb1 = pc.kb1;
             u += kb1 - kb0;
             for (int v = 0; v < V && ok; v++) {
-                const int row0 = (int)((p.tile0[v] + tile) * 128);
+                int lt = tile;
+                const int idx = SWIGLU ? v : part_of(tile, lt);
+                const int row0 = (int)((p.tile0[idx] + lt) * 128);
+                const CUtensorMap* mw = idx == 0 ? &map_w0 : idx == 1 ? &map_w1 : &map_w2;
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!waited && issued == DT_STAGES) after_dependency();
                     if (!mbar_wait(op_empty(stage), phase ^ 1u, 20)) {
@@ -175,7 +203,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                     const uint32_t sw = base + stage * DT_STAGE_BYTES;
                     if (leader) {
                         mbar_arrive_expect_tx(op_full(stage), DT_STAGE_BYTES);
-                        tma_load_2d(sw, v ? &map_w1 : &map_w0, op_full(stage), kb * 128, row0);
+                        tma_load_2d(sw, mw, op_full(stage), kb * 128, row0);
                         if (waited) tma_load_2d(sw + DT_W_BYTES, &map_x, op_full(stage), kb * 128, 0);
                     }
                     if (!waited) pend_kb[issued++] = kb;
@@ -258,7 +286,9 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
             const int tile = pc.tile, kb0 = pc.kb0, kb1 = pc.kb1;
             u += kb1 - kb0;
             for (int v = 0; v < V && ok; v++) {
-                const uint8_t* wsf = p.sfw[v] + (p.tile0[v] + tile) * p.k_tiles64 * 512;
+                int lt = tile;
+                const int idx = SWIGLU ? v : part_of(tile, lt);
+                const uint8_t* wsf = p.sfw[idx] + (p.tile0[idx] + lt) * p.k_tiles64 * 512;
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!waited && issued == DT_STAGES) after_dependency();
                     if (!mbar_wait(sf_empty(stage), phase ^ 1u, 50)) {
@@ -335,8 +365,6 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         // ---------------- epilogue ----------------
         const int quad = warp % 4;
         const int row_in_tile = quad * 32 + lane;
-        const float f0 = p.alpha / *p.wdiv[0];
-        const float f1 = SWIGLU ? p.alpha / *p.wdiv[1] : 0.0f;
         int n = 0;
         for (long long u = u_begin; u < u_end; n++) {
             const Piece pc = piece_at(u);
@@ -415,9 +443,14 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                 }
             }
             if (finish) {
-                const long long row = (p.tile0[0] + tile) * 128 + row_in_tile;
-                const bool row_ok = row >= p.valid_begin && row < p.valid_end;
-                const long long o0 = p.col + (row - p.valid_begin);
+                int lt = tile;
+                const int idx = SWIGLU ? 0 : part_of(tile, lt);
+                const DtOut& o = p.out[idx];
+                const float f0 = p.alpha / *p.wdiv[idx];
+                const float f1 = SWIGLU ? p.alpha / *p.wdiv[1] : 0.0f;
+                const long long row = (p.tile0[idx] + lt) * 128 + row_in_tile;
+                const bool row_ok = row >= o.valid_begin && row < o.valid_end;
+                const long long o0 = o.col + (row - o.valid_begin);
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     if (j < p.m) {   // uniform across the warp
@@ -427,10 +460,10 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                             val = val / (1.0f + __expf(-val)) * u;
                         }
                         if (row_ok) {
-                            if (p.y) p.y[(long long)j * p.ld + o0] = val;
-                            if (p.yb) p.yb[(long long)j * p.ld + o0] = bf16_bits(val);
+                            if (o.y) o.y[(long long)j * o.ld + o0] = val;
+                            if (o.yb) o.yb[(long long)j * o.ld + o0] = bf16_bits(val);
                         }
-                        if (p.q_codes) {
+                        if (o.q_codes) {
                             // The same value as the next linear's NVFP4 input: sixteen consecutive
                             // outputs of a token sit in sixteen consecutive lanes (the host side only
                             // allows views that start on a scale tile and hold whole groups).
@@ -439,14 +472,14 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
 #pragma unroll
                             for (int off = 8; off >= 1; off >>= 1)
                                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-                            const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(p.q_divisor, amax), 6.0f));
-                            const float q = sb ? __fdiv_rn(__fmul_rn(vb, p.q_divisor), e4m3_to_f32(sb)) : 0.0f;
+                            const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(o.q_divisor, amax), 6.0f));
+                            const float q = sb ? __fdiv_rn(__fmul_rn(vb, o.q_divisor), e4m3_to_f32(sb)) : 0.0f;
                             const float qn = __shfl_down_sync(0xffffffffu, q, 1);
                             if (row_ok) {
                                 if ((lane & 1) == 0)
-                                    p.q_codes[((long long)j * p.q_ld + o0) / 2] = (uint8_t)f32x2_to_e2m1x2(q, qn);
+                                    o.q_codes[((long long)j * o.q_ld + o0) / 2] = (uint8_t)f32x2_to_e2m1x2(q, qn);
                                 if ((lane & 15) == 0)
-                                    p.q_atoms[nvfp4_scale_offset(j, o0 / 16, p.q_ld)] = (uint8_t)sb;
+                                    o.q_atoms[nvfp4_scale_offset(j, o0 / 16, o.q_ld)] = (uint8_t)sb;
                             }
                         }
                     }
@@ -499,16 +532,15 @@ int gemv_tc_status_sync() {
     return v;
 }
 
-int gemv_nvfp4_tc(const LinearArgs& a, float divisor) {
-    if (!gemm_available()) return VELOX_ERR_UNSUPPORTED;
-    const velox_sm100_view& w = a.w;
+// One launch for `n` views of the same parent width that read the same activations (n = 1 is the
+// plain linear; the fused SwiGLU pair is a single LinearArgs with swiglu set and n = 1).
+int gemv_nvfp4_tc_parts(const LinearArgs* parts, int n, float divisor) {
+    if (!gemm_available() || n < 1 || n > DT_MAX_PARTS) return VELOX_ERR_UNSUPPORTED;
+    const LinearArgs& a = parts[0];
     const bool sw = a.swiglu != 0;
-    const velox_sm100_view& u = sw ? a.up : a.w;
-    if (w.format != VELOX_FMT_NVFP4 || a.m < 1 || a.m > 16 || w.k % 64 != 0 || !(divisor > 0.0f))
-        return VELOX_ERR_UNSUPPORTED;
-    if (sw && ((w.row_begin - u.row_begin) % 128 != 0 || u.format != VELOX_FMT_NVFP4)) return VELOX_ERR_UNSUPPORTED;
-    if (reinterpret_cast<uintptr_t>(w.w) & 15) return VELOX_ERR_UNSUPPORTED;
-    const long long k = w.k;
+    if (sw && n != 1) return VELOX_ERR_UNSUPPORTED;
+    const long long k = a.w.k;
+    if (a.m < 1 || a.m > 16 || k % 64 != 0 || !(divisor > 0.0f)) return VELOX_ERR_UNSUPPORTED;
 
     const uint8_t* codes = a.q_codes;
     const uint8_t* atoms = a.q_atoms;
@@ -527,32 +559,58 @@ int gemv_nvfp4_tc(const LinearArgs& a, float divisor) {
     p.k_steps = (int)(k / 64);
     p.k_blocks = (p.k_steps + 3) / 4;
     p.k_tiles64 = k / 64;
-    p.tile0[0] = w.row_begin / 128;
-    p.tile0[1] = u.row_begin / 128;
-    p.tiles = (int)((w.row_begin + w.rows - 1) / 128 - w.row_begin / 128 + 1);
-    p.sfw[0] = w.w + align256(w.n * k / 2);
-    p.sfw[1] = u.w + align256(u.n * k / 2);
-    p.wdiv[0] = reinterpret_cast<const float*>(p.sfw[0] + w.n * k / 16);
-    p.wdiv[1] = reinterpret_cast<const float*>(p.sfw[1] + u.n * k / 16);
     p.sfx = atoms;
     p.alpha = 1.0f / divisor;
-    p.valid_begin = w.row_begin;
-    p.valid_end = w.row_begin + w.rows;
-    p.y = a.y;
-    p.yb = a.yb;
-    p.ld = a.ld;
-    p.col = a.col;
     p.status = gemv_tc_status_ptr();
     if (!p.status) return VELOX_ERR_UNSUPPORTED;
-    if (a.qo_codes) {
-        // whole 16-wide groups of whole rows of the quantised matrix, starting at column 0
-        if (!a.qo_atoms || !(a.qo_divisor > 0.0f) || a.col != 0 || w.row_begin % 128 != 0 || w.rows % 64 != 0 || a.y)
-            return VELOX_ERR_UNSUPPORTED;
-        p.q_codes = a.qo_codes;
-        p.q_atoms = a.qo_atoms;
-        p.q_divisor = a.qo_divisor;
-        p.q_ld = w.rows;
+
+    CUtensorMap mw[DT_MAX_PARTS], mx;
+    auto set_weights = [&](int i, const velox_sm100_view& v) -> int {
+        if (v.format != VELOX_FMT_NVFP4 || v.k != k || (reinterpret_cast<uintptr_t>(v.w) & 15)) return VELOX_ERR_UNSUPPORTED;
+        p.tile0[i] = v.row_begin / 128;
+        p.sfw[i] = v.w + align256(v.n * k / 2);
+        p.wdiv[i] = reinterpret_cast<const float*>(p.sfw[i] + v.n * k / 16);
+        return gemm_make_map_u8(&mw[i], v.w, v.n, k / 2, 128);
+    };
+    auto set_out = [&](int i, const LinearArgs& l) -> int {
+        const velox_sm100_view& v = l.w;
+        DtOut& o = p.out[i];
+        o.valid_begin = v.row_begin;
+        o.valid_end = v.row_begin + v.rows;
+        o.y = l.y;
+        o.yb = l.yb;
+        o.ld = l.ld;
+        o.col = l.col;
+        if (l.qo_codes) {
+            // whole 16-wide groups of whole rows of the quantised matrix, starting at column 0
+            if (!l.qo_atoms || !(l.qo_divisor > 0.0f) || l.col != 0 || v.row_begin % 128 != 0 || v.rows % 64 != 0 || l.y)
+                return VELOX_ERR_UNSUPPORTED;
+            o.q_codes = l.qo_codes;
+            o.q_atoms = l.qo_atoms;
+            o.q_divisor = l.qo_divisor;
+            o.q_ld = v.rows;
+        }
+        return 0;
+    };
+    if (sw) {
+        if ((a.w.row_begin - a.up.row_begin) % 128 != 0) return VELOX_ERR_UNSUPPORTED;
+        if ((rc = set_weights(0, a.w)) != 0 || (rc = set_weights(1, a.up)) != 0 || (rc = set_out(0, a)) != 0) return rc;
+        mw[2] = mw[0];
+        p.nparts = 1;
+        p.part_tiles[0] = (int)((a.w.row_begin + a.w.rows - 1) / 128 - a.w.row_begin / 128 + 1);
+        p.tiles = p.part_tiles[0];
+    } else {
+        for (int i = 0; i < n; i++) {
+            const LinearArgs& l = parts[i];
+            if (l.swiglu || l.m != a.m) return VELOX_ERR_UNSUPPORTED;
+            if ((rc = set_weights(i, l.w)) != 0 || (rc = set_out(i, l)) != 0) return rc;
+            p.part_tiles[i] = (int)((l.w.row_begin + l.w.rows - 1) / 128 - l.w.row_begin / 128 + 1);
+            p.tiles += p.part_tiles[i];
+        }
+        for (int i = n; i < DT_MAX_PARTS; i++) mw[i] = mw[0];
+        p.nparts = n;
     }
+    if ((rc = gemm_make_map_u8(&mx, codes, a.m, k / 2, 16)) != 0) return rc;
 
     static int sms = 0;
     if (sms == 0) {
@@ -574,11 +632,6 @@ int gemv_nvfp4_tc(const LinearArgs& a, float divisor) {
         if (!p.partial || !p.tickets) return (int)cudaErrorMemoryAllocation;
     }
 
-    CUtensorMap mw0, mw1, mx;
-    if ((rc = gemm_make_map_u8(&mw0, w.w, w.n, k / 2, 128)) != 0) return rc;
-    if ((rc = gemm_make_map_u8(&mw1, u.w, u.n, k / 2, 128)) != 0) return rc;
-    if ((rc = gemm_make_map_u8(&mx, codes, a.m, k / 2, 16)) != 0) return rc;
-
     cudaError_t e;
     TimedRegion timed(TIMED_GEMV);
     cudaLaunchConfig_t cfg{};
@@ -599,15 +652,17 @@ int gemv_nvfp4_tc(const LinearArgs& a, float divisor) {
         auto kern = gemv_nvfp4_tc_kernel<true>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        e = cudaLaunchKernelEx(&cfg, kern, mw0, mw1, mx, p);
+        e = cudaLaunchKernelEx(&cfg, kern, mw[0], mw[1], mw[2], mx, p);
     } else {
         auto kern = gemv_nvfp4_tc_kernel<false>;
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        e = cudaLaunchKernelEx(&cfg, kern, mw0, mw1, mx, p);
+        e = cudaLaunchKernelEx(&cfg, kern, mw[0], mw[1], mw[2], mx, p);
     }
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
+
+int gemv_nvfp4_tc(const LinearArgs& a, float divisor) { return gemv_nvfp4_tc_parts(&a, 1, divisor); }
 
 }  // namespace vx

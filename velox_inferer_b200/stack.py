@@ -272,13 +272,11 @@ class LinearStack:
             if q4:
                 b.add_rms_norm_q4(self.x, None, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT,
                                   xb=None if first else self.pb)
-                # q feeds o directly (attention passthrough), so it is produced as o's FP4 input
-                if emit:
-                    b.linear_q4_to_q4(self.hq, DIV_NORM_OUT, l.q, m, self.qq, DIV_O_IN)
-                else:
-                    b.linear_q4(self.hq, DIV_NORM_OUT, l.q, None, m, yb=self.qb)
-                b.linear_q4(self.hq, DIV_NORM_OUT, l.k, None, m, yb=self.kb)
-                b.linear_q4(self.hq, DIV_NORM_OUT, l.v, None, m, yb=self.vb)
+                # q feeds o directly (attention passthrough), so it is produced as o's FP4 input;
+                # q, k and v read the same blob: one call (one launch at decode sizes)
+                b.linears_q4(self.hq, DIV_NORM_OUT,
+                             [(l.q, None, self.qq, DIV_O_IN) if emit else (l.q, self.qb, None, 0.0),
+                              (l.k, self.kb, None, 0.0), (l.v, self.vb, None, 0.0)], m)
             else:
                 b.add_rms_norm_twin(self.x, None, self.norm_w, None, self.hb, m, h, s.norm_eps,
                                     xb=None if first else self.pb)
