@@ -185,7 +185,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-components", action="store_true", help="skip the single-linear GEMV / GEMM lines")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--tp", choices=("fused", "nccl"), default="nccl",
+    ap.add_argument("--tp", choices=("fused", "nccl"), default="fused",
                     help="N > 1: communication fused into the GEMM epilogue and the norm over symmetric memory, "
                          "or one NCCL all-reduce after o and down")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")

@@ -25,17 +25,25 @@ def main() -> None:
     x = torch.from_numpy(np.random.default_rng(9).standard_normal((m, spec.hidden)).astype(np.float32))
     xb = x.to(torch.bfloat16).to(b.device)
     ref = stack.forward(xb, m).float().clone()
+    # The same weights unsharded on this GPU. A sharded step rounds each shard's partial sums to
+    # bf16, and FP4 activation quantisation downstream turns those last-bit differences into
+    # occasional one-step code changes, so the comparison is statistical: relative RMS error of a
+    # few percent, and the fused step no further from the unsharded one than the all-reduce step.
+    whole = LinearStack(b, spec, max_tokens=m, rank=0, world=1, a4=True, seed=5).forward(xb, m).float().clone()
+
+    def rel_rms(a, c):
+        return ((a - c).pow(2).mean().sqrt() / c.pow(2).mean().sqrt()).item()
+
+    err_nccl = rel_rms(ref, whole)
+    assert err_nccl <= 0.08, ("all-reduce step vs unsharded", err_nccl)
     assert stack.enable_fused_tp(m)
     for _ in range(2):                                   # twice: buffers are reused between steps
         got = stack.forward_fused_tp(xb).float().clone()
         torch.cuda.synchronize()
         assert b.lib.velox_sm100_debug_status() == 0
-        rms = ref.pow(2).mean().sqrt().item()
-        err = (got - ref).abs().max().item() / rms
-        # both round the partial sums to bf16; the all-reduce also rounds their sum, the fused path
-        # adds them in f32: a few bf16 units of the residual at most
-        assert err <= 3e-2, err
         assert torch.isfinite(got).all()
+        err = rel_rms(got, whole)
+        assert err <= 0.08 and err <= 2.0 * err_nccl + 0.01, ("fused step vs unsharded", err, "all-reduce step", err_nccl)
     # every rank holds the same full output
     mine = got.contiguous()
     others = [torch.empty_like(mine) for _ in range(world)]
@@ -43,7 +51,7 @@ def main() -> None:
     for o in others:
         assert torch.equal(o, mine)
     if rank == 0:
-        print("TP_FUSED_OK", err, flush=True)
+        print("TP_FUSED_OK", err, err_nccl, flush=True)
     torch.cuda.synchronize()
     dist.barrier()
     os._exit(0)

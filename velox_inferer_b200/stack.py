@@ -119,7 +119,10 @@ class TpFabric:
         self.buf = symm.empty(total, dtype=torch.uint8, device=backend.device)
         self.buf.zero_()
         self.hdl = symm.rendezvous(self.buf, group)
-        base = [int(p) for p in self.hdl.buffer_ptrs]
+        # buffer_ptrs are the starts of the ranks' symmetric blocks; this tensor sits at the same
+        # offset inside each of them
+        inside = self.buf.data_ptr() - int(self.hdl.buffer_ptrs[rank])
+        base = [int(p) + inside for p in self.hdl.buffer_ptrs]
         self.codes_ptrs = [p + self.off_codes for p in base]
         self.atoms_ptrs = [p + self.off_atoms for p in base]
         self.out_ptrs = [p + self.off_out for p in base]
