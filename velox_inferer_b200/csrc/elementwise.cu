@@ -169,13 +169,14 @@ struct Q4Dest {
 // Sequence-parallel form: `acc` holds only this rank's rows; the addend is the sum, in slot order,
 // of `nslots` bf16 partial-sum slots (one per source rank, `slot_stride` values apart), and the
 // output row lands at row `row0 + row` of every destination blob.
-template <int ITERS>
-__global__ void __launch_bounds__(256)
+template <int ITERS, int MAXT>
+__global__ void __launch_bounds__(MAXT)
 add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x, const uint16_t* __restrict__ xb,
                             int nslots, long long slot_stride, const float* __restrict__ weight,
                             uint16_t* __restrict__ yb, const Q4Dest dst, long long row0, int rows, int dim,
                             float eps, float offset, float divisor) {
-    __shared__ float red[8];
+    __shared__ float red[32];
+    const int T = (int)blockDim.x;   // a multiple of 32, at most 1024
     const long long row = blockIdx.x;
     if (threadIdx.x == 0) grid_launch_dependents();   // a decode linear behind this may start fetching weights
     if (row >= rows) {
@@ -185,44 +186,93 @@ add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x
     }
     const long long base = row * dim;
     float4 v[ITERS];
+    float4 part[ITERS];   // sum of the partial-sum slots (sequence-parallel form), added to the row once
+    auto sum_slots = [&](int it, const float4& f, bool first) {
+        if (first) {
+            part[it] = f;
+        } else {
+            part[it].x += f.x; part[it].y += f.y; part[it].z += f.z; part[it].w += f.w;
+        }
+    };
     float ss = 0.0f;
+    // All loads of the row are issued before anything is stored back: a store to acc between them
+    // would order the later loads behind it (same array) and cost one memory round trip per slice.
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
-        const int c = (it * 256 + (int)threadIdx.x) * 4;
-        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (c < dim) {
-            a = *reinterpret_cast<const float4*>(acc + base + c);
-            if (x) {
-                const float4 b = *reinterpret_cast<const float4*>(x + base + c);
-                a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
-                *reinterpret_cast<float4*>(acc + base + c) = a;
-            } else if (xb) {
-                float4 t = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                for (int sl = 0; sl < nslots; sl++) {
-                    const uint2 b = *reinterpret_cast<const uint2*>(xb + sl * slot_stride + base + c);
-                    t.x += __uint_as_float(b.x << 16); t.y += __uint_as_float(b.x & 0xffff0000u);
-                    t.z += __uint_as_float(b.y << 16); t.w += __uint_as_float(b.y & 0xffff0000u);
+        const int c = (it * T + (int)threadIdx.x) * 4;
+        v[it] = c < dim ? __ldcs(reinterpret_cast<const float4*>(acc + base + c)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+    if (x) {
+        float4 t[ITERS];
+#pragma unroll
+        for (int it = 0; it < ITERS; it++) {
+            const int c = (it * T + (int)threadIdx.x) * 4;
+            t[it] = c < dim ? __ldcs(reinterpret_cast<const float4*>(x + base + c)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int it = 0; it < ITERS; it++) {
+            v[it].x += t[it].x; v[it].y += t[it].y; v[it].z += t[it].z; v[it].w += t[it].w;
+        }
+    } else if (xb) {
+        for (int sl = 0; sl < nslots; sl++) {
+            uint2 t[ITERS];
+#pragma unroll
+            for (int it = 0; it < ITERS; it++) {
+                const int c = (it * T + (int)threadIdx.x) * 4;
+                t[it] = c < dim ? __ldcs(reinterpret_cast<const uint2*>(xb + sl * slot_stride + base + c)) : make_uint2(0u, 0u);
+            }
+            if (sl == 0) {
+                // the addend of the first slot goes in as it is; further slots are summed first
+#pragma unroll
+                for (int it = 0; it < ITERS; it++) {
+                    const float4 f = make_float4(__uint_as_float(t[it].x << 16), __uint_as_float(t[it].x & 0xffff0000u),
+                                                 __uint_as_float(t[it].y << 16), __uint_as_float(t[it].y & 0xffff0000u));
+                    if (nslots == 1) {
+                        v[it].x += f.x; v[it].y += f.y; v[it].z += f.z; v[it].w += f.w;
+                    } else {
+                        sum_slots(it, f, true);
+                    }
                 }
-                a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w;
-                *reinterpret_cast<float4*>(acc + base + c) = a;
+            } else {
+#pragma unroll
+                for (int it = 0; it < ITERS; it++) {
+                    const float4 f = make_float4(__uint_as_float(t[it].x << 16), __uint_as_float(t[it].x & 0xffff0000u),
+                                                 __uint_as_float(t[it].y << 16), __uint_as_float(t[it].y & 0xffff0000u));
+                    sum_slots(it, f, false);
+                }
             }
         }
-        v[it] = a;
+        if (nslots > 1) {
+#pragma unroll
+            for (int it = 0; it < ITERS; it++) {
+                v[it].x += part[it].x; v[it].y += part[it].y; v[it].z += part[it].z; v[it].w += part[it].w;
+            }
+        }
+    }
+    if (x || xb) {
+#pragma unroll
+        for (int it = 0; it < ITERS; it++) {
+            const int c = (it * T + (int)threadIdx.x) * 4;
+            if (c < dim) __stcs(reinterpret_cast<float4*>(acc + base + c), v[it]);
+        }
+    }
+#pragma unroll
+    for (int it = 0; it < ITERS; it++) {
         // the order of the reference's running sum does not survive any parallel reduction; this
         // one matches add_rms_norm_twin's up to the f32 rounding of the partial sums
-        ss = fmaf(a.x, a.x, ss); ss = fmaf(a.y, a.y, ss); ss = fmaf(a.z, a.z, ss); ss = fmaf(a.w, a.w, ss);
+        ss = fmaf(v[it].x, v[it].x, ss); ss = fmaf(v[it].y, v[it].y, ss);
+        ss = fmaf(v[it].z, v[it].z, ss); ss = fmaf(v[it].w, v[it].w, ss);
     }
     ss = warp_sum(ss);
     if (threadIdx.x % VX_WARP == 0) red[threadIdx.x / VX_WARP] = ss;
     __syncthreads();
     float total = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; i++) total += red[i];
+    for (int i = 0; i < T / VX_WARP; i++) total += red[i];
     const float inv = 1.0f / sqrtf(total / (float)dim + eps);
     const long long obase = (row0 + row) * dim;
 #pragma unroll
     for (int it = 0; it < ITERS; it++) {
-        const int c = (it * 256 + (int)threadIdx.x) * 4;
+        const int c = (it * T + (int)threadIdx.x) * 4;
         const bool in = c < dim;
         float n[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         if (in) {
@@ -295,11 +345,15 @@ static int launch_norm_q4(float* acc, const float* x, const uint16_t* xb, int ns
                           const float* weight, uint16_t* yb, const Q4Dest& dst, long long row0, int rows,
                           int rows_padded, int dim, float eps, int offset, float divisor) {
     const float off = offset ? 1.0f : 0.0f;
-    if (dim <= 2048)
-        add_rms_norm_q4_rows_kernel<2><<<(unsigned)rows_padded, 256, 0, stream()>>>(
+    if (dim % 256 == 0)
+        // one block per row with dim / 8 threads: two 128-bit slices per thread, many warps in flight
+        add_rms_norm_q4_rows_kernel<2, 1024><<<(unsigned)rows_padded, dim / 8, 0, stream()>>>(
+            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor);
+    else if (dim <= 2048)
+        add_rms_norm_q4_rows_kernel<2, 256><<<(unsigned)rows_padded, 256, 0, stream()>>>(
             acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor);
     else
-        add_rms_norm_q4_rows_kernel<8><<<(unsigned)rows_padded, 256, 0, stream()>>>(
+        add_rms_norm_q4_rows_kernel<8, 256><<<(unsigned)rows_padded, 256, 0, stream()>>>(
             acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor);
     return launch_status();
 }
