@@ -106,6 +106,7 @@ struct GemmParams {
     uint8_t* q_atoms;   // ... and scale atoms over ceil(m / 128) * 128 rows
     float q_divisor;
     long long q_ld;     // columns of the quantised matrix (a multiple of 64)
+    int early;      // the launch may start before the kernel ahead of it has finished (see the producers)
     int* status;
     int dbg;        // profiling builds only: 1 no epilogue at all, 2 loads only, 8 no operand loads, 16 no scale path, 32 no MMAs
 };
@@ -166,6 +167,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    // A kernel launched behind this one with early start allowed may begin as CTAs here retire.
+    if (threadIdx.x == 0) grid_launch_dependents();
     // In a pair, CTA 0 issues the MMAs for both and owns the barriers the other CTA reports to.
     const uint32_t rank = CG == 2 ? cluster_ctarank() : 0u;
     auto arrive_lead = [&](uint32_t bar) {
@@ -237,11 +240,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const bool leader = elect_one();
             PROF_DECL;
             PROF_T0(t_all);
+            // Weights that are read from their stored payload do not depend on the kernel ahead of
+            // this one in the stream, the activations do: with early start allowed the first ring
+            // pass requests its W boxes at once, then waits for that kernel and adds the x boxes.
+            // (The bf16 path's W operand is scratch the kernel ahead wrote: it waits first.)
+            int issued = 0, pend_x[OP_STAGES], pend_y[OP_STAGES];
+            bool waited = !(p.early && KIND != KIND_BF16);
+            if (waited) grid_dependency_wait();
+            auto after_dependency = [&]() {
+                grid_dependency_wait();
+                if (leader)
+                    for (int i = 0; i < issued; i++)
+                        tma_load_2d(base + i * OP_STAGE_BYTES, &tmap_a, op_full(i), pend_x[i], pend_y[i]);
+                waited = true;
+            };
             for (int tile = unit; tile < num_tiles && ok; tile += units) {
                 const int mt = (tile % tiles_mu) * CG + (int)rank, nt = tile / tiles_mu;
                 const int r0 = (int)(p.b_row0[0] + (long long)nt * p.b_tile_rows);
                 const int r1 = (int)(p.b_row0[1] + (long long)nt * p.b_tile_rows);
                 for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!waited && issued == OP_STAGES) after_dependency();
                     PROF_T0(t_w);
                     if (!mbar_wait(op_empty(stage), phase ^ 1u, 20)) {
                         if (leader) atomicExch(p.status, ST_TIMEOUT_EMPTY);
@@ -260,8 +278,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #endif
                         {
                             mbar_arrive_expect_tx(op_full(stage), A_BYTES + PL::B_BYTES);
-                            tma_load_2d(sa, &tmap_a, op_full(stage), (kb % p.a_k_blocks) * p.k_elems_per_block,
-                                        mt * BM);
+                            if (waited)
+                                tma_load_2d(sa, &tmap_a, op_full(stage), (kb % p.a_k_blocks) * p.k_elems_per_block,
+                                            mt * BM);
                             if (CG == 2) {
                                 // one half of the W tile; the MMA reads the other from the partner
                                 if (rank)
@@ -274,12 +293,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                             }
                         }
                     }
+                    if (!waited) {
+                        pend_x[issued] = (kb % p.a_k_blocks) * p.k_elems_per_block;
+                        pend_y[issued] = mt * BM;
+                        issued++;
+                    }
                     if (++stage == OP_STAGES) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
             }
+            if (!waited) after_dependency();
             if (!ok) __nanosleep(200000);  // let copies already in flight land before the CTA exits
             PROF_ADD(1, t_all);
             if (leader) {
@@ -668,6 +693,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             bool ok = true;
             const bool leader = elect_one();
             if (p.dbg & 16) ok = false;   // profiling builds, timing only: no scales at all
+            grid_dependency_wait();   // the activation scales come from the kernel ahead of this one
             for (int tile = unit; tile < num_tiles && ok; tile += units) {
                 const int mt = (tile % tiles_mu) * CG + (int)rank, nt = tile / tiles_mu;
                 const long long r0 = p.b_row0[0] + (long long)nt * p.b_tile_rows;
@@ -884,14 +910,15 @@ static int launch_cfg(const CUtensorMap& a, const CUtensorMap& b0, const CUtenso
     cfg.blockDim = dim3(GEMM_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream();
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     int units = sms / CG;
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
     if (CG == 2) {
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
         cfg.numAttrs = 1;
         // pairs that can be resident at once (GPCs with an odd SM count leave one SM out)
         static int max_pairs[2] = {0, 0};
@@ -907,6 +934,13 @@ static int launch_cfg(const CUtensorMap& a, const CUtensorMap& b0, const CUtenso
     }
     if (tiles < units) units = tiles;
     cfg.gridDim = dim3(units * CG);
+    if (p.early) {
+        // early start: CTAs may become resident while the kernel ahead in the stream drains; they
+        // fetch weights and wait for that kernel before reading or writing anything it touches
+        attr[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs++;
+    }
 #ifdef VX_GEMM_PROFILE
     if (getenv("VX_GEMM_VERBOSE")) fprintf(stderr, "gemm launch: CG=%d units=%d tiles=%d smem=%d\n", CG, units, tiles, smem);
 #endif
@@ -972,6 +1006,8 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
     p.col = a.col;
     p.status = status_ptr();
     p.alpha = 1.0f;
+    static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
+    p.early = early ? 1 : 0;
 #ifdef VX_GEMM_PROFILE
     if (const char* e = getenv("VX_GEMM_DBG")) p.dbg = atoi(e);
 #endif
