@@ -206,12 +206,45 @@ class LinearStack:
         self.qq = backend.q4_blob(m, s.q_dim // world)                  # q projection as NVFP4 (o's input)
         self.gq = backend.q4_blob(m, s.intermediate // world)           # silu(gate)*up as NVFP4 (down's input)
         self.fabric: Optional[TpFabric] = None
+        self.kv_side_streams = True
+        self._side = None
+        self._kv_pending: list = []
         self.weight_bytes = sum(v.buf.numel() for l in self.layers
                                 for v in (l.q, l.k, l.v, l.o, l.gate, l.up, l.down))
 
     def _all_reduce(self, t: torch.Tensor) -> None:
         if self.world > 1:
             torch.distributed.all_reduce(t, group=self.group)
+
+    # -- q, k, v of one input. At decode sizes they are one launch. At prefill sizes k and v go to
+    #    side streams: when a rank's projections are small (tensor parallel shards) the three
+    #    persistent GEMMs fit on the SMs side by side instead of queueing behind one another.
+    def _qkv(self, l: LayerWeights, hq, m: int, emit: bool) -> None:
+        b = self.b
+        qpart = (l.q, None, self.qq, DIV_O_IN) if emit else (l.q, self.qb, None, 0.0)
+        if m <= 16 or not self.kv_side_streams:
+            b.linears_q4(hq, DIV_NORM_OUT, [qpart, (l.k, self.kb, None, 0.0), (l.v, self.vb, None, 0.0)], m)
+            return
+        if self._side is None:
+            self._side = [torch.cuda.Stream(device=b.device), torch.cuda.Stream(device=b.device)]
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        b.linears_q4(hq, DIV_NORM_OUT, [qpart], m)
+        for side, (w, yb) in zip(self._side, ((l.k, self.kb), (l.v, self.vb))):
+            side.wait_event(ready)
+            with torch.cuda.stream(side):
+                b.linears_q4(hq, DIV_NORM_OUT, [(w, yb, None, 0.0)], m)
+                done = torch.cuda.Event()
+                done.record(side)
+            self._kv_pending.append(done)
+
+    def _join_kv(self) -> None:
+        """k and v read the norm's blob: they must be done before it is written again."""
+        main = torch.cuda.current_stream()
+        for ev in self._kv_pending:
+            main.wait_event(ev)
+        self._kv_pending.clear()
 
     def enable_fused_tp(self, m: int) -> bool:
         """Set up the symmetric buffers of the fused scatter / gather path for steps of m tokens.
@@ -241,10 +274,9 @@ class LinearStack:
                          s.norm_eps, DIV_NORM_OUT)
             nslots = world
             f.barrier()                                   # every rank's rows of the blob are in place
-            b.linear_q4_to_q4(hq, DIV_NORM_OUT, l.q, m, self.qq, DIV_O_IN)
-            b.linear_q4(hq, DIV_NORM_OUT, l.k, None, m, yb=self.kb)
-            b.linear_q4(hq, DIV_NORM_OUT, l.v, None, m, yb=self.vb)
+            self._qkv(l, hq, m, True)
             b.tp_linear_q4_scatter(self.qq, DIV_O_IN, l.o, m, f.maps, rows)
+            self._join_kv()
             f.barrier()                                   # all partial sums of o have landed
             b.tp_norm_q4(x_own, f.slots, world, rows * h, self.norm_w, f.codes_ptrs, f.atoms_ptrs, r0, rows, h,
                          s.norm_eps, DIV_NORM_OUT)
@@ -275,11 +307,8 @@ class LinearStack:
             if q4:
                 b.add_rms_norm_q4(self.x, None, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT,
                                   xb=None if first else self.pb)
-                # q feeds o directly (attention passthrough), so it is produced as o's FP4 input;
-                # q, k and v read the same blob: one call (one launch at decode sizes)
-                b.linears_q4(self.hq, DIV_NORM_OUT,
-                             [(l.q, None, self.qq, DIV_O_IN) if emit else (l.q, self.qb, None, 0.0),
-                              (l.k, self.kb, None, 0.0), (l.v, self.vb, None, 0.0)], m)
+                # q feeds o directly (attention passthrough), so it is produced as o's FP4 input
+                self._qkv(l, self.hq, m, emit)
             else:
                 b.add_rms_norm_twin(self.x, None, self.norm_w, None, self.hb, m, h, s.norm_eps,
                                     xb=None if first else self.pb)
@@ -292,6 +321,7 @@ class LinearStack:
             else:
                 b.linear_bf16(self.qb, l.o, None, m, yb=self.pb)   # attention passthrough: a = q
             self._all_reduce(self.pb[: m * h])
+            self._join_kv()
             if q4:
                 b.add_rms_norm_q4(self.x, None, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT,
                                   xb=self.pb)
