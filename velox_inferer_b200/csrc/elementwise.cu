@@ -214,31 +214,31 @@ add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x
             v[it].x += t[it].x; v[it].y += t[it].y; v[it].z += t[it].z; v[it].w += t[it].w;
         }
     } else if (xb) {
-        for (int sl = 0; sl < nslots; sl++) {
-            uint2 t[ITERS];
+        // slots are fetched four at a time (their loads in flight together) and added in slot order
+        for (int s0 = 0; s0 < nslots; s0 += 4) {
+            uint2 t[4][ITERS];
 #pragma unroll
-            for (int it = 0; it < ITERS; it++) {
-                const int c = (it * T + (int)threadIdx.x) * 4;
-                t[it] = c < dim ? __ldcs(reinterpret_cast<const uint2*>(xb + sl * slot_stride + base + c)) : make_uint2(0u, 0u);
-            }
-            if (sl == 0) {
-                // the addend of the first slot goes in as it is; further slots are summed first
+            for (int j = 0; j < 4; j++)
 #pragma unroll
                 for (int it = 0; it < ITERS; it++) {
-                    const float4 f = make_float4(__uint_as_float(t[it].x << 16), __uint_as_float(t[it].x & 0xffff0000u),
-                                                 __uint_as_float(t[it].y << 16), __uint_as_float(t[it].y & 0xffff0000u));
+                    const int c = (it * T + (int)threadIdx.x) * 4;
+                    t[j][it] = (c < dim && s0 + j < nslots)
+                                   ? __ldcs(reinterpret_cast<const uint2*>(xb + (s0 + j) * slot_stride + base + c))
+                                   : make_uint2(0u, 0u);
+                }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (s0 + j >= nslots) break;
+#pragma unroll
+                for (int it = 0; it < ITERS; it++) {
+                    const float4 f = make_float4(__uint_as_float(t[j][it].x << 16), __uint_as_float(t[j][it].x & 0xffff0000u),
+                                                 __uint_as_float(t[j][it].y << 16), __uint_as_float(t[j][it].y & 0xffff0000u));
                     if (nslots == 1) {
+                        // a single addend goes in as it is; several are summed first
                         v[it].x += f.x; v[it].y += f.y; v[it].z += f.z; v[it].w += f.w;
                     } else {
-                        sum_slots(it, f, true);
+                        sum_slots(it, f, s0 + j == 0);
                     }
-                }
-            } else {
-#pragma unroll
-                for (int it = 0; it < ITERS; it++) {
-                    const float4 f = make_float4(__uint_as_float(t[it].x << 16), __uint_as_float(t[it].x & 0xffff0000u),
-                                                 __uint_as_float(t[it].y << 16), __uint_as_float(t[it].y & 0xffff0000u));
-                    sum_slots(it, f, false);
                 }
             }
         }
