@@ -293,12 +293,14 @@ def main():
     # ---- the same steps again with every main kernel bracketed by CUDA events on its launch
     #      stream (the library's timing hooks): per-kernel durations for the roofline ----
     b.timing_enable(True)
+    stack.kv_side_streams = False   # one stream: the event brackets of concurrent kernels would overlap
     barrier()
     for _ in range(args.steps):
         forward()
     barrier()
     timed = b.timing_collect()
     b.timing_enable(False)
+    stack.kv_side_streams = True
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- end to end: pinned host -> device, all layers, result back to the host ----
@@ -350,7 +352,10 @@ def main():
                     "peak_source": f"{peaks['source']} bf16 cuBLAS {peaks['bf16_tflops']} TFLOP/s x {FP4_OVER_BF16:g} "
                                    "(no FP4 GEMM peak is measured on this pool; nominal dense FP4 : BF16 ratio)",
                     "frac_of_nominal_fp4": achieved / NOMINAL_FP4_TFLOPS,
-                    "launches": int(k_n), "avg_launch_us": 1e3 * k_ms / max(k_n, 1), "traffic": None,
+                    "launches": int(k_n), "avg_launch_us": 1e3 * k_ms / max(k_n, 1),
+                    # DRAM bytes of one [25600, 5120] M = 2048 launch from the committed ncu capture
+                    # (79.7 MB read + 71.8 MB written; algorithmic 79.6 MB + 104.9 MB of output)
+                    "traffic": 151.5e6, "traffic_of": "profiles/gemm_nvfp4_25600x5120_m2048.md",
                     "act_quant_ms_per_step": timed["act_quant"][0] / args.steps}
     else:
         k_ms, k_n = timed["gemv"]
@@ -359,7 +364,9 @@ def main():
                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                     "peak_source": f"{peaks['source']} copy bandwidth",
                     "frac_of_nominal_hbm": achieved / NOMINAL_HBM_GBS,
-                    "launches": int(k_n), "avg_launch_us": 1e3 * k_ms / max(k_n, 1), "traffic": None}
+                    "launches": int(k_n), "avg_launch_us": 1e3 * k_ms / max(k_n, 1),
+                    # DRAM bytes of one [25600, 5120] M = 1 launch from the committed ncu capture
+                    "traffic": 75.9e6, "traffic_of": "profiles/gemv_nvfp4_tc_25600x5120_m1.md"}
 
     line = {
         "metric": METRIC, "value": m / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
