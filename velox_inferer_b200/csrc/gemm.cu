@@ -972,10 +972,17 @@ static int launch(bool swiglu, const CUtensorMap& a, const CUtensorMap& b0, cons
     return pair ? launch_cfg<KIND, false, 2>(a, b0, b1, mo, p, sms) : launch_cfg<KIND, false, 1>(a, b0, b1, mo, p, sms);
 }
 
+// Device address of the status word, per device ordinal (a __device__ variable has one instance
+// per device).
 static int* status_ptr() {
-    static int* ptr = nullptr;
-    if (!ptr) cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_gemm_status);
-    return ptr;
+    static int* ptrs[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptrs[dev] && cudaGetSymbolAddress(reinterpret_cast<void**>(&ptrs[dev]), g_gemm_status) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return ptrs[dev];
 }
 
 #ifdef VX_GEMM_PROFILE
