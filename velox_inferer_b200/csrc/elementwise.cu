@@ -318,6 +318,108 @@ add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x
     }
 }
 
+// The hot form of the norm above (one bf16 addend or none, one destination, rows of dim / 8 threads
+// x two 128-bit slices): persistent blocks walk the rows and request the next row's values before
+// they finish the current one, so loads stay in flight across the reduction barrier and the
+// stores. Same arithmetic, same bytes written.
+__global__ void __launch_bounds__(1024)
+add_rms_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ xb,
+                              const float* __restrict__ weight, uint16_t* __restrict__ yb,
+                              uint8_t* __restrict__ codes, uint8_t* __restrict__ atoms, int rows, int rows_padded,
+                              int dim, float eps, float offset, float divisor) {
+    __shared__ float red[2][32];
+    const int T = (int)blockDim.x, tid = (int)threadIdx.x;
+    const int c0 = tid * 4, c1 = (T + tid) * 4;     // this thread's two slices of every row
+    if (tid == 0) grid_launch_dependents();          // a linear behind this may start fetching weights
+    const float4 w0 = *reinterpret_cast<const float4*>(weight + c0);
+    const float4 w1 = *reinterpret_cast<const float4*>(weight + c1);
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    uint2 b0 = make_uint2(0u, 0u), b1 = b0;
+    auto fetch = [&](long long r) {
+        const long long base = r * dim;
+        a0 = __ldcs(reinterpret_cast<const float4*>(acc + base + c0));
+        a1 = __ldcs(reinterpret_cast<const float4*>(acc + base + c1));
+        if (xb) {
+            b0 = __ldcs(reinterpret_cast<const uint2*>(xb + base + c0));
+            b1 = __ldcs(reinterpret_cast<const uint2*>(xb + base + c1));
+        }
+    };
+    long long row = blockIdx.x;
+    if (row < rows) fetch(row);
+    int par = 0;
+    for (; row < rows_padded; row += gridDim.x, par ^= 1) {
+        if (row >= rows) {   // rows that only complete the last 128-row scale tile
+            for (int g = tid; g < dim / 16; g += T) atoms[nvfp4_scale_offset(row, g, dim)] = 0;
+            continue;
+        }
+        float4 v[2] = {a0, a1};
+        const uint2 t[2] = {b0, b1};
+        const long long next = row + gridDim.x;
+        if (next < rows) fetch(next);   // in flight while this row is finished
+        const long long base = row * dim;
+        if (xb) {
+#pragma unroll
+            for (int it = 0; it < 2; it++) {
+                v[it].x += __uint_as_float(t[it].x << 16); v[it].y += __uint_as_float(t[it].x & 0xffff0000u);
+                v[it].z += __uint_as_float(t[it].y << 16); v[it].w += __uint_as_float(t[it].y & 0xffff0000u);
+            }
+            __stcs(reinterpret_cast<float4*>(acc + base + c0), v[0]);
+            __stcs(reinterpret_cast<float4*>(acc + base + c1), v[1]);
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int it = 0; it < 2; it++) {
+            ss = fmaf(v[it].x, v[it].x, ss); ss = fmaf(v[it].y, v[it].y, ss);
+            ss = fmaf(v[it].z, v[it].z, ss); ss = fmaf(v[it].w, v[it].w, ss);
+        }
+        ss = warp_sum(ss);
+        if (tid % VX_WARP == 0) red[par][tid / VX_WARP] = ss;
+        __syncthreads();
+        float total = 0.0f;
+        for (int i = 0; i < T / VX_WARP; i++) total += red[par][i];
+        const float inv = 1.0f / sqrtf(total / (float)dim + eps);
+#pragma unroll
+        for (int it = 0; it < 2; it++) {
+            const int c = it ? c1 : c0;
+            const float4 w = it ? w1 : w0;
+            float n[4];
+            n[0] = round_bf16(v[it].x * inv * (offset + w.x));
+            n[1] = round_bf16(v[it].y * inv * (offset + w.y));
+            n[2] = round_bf16(v[it].z * inv * (offset + w.z));
+            n[3] = round_bf16(v[it].w * inv * (offset + w.w));
+            if (yb)
+                *reinterpret_cast<uint2*>(yb + base + c) =
+                    make_uint2((__float_as_uint(n[0]) >> 16) | (__float_as_uint(n[1]) & 0xffff0000u),
+                               (__float_as_uint(n[2]) >> 16) | (__float_as_uint(n[3]) & 0xffff0000u));
+            float amax = fmaxf(fmaxf(fabsf(n[0]), fabsf(n[1])), fmaxf(fabsf(n[2]), fabsf(n[3])));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(divisor, amax), 6.0f));
+            uint32_t out = 0;
+            if (sb != 0) {
+                const float ds = e4m3_to_f32(sb);
+                const float rc = __frcp_rn(ds);
+                float q[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float a = __fmul_rn(n[i], divisor);
+                    const float q0 = __fmul_rn(a, rc);
+                    q[i] = __fmaf_rn(__fmaf_rn(-q0, ds, a), rc, q0);
+                }
+                out = f32x2_to_e2m1x2(q[0], q[1]) | (f32x2_to_e2m1x2(q[2], q[3]) << 8);
+            }
+            const uint32_t o1 = __shfl_down_sync(0xffffffffu, out, 1);
+            const uint32_t o2 = __shfl_down_sync(0xffffffffu, out, 2);
+            const uint32_t o3 = __shfl_down_sync(0xffffffffu, out, 3);
+            if ((tid & 3) == 0) {
+                *reinterpret_cast<uint2*>(codes + (base + c) / 2) =
+                    make_uint2((out & 0xffffu) | (o1 << 16), (o2 & 0xffffu) | (o3 << 16));
+                atoms[nvfp4_scale_offset(row, c / 16, dim)] = (uint8_t)sb;
+            }
+        }
+    }
+}
+
 // x_own += sum of the slots, then the rows as bf16 to every destination (the last step of a
 // sequence-parallel stack: residual add and all-gather of the result in one pass).
 __global__ void __launch_bounds__(256)
@@ -366,6 +468,21 @@ int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float*
                            reinterpret_cast<uintptr_t>(weight)) & 15) == 0 &&
                          ((reinterpret_cast<uintptr_t>(xb) | reinterpret_cast<uintptr_t>(yb) |
                            reinterpret_cast<uintptr_t>(codes)) & 7) == 0;
+    if (aligned && !x && dim % 256 == 0 && dim <= 8192) {
+        static int sms = 0;
+        if (sms == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 148;
+        }
+        const int threads = dim / 8;
+        int blocks = sms * (2048 / threads);
+        if (blocks > rows_padded) blocks = rows_padded;
+        add_rms_norm_q4_stream_kernel<<<(unsigned)blocks, threads, 0, stream()>>>(
+            acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, offset ? 1.0f : 0.0f, divisor);
+        return launch_status();
+    }
     if (aligned && dim <= 8192) {
         Q4Dest dst{};
         dst.codes[0] = codes;
