@@ -322,7 +322,8 @@ add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x
 // x two 128-bit slices): persistent blocks walk the rows and request the next row's values before
 // they finish the current one, so loads stay in flight across the reduction barrier and the
 // stores. Same arithmetic, same bytes written.
-__global__ void __launch_bounds__(1024)
+template <int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB)
 add_rms_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ xb,
                               const float* __restrict__ weight, uint16_t* __restrict__ yb,
                               uint8_t* __restrict__ codes, uint8_t* __restrict__ atoms, int rows, int rows_padded,
@@ -331,8 +332,6 @@ add_rms_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restric
     const int T = (int)blockDim.x, tid = (int)threadIdx.x;
     const int c0 = tid * 4, c1 = (T + tid) * 4;     // this thread's two slices of every row
     if (tid == 0) grid_launch_dependents();          // a linear behind this may start fetching weights
-    const float4 w0 = *reinterpret_cast<const float4*>(weight + c0);
-    const float4 w1 = *reinterpret_cast<const float4*>(weight + c1);
     float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
     uint2 b0 = make_uint2(0u, 0u), b1 = b0;
     auto fetch = [&](long long r) {
@@ -381,7 +380,7 @@ add_rms_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restric
 #pragma unroll
         for (int it = 0; it < 2; it++) {
             const int c = it ? c1 : c0;
-            const float4 w = it ? w1 : w0;
+            const float4 w = __ldg(reinterpret_cast<const float4*>(weight + c));   // L1-resident after the first row
             float n[4];
             n[0] = round_bf16(v[it].x * inv * (offset + w.x));
             n[1] = round_bf16(v[it].y * inv * (offset + w.y));
@@ -476,11 +475,31 @@ int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float*
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
             if (sms <= 0) sms = 148;
         }
+        // register budgets chosen so that about 1300-1500 threads are resident per SM: the loads of
+        // the next rows in flight are what hides the row-wide reduction barrier
         const int threads = dim / 8;
-        int blocks = sms * (2048 / threads);
-        if (blocks > rows_padded) blocks = rows_padded;
-        add_rms_norm_q4_stream_kernel<<<(unsigned)blocks, threads, 0, stream()>>>(
-            acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, offset ? 1.0f : 0.0f, divisor);
+        const float off = offset ? 1.0f : 0.0f;
+        if (threads <= 256) {
+            int blocks = sms * 6;
+            if (blocks > rows_padded) blocks = rows_padded;
+            add_rms_norm_q4_stream_kernel<256, 6><<<(unsigned)blocks, threads, 0, stream()>>>(
+                acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, off, divisor);
+        } else if (threads <= 512) {
+            int blocks = sms * 3;
+            if (blocks > rows_padded) blocks = rows_padded;
+            add_rms_norm_q4_stream_kernel<512, 3><<<(unsigned)blocks, threads, 0, stream()>>>(
+                acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, off, divisor);
+        } else if (threads <= 768) {
+            int blocks = sms * 2;
+            if (blocks > rows_padded) blocks = rows_padded;
+            add_rms_norm_q4_stream_kernel<768, 2><<<(unsigned)blocks, threads, 0, stream()>>>(
+                acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, off, divisor);
+        } else {
+            int blocks = sms;
+            if (blocks > rows_padded) blocks = rows_padded;
+            add_rms_norm_q4_stream_kernel<1024, 1><<<(unsigned)blocks, threads, 0, stream()>>>(
+                acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, off, divisor);
+        }
         return launch_status();
     }
     if (aligned && dim <= 8192) {
