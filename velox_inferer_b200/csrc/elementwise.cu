@@ -374,8 +374,9 @@ add_rms_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restric
         ss = warp_sum(ss);
         if (tid % VX_WARP == 0) red[par][tid / VX_WARP] = ss;
         __syncthreads();
-        float total = 0.0f;
-        for (int i = 0; i < T / VX_WARP; i++) total += red[par][i];
+        // every warp adds the warps' sums with one shuffle tree (a serial loop over up to 32 shared
+        // words is several hundred cycles of dependent latency per row)
+        float total = warp_sum((tid % VX_WARP) < T / VX_WARP ? red[par][tid % VX_WARP] : 0.0f);
         const float inv = 1.0f / sqrtf(total / (float)dim + eps);
 #pragma unroll
         for (int it = 0; it < 2; it++) {
