@@ -185,6 +185,51 @@ def test_linear_swiglu_decode_nvfp4_activations(b, k, w, m, order):
     assert O.max_err(out.cpu().numpy(), want) <= 5e-4
 
 
+@pytest.mark.parametrize("n,k,begin,rows,m", [
+    (64, 512, 0, 64, 9), (64, 128, 0, 64, 2), (512, 2048, 64, 384, 8), (300, 256, 0, 300, 5),
+    (160, 1024, 16, 128, 16), (1280, 4096, 0, 1280, 3),
+])
+def test_linear_decode_fp8_rows_on_tensor_cores(b, n, k, begin, rows, m):
+    """FP8-row views that admit FP8 activations decode through kind::f8f6f4: ragged row counts,
+    views starting inside a 128-row tile, K splits (long K, few tiles)."""
+    r = O.Rng(17)
+    payload = r.random_weight(FMT_O[F8], n, k)
+    x = r.vec(m * k, 1.0)
+    view = make_view(b, payload, F8, n, k, begin, rows, ActPolicy.allow_a8())
+    act = b.linear_act(view, m)
+    # two tokens and more take the tensor cores; a single token is faster on the unpacking GEMV
+    assert act == (ActQuant(ActQuant.FP8_ROW) if m >= 2 else ActQuant(ActQuant.BF16))
+    want = oracle_linear(x, payload, F8, n, k, begin, rows, m, act)
+    y = b.alloc(m * rows + 2)
+    yb = torch.zeros(m * rows, dtype=torch.bfloat16, device=y.device)
+    for _ in range(2):
+        y.zero_()
+        b.linear(b.upload(x), view, y, m, yb=yb)
+        assert b.lib.velox_sm100_debug_status() == 0
+        got = y.cpu().numpy()
+        assert got[-2:].tolist() == [0.0, 0.0]
+        got = got[:-2].reshape(m, rows)
+        e_conf, e_rms = both_metrics(got, want)
+        assert e_conf <= LINEAR_TOL and e_rms <= RMS_TOL, (e_conf, e_rms)
+        assert np.array_equal(bf16_bits(yb).reshape(-1), f32_to_bf16_bits(got.reshape(-1)))
+
+
+def test_linear_swiglu_decode_fp8_rows(b):
+    r = O.Rng(0x5e3)
+    k, w, m = 512, 128, 4
+    x = r.vec(m * k, 1.0)
+    p = r.random_weight(FMT_O[F8], 2 * w, k)
+    parent = WeightView.full(b.upload_bytes(p), F8, 2 * w, k).with_act(ActPolicy.allow_a8())
+    gate, up = parent.rows_view(0, w), parent.rows_view(w, w)
+    act = b.linear_swiglu_act(gate, up, m)
+    assert act == ActQuant(ActQuant.FP8_ROW)
+    want = _swiglu_want(x, p, p, F8, 2 * w, 2 * w, k, 0, w, w, m, act)
+    out = b.alloc(m * w)
+    b.linear_swiglu(b.upload(x), gate, up, out, m)
+    assert b.lib.velox_sm100_debug_status() == 0
+    assert O.max_err(out.cpu().numpy(), want) <= 5e-4
+
+
 def test_portable_signature_entry_point(b):
     # velox_sm100_linear has velox_portable_linear's signature (portable.rs:81-91)
     n, k, m = 256, 512, 4

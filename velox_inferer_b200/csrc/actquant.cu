@@ -18,6 +18,7 @@ quantize_fp8row_kernel(const float* __restrict__ x, const uint16_t* __restrict__
                        uint8_t* __restrict__ codes, float* __restrict__ scales) {
     __shared__ float red[8];
     const long long row = blockIdx.x;
+    if (threadIdx.x == 0) grid_launch_dependents();   // the linear behind this may start fetching weights
     float amax = 0.0f;
     for (long long c = threadIdx.x; c < k; c += blockDim.x)
         amax = fmaxf(amax, fabsf(load_act(x, xb, row * k + c)));

@@ -100,6 +100,14 @@ struct Plan {
 // Kernel and activation rounding for one view at m rows. The rounding never exceeds the view's
 // policy (crates/velox-conformance/src/lib.rs:64-74): bf16 is always permitted; FP8 rows need
 // AllowA8 or AllowA4; NVFP4 activations need AllowA4 and use its divisor.
+static int fp8_tc_min_m() {
+    static const int v = []() {
+        const char* e = getenv("VELOX_SM100_FP8_TC_MIN_M");
+        return e && atoi(e) > 0 ? atoi(e) : 2;
+    }();
+    return v;
+}
+
 static Plan plan_for(const velox_sm100_view& v, int m) {
     Plan p{PATH_GENERIC, VELOX_ACT_EXACT, 0.0f};
     if (v.k % 64 != 0) return p;
@@ -111,6 +119,13 @@ static Plan plan_for(const velox_sm100_view& v, int m) {
             p.path = PATH_GEMV_TC;
             p.act = VELOX_ACT_NVFP4;
             p.divisor = v.divisor;
+            return p;
+        }
+        // (for a single token the unpacking GEMV still wins against quantiser + tensor-core launch)
+        if (v.format == VELOX_FMT_FP8_ROW_BF16 && v.policy != VELOX_POLICY_A16_ONLY && v.k % 128 == 0 &&
+            m >= fp8_tc_min_m() && gemm_available() && !getenv("VELOX_SM100_DECODE_BF16")) {
+            p.path = PATH_GEMV_TC;
+            p.act = VELOX_ACT_FP8_ROW;
             return p;
         }
         p.path = PATH_GEMV;
@@ -155,7 +170,7 @@ static int run(const LinearArgs& a, const Plan& p) {
             rc = gemv(a);
             break;
         case PATH_GEMV_TC:
-            rc = gemv_nvfp4_tc(a, p.divisor);
+            rc = gemv_tc(a, p.act, p.divisor);
             break;
         case PATH_GEMM_A4:
         case PATH_GEMM_A8:

@@ -22,9 +22,10 @@ int gemm_make_map_u8(CUtensorMap* map, const void* ptr, long long rows, long lon
 
 int gemm_make_rs_maps(void* maps_dev, const unsigned long long* ptrs, int n, int rows_per_owner, long long cols);
 
-// NVFP4 decode linear (m <= 16) on the block-scaled tensor cores, activations quantised to NVFP4
-// with `divisor` (or taken from a.q_codes / a.q_atoms). VELOX_ERR_UNSUPPORTED for other shapes.
-int gemv_nvfp4_tc(const LinearArgs& a, float divisor);
+// Decode linear (m <= 16) on the tensor cores: NVFP4 views with activations quantised to NVFP4 with
+// `divisor` (or taken from a.q_codes / a.q_atoms), or FP8-row views with FP8-row activations (`act`
+// says which). VELOX_ERR_UNSUPPORTED for other shapes.
+int gemv_tc(const LinearArgs& a, int act, float divisor);
 // The same for up to three views of one width that share the activations, in one launch.
 int gemv_nvfp4_tc_parts(const LinearArgs* parts, int n, float divisor);
 

@@ -1,4 +1,4 @@
-// NVFP4 decode linear (m <= 16 tokens) on the block-scaled tensor cores.
+// Decode linear (m <= 16 tokens) on the tensor cores: NVFP4 weights (block-scaled MMA) and FP8 rows.
 //
 // Decode is a byte stream: 0.5625 B per weight, every byte once. The SIMT/mma.sync GEMV spends
 // about 1.6 issue slots per weight on unpacking (E2M1 -> f16, times the block scale) and is bound
@@ -19,6 +19,9 @@
 //   warp 2      scale producer (bulk copies of whole atoms, W then x);
 //   warps 4-7   epilogue: tcgen05.ld, K-split fix-up, per-tensor factors, optional silu(gate)*up;
 //   warps 8-11  scale movers: shared memory -> tensor memory (tcgen05.st), one per lane quadrant.
+// FP8-E4M3 rows with FP8-row activations (ActQuant::Fp8Row, views that admit it) take the same
+// route without the scale roles: kind::f8f6f4, 128 k per stage, the bf16 row scale and the f32
+// token scale applied in the epilogue.
 // Every mbarrier wait is bounded; a wait that gives up records a code in the status word.
 //
 // Reference counterpart: linear_gemv_vec_kernel, crates/velox-cuda/kernels/portable_model.cu:1448-1626.
@@ -76,6 +79,8 @@ struct DtParams {
     long long per_cta;           // (tile, k-block) steps per CTA; CTA c takes steps [c * per_cta, (c + 1) * per_cta)
     const uint8_t* sfx;
     float alpha;                 // 1 / activation divisor
+    const uint16_t* rowscale[DT_MAX_PARTS];   // FP8 rows: bf16 scale per weight row
+    const float* tokscale;                     // FP8 rows: f32 scale per token
     float* partial;              // [CTAs][2][V][128][16]: a CTA's first and last run can be partial tiles
     int* tickets;                // [tiles], zero between launches
     int* status;
@@ -83,7 +88,7 @@ struct DtParams {
 
 __device__ int g_gemv_tc_status = 0;
 
-template <bool SWIGLU>
+template <bool SWIGLU, int KIND>
 __global__ void __launch_bounds__(DT_THREADS, 1)
 gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
                      const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_x,
@@ -223,7 +228,9 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         bool ok = true;
         const bool leader = elect_one();
         // M = 128, N = 16, E2M1 x E2M1 with UE4M3 block scales, K-major operands, f32 accumulate
-        const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        const uint32_t shape = ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        const uint32_t idesc = KIND == KIND_MXF4 ? ((1u << 7) | (1u << 10) | shape)   // E2M1 x E2M1, UE4M3 scales
+                                                 : ((1u << 4) | shape);                // E4M3 x E4M3 -> f32
         int n = 0;
         for (long long u = u_begin; u < u_end && ok; n++) {
             const Piece pc = piece_at(u);
@@ -237,7 +244,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
             for (int v = 0; v < V && ok; v++) {
                 const uint32_t d = tmem + buf * DT_ACC_COLS + v * 16;
                 for (int kb = kb0; kb < kb1; kb++) {
-                    if (!mbar_wait(op_full(stage), phase) || !mbar_wait(tsf_full(stage), phase)) {
+                    if (!mbar_wait(op_full(stage), phase) || (KIND == KIND_MXF4 && !mbar_wait(tsf_full(stage), phase))) {
                         if (leader) atomicExch(p.status, 23);
                         ok = false;
                         break;
@@ -249,10 +256,10 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                     const uint32_t tsf = tmem + DT_SF_COL + stage * DT_SF_SET;
                     if (leader) {
                         for (int j = 0; j < steps; j++)
-                            tc_mma<KIND_MXF4, 1>(d, da + 2u * j, db + 2u * j, idesc, (kb != kb0 || j != 0) ? 1u : 0u,
+                            tc_mma<KIND, 1>(d, da + 2u * j, db + 2u * j, idesc, (kb != kb0 || j != 0) ? 1u : 0u,
                                                  tsf + 4 * j, tsf + 16 + 4 * j);
                         tc_commit(op_empty(stage));
-                        tc_commit(tsf_empty(stage));
+                        if (KIND == KIND_MXF4) tc_commit(tsf_empty(stage));
                     }
                     if (++stage == DT_STAGES) {
                         stage = 0;
@@ -262,7 +269,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
             }
             if (ok && leader) tc_commit(acc_full(buf));
         }
-    } else if (warp == 2) {
+    } else if (KIND == KIND_MXF4 && warp == 2) {
         // ---------------- scale producer ----------------
         // (weight atoms at once, activation atoms after the preceding grid, as the operand producer)
         int stage = 0;
@@ -313,7 +320,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         }
         if (!waited) after_dependency();
         if (!ok) __nanosleep(200000);
-    } else if (warp >= 8) {
+    } else if (KIND == KIND_MXF4 && warp >= 8) {
         // ---------------- scale movers ----------------
         // Lane i of the warp serving lane quadrant q writes atom rows i, i+32, i+64, i+96: the 16
         // bytes of atom row i are that atom's four 32-bit columns, replicated in every quadrant.
@@ -361,7 +368,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                 }
             }
         }
-    } else if (warp >= 4) {
+    } else if (warp >= 4 && warp < 8) {
         // ---------------- epilogue ----------------
         const int quad = warp % 4;
         const int row_in_tile = quad * 32 + lane;
@@ -446,17 +453,25 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                 int lt = tile;
                 const int idx = SWIGLU ? 0 : part_of(tile, lt);
                 const DtOut& o = p.out[idx];
-                const float f0 = p.alpha / *p.wdiv[idx];
-                const float f1 = SWIGLU ? p.alpha / *p.wdiv[1] : 0.0f;
                 const long long row = (p.tile0[idx] + lt) * 128 + row_in_tile;
                 const bool row_ok = row >= o.valid_begin && row < o.valid_end;
                 const long long o0 = o.col + (row - o.valid_begin);
+                float f0, f1 = 0.0f;
+                if (KIND == KIND_MXF4) {
+                    f0 = p.alpha / *p.wdiv[idx];
+                    if (SWIGLU) f1 = p.alpha / *p.wdiv[1];
+                } else {
+                    // row scales; the matching up row sits at the same offset from its view's start
+                    f0 = row_ok ? bf16_bits_to_f32(p.rowscale[idx][row]) : 0.0f;
+                    if (SWIGLU) f1 = row_ok ? bf16_bits_to_f32(p.rowscale[1][(p.tile0[1] + lt) * 128 + row_in_tile]) : 0.0f;
+                }
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     if (j < p.m) {   // uniform across the warp
-                        float val = acc[0][j] * f0;
+                        const float ts = KIND == KIND_MXF4 ? 1.0f : p.tokscale[j];
+                        float val = acc[0][j] * f0 * ts;
                         if (SWIGLU) {
-                            const float u = acc[V - 1][j] * f1;
+                            const float u = acc[V - 1][j] * f1 * ts;
                             val = val / (1.0f + __expf(-val)) * u;
                         }
                         if (row_ok) {
@@ -533,44 +548,64 @@ int gemv_tc_status_sync() {
 }
 
 // One launch for `n` views of the same parent width that read the same activations (n = 1 is the
-// plain linear; the fused SwiGLU pair is a single LinearArgs with swiglu set and n = 1).
-int gemv_nvfp4_tc_parts(const LinearArgs* parts, int n, float divisor) {
+// plain linear; the fused SwiGLU pair is a single LinearArgs with swiglu set and n = 1). `act` is
+// VELOX_ACT_NVFP4 (NVFP4 views, `divisor`) or VELOX_ACT_FP8_ROW (FP8-row views).
+int gemv_tc_parts(const LinearArgs* parts, int n, int act, float divisor) {
     if (!gemm_available() || n < 1 || n > DT_MAX_PARTS) return VELOX_ERR_UNSUPPORTED;
     const LinearArgs& a = parts[0];
     const bool sw = a.swiglu != 0;
+    const bool f8 = act == VELOX_ACT_FP8_ROW;
+    if (!f8 && act != VELOX_ACT_NVFP4) return VELOX_ERR_UNSUPPORTED;
     if (sw && n != 1) return VELOX_ERR_UNSUPPORTED;
     const long long k = a.w.k;
-    if (a.m < 1 || a.m > 16 || k % 64 != 0 || !(divisor > 0.0f)) return VELOX_ERR_UNSUPPORTED;
-
-    const uint8_t* codes = a.q_codes;
-    const uint8_t* atoms = a.q_atoms;
-    int rc;
-    if (!codes || !atoms) {
-        uint8_t* c = static_cast<uint8_t*>(scratch(SCRATCH_ACT_CODES, (size_t)a.m * k / 2));
-        uint8_t* s = static_cast<uint8_t*>(scratch(SCRATCH_ACT_SCALES, (size_t)128 * k / 16));
-        if (!c || !s) return (int)cudaErrorMemoryAllocation;
-        if ((rc = quantize_act_nvfp4(a.x, a.xb, a.m, k, divisor, c, s)) != 0) return rc;
-        codes = c;
-        atoms = s;
-    }
+    if (a.m < 1 || a.m > 16) return VELOX_ERR_UNSUPPORTED;
+    if (f8 ? (k % 128 != 0 || a.q_codes) : (k % 64 != 0 || !(divisor > 0.0f))) return VELOX_ERR_UNSUPPORTED;
 
     DtParams p{};
+    const uint8_t* codes = a.q_codes;
+    int rc;
+    if (f8) {
+        uint8_t* c = static_cast<uint8_t*>(scratch(SCRATCH_ACT_CODES, (size_t)a.m * k));
+        float* sc = static_cast<float*>(scratch(SCRATCH_ACT_SCALES, 16 * sizeof(float)));
+        if (!c || !sc) return (int)cudaErrorMemoryAllocation;
+        if ((rc = quantize_act_fp8row(a.x, a.xb, a.m, k, c, sc)) != 0) return rc;
+        codes = c;
+        p.tokscale = sc;
+        p.k_steps = (int)(k / 32);
+    } else {
+        const uint8_t* atoms = a.q_atoms;
+        if (!codes || !atoms) {
+            uint8_t* c = static_cast<uint8_t*>(scratch(SCRATCH_ACT_CODES, (size_t)a.m * k / 2));
+            uint8_t* s = static_cast<uint8_t*>(scratch(SCRATCH_ACT_SCALES, (size_t)128 * k / 16));
+            if (!c || !s) return (int)cudaErrorMemoryAllocation;
+            if ((rc = quantize_act_nvfp4(a.x, a.xb, a.m, k, divisor, c, s)) != 0) return rc;
+            codes = c;
+            atoms = s;
+        }
+        p.sfx = atoms;
+        p.alpha = 1.0f / divisor;
+        p.k_steps = (int)(k / 64);
+    }
+    const long long row_bytes = f8 ? k : k / 2;
     p.m = a.m;
-    p.k_steps = (int)(k / 64);
     p.k_blocks = (p.k_steps + 3) / 4;
     p.k_tiles64 = k / 64;
-    p.sfx = atoms;
-    p.alpha = 1.0f / divisor;
     p.status = gemv_tc_status_ptr();
     if (!p.status) return VELOX_ERR_UNSUPPORTED;
 
     CUtensorMap mw[DT_MAX_PARTS], mx;
     auto set_weights = [&](int i, const velox_sm100_view& v) -> int {
-        if (v.format != VELOX_FMT_NVFP4 || v.k != k || (reinterpret_cast<uintptr_t>(v.w) & 15)) return VELOX_ERR_UNSUPPORTED;
+        if (v.format != (f8 ? VELOX_FMT_FP8_ROW_BF16 : VELOX_FMT_NVFP4) || v.k != k ||
+            (reinterpret_cast<uintptr_t>(v.w) & 15))
+            return VELOX_ERR_UNSUPPORTED;
         p.tile0[i] = v.row_begin / 128;
-        p.sfw[i] = v.w + align256(v.n * k / 2);
-        p.wdiv[i] = reinterpret_cast<const float*>(p.sfw[i] + v.n * k / 16);
-        return gemm_make_map_u8(&mw[i], v.w, v.n, k / 2, 128);
+        if (f8) {
+            p.rowscale[i] = reinterpret_cast<const uint16_t*>(v.w + align256(v.n * k));
+        } else {
+            p.sfw[i] = v.w + align256(v.n * k / 2);
+            p.wdiv[i] = reinterpret_cast<const float*>(p.sfw[i] + v.n * k / 16);
+        }
+        return gemm_make_map_u8(&mw[i], v.w, v.n, row_bytes, 128);
     };
     auto set_out = [&](int i, const LinearArgs& l) -> int {
         const velox_sm100_view& v = l.w;
@@ -583,7 +618,8 @@ int gemv_nvfp4_tc_parts(const LinearArgs* parts, int n, float divisor) {
         o.col = l.col;
         if (l.qo_codes) {
             // whole 16-wide groups of whole rows of the quantised matrix, starting at column 0
-            if (!l.qo_atoms || !(l.qo_divisor > 0.0f) || l.col != 0 || v.row_begin % 128 != 0 || v.rows % 64 != 0 || l.y)
+            if (f8 || !l.qo_atoms || !(l.qo_divisor > 0.0f) || l.col != 0 || v.row_begin % 128 != 0 ||
+                v.rows % 64 != 0 || l.y)
                 return VELOX_ERR_UNSUPPORTED;
             o.q_codes = l.qo_codes;
             o.q_atoms = l.qo_atoms;
@@ -610,7 +646,7 @@ int gemv_nvfp4_tc_parts(const LinearArgs* parts, int n, float divisor) {
         for (int i = n; i < DT_MAX_PARTS; i++) mw[i] = mw[0];
         p.nparts = n;
     }
-    if ((rc = gemm_make_map_u8(&mx, codes, a.m, k / 2, 16)) != 0) return rc;
+    if ((rc = gemm_make_map_u8(&mx, codes, a.m, row_bytes, 16)) != 0) return rc;
 
     static int sms = 0;
     if (sms == 0) {
@@ -648,21 +684,23 @@ int gemv_nvfp4_tc_parts(const LinearArgs* parts, int n, float divisor) {
     static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
     cfg.attrs = attr;
     cfg.numAttrs = early ? 1 : 0;
-    if (sw) {
-        auto kern = gemv_nvfp4_tc_kernel<true>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaLaunchKernelEx(&cfg, kern, mw[0], mw[1], mw[2], mx, p);
-    } else {
-        auto kern = gemv_nvfp4_tc_kernel<false>;
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM_BYTES);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaLaunchKernelEx(&cfg, kern, mw[0], mw[1], mw[2], mx, p);
-    }
+    auto go = [&](auto kern) {
+        cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM_BYTES);
+        if (err != cudaSuccess) return err;
+        return cudaLaunchKernelEx(&cfg, kern, mw[0], mw[1], mw[2], mx, p);
+    };
+    if (f8)
+        e = sw ? go(gemv_nvfp4_tc_kernel<true, KIND_F8>) : go(gemv_nvfp4_tc_kernel<false, KIND_F8>);
+    else
+        e = sw ? go(gemv_nvfp4_tc_kernel<true, KIND_MXF4>) : go(gemv_nvfp4_tc_kernel<false, KIND_MXF4>);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
 
-int gemv_nvfp4_tc(const LinearArgs& a, float divisor) { return gemv_nvfp4_tc_parts(&a, 1, divisor); }
+int gemv_nvfp4_tc_parts(const LinearArgs* parts, int n, float divisor) {
+    return gemv_tc_parts(parts, n, VELOX_ACT_NVFP4, divisor);
+}
+
+int gemv_tc(const LinearArgs& a, int act, float divisor) { return gemv_tc_parts(&a, 1, act, divisor); }
 
 }  // namespace vx
