@@ -98,14 +98,14 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def cpu_baseline_sample(spec, m_tokens: int, seconds_target: float = 12.0):
+def cpu_baseline_sample(spec, m_tokens: int, seconds_target: float = 12.0, threads: int = 0):
     """The CPU oracle (row-parallel over all host threads, f64 accumulation, same arithmetic as the
     reference's velox-cpu) on a bounded sample: a row slice of one gate projection. Returns
     (tokens/s the whole stack would reach at that MAC rate, cores, description)."""
     import numpy as np
     from oracle import oracle as O
 
-    cores = os.cpu_count() or 1
+    cores = threads if threads > 0 else (os.cpu_count() or 1)
     k, n = spec.hidden, 256
     rng = np.random.default_rng(0)
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
@@ -114,13 +114,13 @@ def cpu_baseline_sample(spec, m_tokens: int, seconds_target: float = 12.0):
     x = rng.standard_normal((m, k)).astype(np.float32)
     # calibrate, then size the sample to the time target
     t0 = time.perf_counter()
-    O.linear(x, payload, O.FMT_NVFP4, n, k, 0, n, m, threads=0, act=O.ACT_NVFP4 if m_tokens > 16 else O.ACT_BF16,
-             divisor=256.0)
+    O.linear(x, payload, O.FMT_NVFP4, n, k, 0, n, m, threads=threads,
+             act=O.ACT_NVFP4 if m_tokens > 16 else O.ACT_BF16, divisor=256.0)
     dt = max(time.perf_counter() - t0, 1e-4)
-    reps = max(1, min(400, int(seconds_target / dt)))
+    reps = max(1, min(20000, int(seconds_target / dt)))
     t0 = time.perf_counter()
     for _ in range(reps):
-        O.linear(x, payload, O.FMT_NVFP4, n, k, 0, n, m, threads=0,
+        O.linear(x, payload, O.FMT_NVFP4, n, k, 0, n, m, threads=threads,
                  act=O.ACT_NVFP4 if m_tokens > 16 else O.ACT_BF16, divisor=256.0)
     dt = time.perf_counter() - t0
     macs = reps * m * n * k
@@ -384,7 +384,10 @@ def main():
         line["components"] = components(b, peaks)
     if world == 1 and not args.no_cpu_baseline:
         tok_s, cores, sample, _ = cpu_baseline_sample(spec, m)
-        line["cpu_baseline"] = {"value": tok_s, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        # the reference's own CPU backend is single-threaded: the same sample on one thread beside it
+        tok_1, _, sample_1, _ = cpu_baseline_sample(spec, m, seconds_target=4.0, threads=1)
+        line["cpu_baseline"] = {"value": tok_s, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                                "single_thread": {"value": tok_1, "unit": UNIT, "cores": 1, "sample": sample_1}}
     else:
         line["cpu_baseline"] = None
     print(json.dumps(line), flush=True)
