@@ -234,10 +234,16 @@ __device__ __forceinline__ void accum_q4k(const uint8_t* __restrict__ w, long lo
                 for (int j = 0; j < GEMV_R; j++) {
                     const uint4 q = qs[j][cc >> 1];
                     const uint32_t w0 = (cc & 1) ? q.z : q.x, w1 = (cc & 1) ? q.w : q.y;
+                    // the four nibbles of a word at once; each then becomes a float with one byte
+                    // permute (nibble into the mantissa of 2^23) and one subtraction, instead of
+                    // an integer-to-float conversion, which issues at a fraction of the FMA rate
+                    const uint32_t n0 = (half ? (w0 >> 4) : w0) & 0x0f0f0f0fu;
+                    const uint32_t n1 = (half ? (w1 >> 4) : w1) & 0x0f0f0f0fu;
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
-                        const uint32_t byte = ((e < 4 ? w0 : w1) >> (8 * (e & 3))) & 0xffu;
-                        const float qv = (float)(half ? (byte >> 4) : (byte & 0xfu));
+                        const float qv =
+                            __uint_as_float(__byte_perm(e < 4 ? n0 : n1, 0x4B000000u, 0x7440u | (uint32_t)(e & 3))) -
+                            8388608.0f;
 #pragma unroll
                         for (int t = 0; t < MT; t++) qx[j][t] = fmaf(qv, xv[t][e], qx[j][t]);
                     }
