@@ -3,6 +3,8 @@
 // computes these in f64 (crates/velox-cpu/src/lib.rs:188-230, 688-707), results agree to f32
 // rounding. Reference kernels: crates/velox-cuda/kernels/portable.cu:109-115, 1519-1550;
 // portable_model.cu:2011-2022.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -332,6 +334,7 @@ add_rms_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restric
     const int T = (int)blockDim.x, tid = (int)threadIdx.x;
     const int c0 = tid * 4, c1 = (T + tid) * 4;     // this thread's two slices of every row
     if (tid == 0) grid_launch_dependents();          // a linear behind this may start fetching weights
+    grid_dependency_wait();   // launched with early start allowed: everything it reads comes from the kernel ahead
     float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
     uint2 b0 = make_uint2(0u, 0u), b1 = b0;
     auto fetch = [&](long long r) {
@@ -480,27 +483,34 @@ int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float*
         // the next rows in flight are what hides the row-wide reduction barrier
         const int threads = dim / 8;
         const float off = offset ? 1.0f : 0.0f;
-        if (threads <= 256) {
-            int blocks = sms * 6;
+        // early start allowed: the launch overlaps the tail of the kernel ahead (the kernel waits
+        // for it before its first load)
+        cudaLaunchConfig_t cfg{};
+        cfg.blockDim = dim3(threads);
+        cfg.stream = stream();
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
+        cfg.attrs = attr;
+        cfg.numAttrs = early ? 1 : 0;
+        auto go = [&](auto kern, int per_sm) {
+            int blocks = sms * per_sm;
             if (blocks > rows_padded) blocks = rows_padded;
-            add_rms_norm_q4_stream_kernel<256, 6><<<(unsigned)blocks, threads, 0, stream()>>>(
-                acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, off, divisor);
-        } else if (threads <= 512) {
-            int blocks = sms * 3;
-            if (blocks > rows_padded) blocks = rows_padded;
-            add_rms_norm_q4_stream_kernel<512, 3><<<(unsigned)blocks, threads, 0, stream()>>>(
-                acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, off, divisor);
-        } else if (threads <= 768) {
-            int blocks = sms * 2;
-            if (blocks > rows_padded) blocks = rows_padded;
-            add_rms_norm_q4_stream_kernel<768, 2><<<(unsigned)blocks, threads, 0, stream()>>>(
-                acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, off, divisor);
-        } else {
-            int blocks = sms;
-            if (blocks > rows_padded) blocks = rows_padded;
-            add_rms_norm_q4_stream_kernel<1024, 1><<<(unsigned)blocks, threads, 0, stream()>>>(
-                acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, off, divisor);
-        }
+            cfg.gridDim = dim3(blocks);
+            return cudaLaunchKernelEx(&cfg, kern, acc, xb, weight, yb, codes, atoms, rows, rows_padded, dim, eps, off,
+                                      divisor);
+        };
+        cudaError_t e;
+        if (threads <= 256)
+            e = go(add_rms_norm_q4_stream_kernel<256, 6>, 6);
+        else if (threads <= 512)
+            e = go(add_rms_norm_q4_stream_kernel<512, 3>, 3);
+        else if (threads <= 768)
+            e = go(add_rms_norm_q4_stream_kernel<768, 2>, 2);
+        else
+            e = go(add_rms_norm_q4_stream_kernel<1024, 1>, 1);
+        if (e != cudaSuccess) return (int)e;
         return launch_status();
     }
     if (aligned && dim <= 8192) {
