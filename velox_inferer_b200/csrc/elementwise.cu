@@ -423,6 +423,111 @@ add_rms_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restric
     }
 }
 
+// The sequence-parallel norm in the same persistent, fetch-ahead form: NS partial-sum slots added in
+// slot order, the NVFP4 row written at row0 + row of every destination blob. (One block per SM:
+// a rank owns few rows and the slots' values take the registers.)
+template <int NS>
+__global__ void __launch_bounds__(1024, 1)
+sp_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ slots, long long slot_stride,
+                         const float* __restrict__ weight, const Q4Dest dst, long long row0, int rows, int dim,
+                         float eps, float offset, float divisor) {
+    __shared__ float red[2][32];
+    const int T = (int)blockDim.x, tid = (int)threadIdx.x;
+    const int c0 = tid * 4, c1 = (T + tid) * 4;
+    if (tid == 0) grid_launch_dependents();
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+    uint2 b0[NS], b1[NS];
+    auto fetch = [&](long long r) {
+        const long long base = r * dim;
+        a0 = __ldcs(reinterpret_cast<const float4*>(acc + base + c0));
+        a1 = __ldcs(reinterpret_cast<const float4*>(acc + base + c1));
+#pragma unroll
+        for (int sl = 0; sl < NS; sl++) {
+            b0[sl] = __ldcs(reinterpret_cast<const uint2*>(slots + sl * slot_stride + base + c0));
+            b1[sl] = __ldcs(reinterpret_cast<const uint2*>(slots + sl * slot_stride + base + c1));
+        }
+    };
+    long long row = blockIdx.x;
+    if (row < rows) fetch(row);
+    int par = 0;
+    for (; row < rows; row += gridDim.x, par ^= 1) {
+        float4 v[2] = {a0, a1};
+        float4 part[2];
+#pragma unroll
+        for (int it = 0; it < 2; it++) {
+#pragma unroll
+            for (int sl = 0; sl < NS; sl++) {
+                const uint2 t = it ? b1[sl] : b0[sl];
+                const float4 f = make_float4(__uint_as_float(t.x << 16), __uint_as_float(t.x & 0xffff0000u),
+                                             __uint_as_float(t.y << 16), __uint_as_float(t.y & 0xffff0000u));
+                if (sl == 0) {
+                    part[it] = f;
+                } else {
+                    part[it].x += f.x; part[it].y += f.y; part[it].z += f.z; part[it].w += f.w;
+                }
+            }
+        }
+        const long long next = row + gridDim.x;
+        if (next < rows) fetch(next);   // in flight while this row is finished
+        const long long base = row * dim, obase = (row0 + row) * dim;
+#pragma unroll
+        for (int it = 0; it < 2; it++) {
+            v[it].x += part[it].x; v[it].y += part[it].y; v[it].z += part[it].z; v[it].w += part[it].w;
+        }
+        __stcs(reinterpret_cast<float4*>(acc + base + c0), v[0]);
+        __stcs(reinterpret_cast<float4*>(acc + base + c1), v[1]);
+        float ss = 0.0f;
+#pragma unroll
+        for (int it = 0; it < 2; it++) {
+            ss = fmaf(v[it].x, v[it].x, ss); ss = fmaf(v[it].y, v[it].y, ss);
+            ss = fmaf(v[it].z, v[it].z, ss); ss = fmaf(v[it].w, v[it].w, ss);
+        }
+        ss = warp_sum(ss);
+        if (tid % VX_WARP == 0) red[par][tid / VX_WARP] = ss;
+        __syncthreads();
+        const float total = warp_sum((tid % VX_WARP) < T / VX_WARP ? red[par][tid % VX_WARP] : 0.0f);
+        const float inv = 1.0f / sqrtf(total / (float)dim + eps);
+#pragma unroll
+        for (int it = 0; it < 2; it++) {
+            const int c = it ? c1 : c0;
+            const float4 w = __ldg(reinterpret_cast<const float4*>(weight + c));
+            float n[4];
+            n[0] = round_bf16(v[it].x * inv * (offset + w.x));
+            n[1] = round_bf16(v[it].y * inv * (offset + w.y));
+            n[2] = round_bf16(v[it].z * inv * (offset + w.z));
+            n[3] = round_bf16(v[it].w * inv * (offset + w.w));
+            float amax = fmaxf(fmaxf(fabsf(n[0]), fabsf(n[1])), fmaxf(fabsf(n[2]), fabsf(n[3])));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(divisor, amax), 6.0f));
+            uint32_t out = 0;
+            if (sb != 0) {
+                const float ds = e4m3_to_f32(sb);
+                const float rc = __frcp_rn(ds);
+                float q[4];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float a = __fmul_rn(n[i], divisor);
+                    const float q0 = __fmul_rn(a, rc);
+                    q[i] = __fmaf_rn(__fmaf_rn(-q0, ds, a), rc, q0);
+                }
+                out = f32x2_to_e2m1x2(q[0], q[1]) | (f32x2_to_e2m1x2(q[2], q[3]) << 8);
+            }
+            const uint32_t o1 = __shfl_down_sync(0xffffffffu, out, 1);
+            const uint32_t o2 = __shfl_down_sync(0xffffffffu, out, 2);
+            const uint32_t o3 = __shfl_down_sync(0xffffffffu, out, 3);
+            if ((tid & 3) == 0) {
+                const uint2 pk = make_uint2((out & 0xffffu) | (o1 << 16), (o2 & 0xffffu) | (o3 << 16));
+                const long long soff = nvfp4_scale_offset(row0 + row, c / 16, dim);
+                for (int d = 0; d < dst.n; d++) {
+                    *reinterpret_cast<uint2*>(dst.codes[d] + (obase + c) / 2) = pk;
+                    dst.atoms[d][soff] = (uint8_t)sb;
+                }
+            }
+        }
+    }
+}
+
 // x_own += sum of the slots, then the rows as bf16 to every destination (the last step of a
 // sequence-parallel stack: residual add and all-gather of the result in one pass).
 __global__ void __launch_bounds__(256)
@@ -537,6 +642,29 @@ int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_str
         dst.atoms[d] = atoms[d];
     }
     dst.n = ndst;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(slots) & 7) == 0 && slot_stride % 4 == 0;
+    if (aligned && dim % 256 == 0 && (nslots == 2 || nslots == 4 || nslots == 8)) {
+        static int sms = 0;
+        if (sms == 0) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 148;
+        }
+        const int blocks = rows < sms ? rows : sms;
+        const float off = offset ? 1.0f : 0.0f;
+        if (nslots == 2)
+            sp_norm_q4_stream_kernel<2><<<blocks, dim / 8, 0, stream()>>>(acc, slots, slot_stride, weight, dst, row0, rows,
+                                                                            dim, eps, off, divisor);
+        else if (nslots == 4)
+            sp_norm_q4_stream_kernel<4><<<blocks, dim / 8, 0, stream()>>>(acc, slots, slot_stride, weight, dst, row0, rows,
+                                                                            dim, eps, off, divisor);
+        else
+            sp_norm_q4_stream_kernel<8><<<blocks, dim / 8, 0, stream()>>>(acc, slots, slot_stride, weight, dst, row0, rows,
+                                                                            dim, eps, off, divisor);
+        return launch_status();
+    }
     return launch_norm_q4(acc, nullptr, nslots > 0 ? slots : nullptr, nslots, slot_stride, weight, nullptr, dst, row0,
                           rows, rows, dim, eps, offset, divisor);
 }
