@@ -105,7 +105,11 @@ def cpu_baseline_sample(spec, m_tokens: int, seconds_target: float = 12.0, threa
     import numpy as np
     from oracle import oracle as O
 
-    cores = threads if threads > 0 else (os.cpu_count() or 1)
+    # an explicit count: launchers such as torchrun export OMP_NUM_THREADS=1, which would otherwise
+    # turn "all host threads" into one
+    cores = threads if threads > 0 else (len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity")
+                                         else (os.cpu_count() or 1))
+    threads = cores
     k, n = spec.hidden, 256
     rng = np.random.default_rng(0)
     w = (rng.standard_normal((n, k)) * 0.02).astype(np.float32)
