@@ -69,3 +69,73 @@ def test_two_rank_megatron_split_matches_unsharded_oracle(tmp_path):
     port = 29500 + os.getpid() % 2000
     mp.spawn(_rank_main, args=(2, port, out), nprocs=2, join=True)
     assert float(open(out).read()) <= 1e-6
+
+
+def _bf16(a):
+    return O.quantize_activations(np.asarray(a, dtype=np.float32).reshape(-1), 1, O.ACT_BF16).reshape(np.shape(a))
+
+
+def _fused_rank_main(rank, world, port, out):
+    """The data flow of the fused tensor-parallel step, restated with the oracle on CPU ranks: the
+    row-split projection's bf16 partial rows go to the rank that owns those token rows (scatter),
+    the owner adds the slots in rank order to its rows of the residual, normalises them, quantises
+    to NVFP4, and every rank ends up with all rows of the blob (gather)."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        hidden, kfull, m, div = 128, 256, 256, 256.0
+        own = m // world
+        rng = np.random.default_rng(11)
+        resid = rng.standard_normal((m, hidden)).astype(np.float32)          # residual stream, all rows
+        act = _bf16(rng.standard_normal((m, kfull)).astype(np.float32))      # input of the row-split projection
+        p_row = _payload(hidden, kfull, 3)
+        ks = kfull // world
+        kshard = slice_k_nvfp4(torch.from_numpy(p_row.copy()), hidden, kfull, rank * ks, ks).numpy()
+        part = _bf16(O.linear(act[:, rank * ks:(rank + 1) * ks].copy(), kshard, O.FMT_NVFP4, hidden, ks, 0, hidden, m))
+        # scatter: every rank's partial rows of owner o end up in o's slot for that source rank
+        gathered = [torch.empty(m, hidden) for _ in range(world)]
+        dist.all_gather(gathered, torch.from_numpy(part))
+        slots = [g.numpy()[rank * own:(rank + 1) * own] for g in gathered]    # slots[src]: my rows from src
+        x_own = resid[rank * own:(rank + 1) * own].copy()
+        total = slots[0].copy()
+        for s in slots[1:]:
+            total = (total + s).astype(np.float32)                            # rank order, f32
+        x_own = (x_own + total).astype(np.float32)
+        normed = _bf16(O.rms_norm(x_own, np.ones(hidden, np.float32), 1e-6))
+        codes, scales = O.act_codes_nvfp4(normed, div)
+        # gather: all rows of the blob on every rank
+        all_codes = [torch.empty(own, hidden // 2, dtype=torch.uint8) for _ in range(world)]
+        all_scales = [torch.empty(own, hidden // 16, dtype=torch.uint8) for _ in range(world)]
+        dist.all_gather(all_codes, torch.from_numpy(codes))
+        dist.all_gather(all_scales, torch.from_numpy(scales))
+        blob_codes = torch.cat(all_codes).numpy()
+        blob_scales = torch.cat(all_scales).numpy()
+        # what the unsharded sequence gives when the shards' partials are added in rank order
+        parts = []
+        for r in range(world):
+            kr = slice_k_nvfp4(torch.from_numpy(p_row.copy()), hidden, kfull, r * ks, ks).numpy()
+            parts.append(_bf16(O.linear(act[:, r * ks:(r + 1) * ks].copy(), kr, O.FMT_NVFP4, hidden, ks, 0, hidden, m)))
+        tot = parts[0].copy()
+        for q in parts[1:]:
+            tot = (tot + q).astype(np.float32)
+        want_norm = _bf16(O.rms_norm((resid + tot).astype(np.float32), np.ones(hidden, np.float32), 1e-6))
+        want_codes, want_scales = O.act_codes_nvfp4(want_norm, div)
+        ok = np.array_equal(blob_codes, want_codes) and np.array_equal(blob_scales, want_scales)
+        # and it stays close to the product with the unsharded weights
+        full = O.linear(act, p_row, O.FMT_NVFP4, hidden, kfull, 0, hidden, m)
+        err = O.max_err(tot, full)
+        with open(f"{out}.{rank}", "w") as f:
+            f.write(repr((bool(ok), float(err))))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_scatter_norm_gather_equals_rank_ordered_sum(tmp_path):
+    out = str(tmp_path / "fused")
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_fused_rank_main, args=(2, port, out), nprocs=2, join=True)
+    for r in range(2):
+        ok, err = eval(open(f"{out}.{r}").read())
+        assert ok
+        assert err <= 1e-2          # bf16 rounding of the two partial sums
