@@ -279,10 +279,10 @@ def test_linear_q4_refuses_what_the_fp4_gemm_does_not_serve(b):
 
 
 def _assert_atoms_equal(got, want, m, cols):
-    """Scale atoms agree: everywhere after a prefill call, over rows < m after a decode call (which
-    leaves the other rows' bytes alone)."""
+    """Scale atoms agree: everywhere after a prefill call, over rows < m after a call served by the
+    streaming kernel (decode and small batches, which leave the other rows' bytes alone)."""
     got, want = got.cpu().numpy().reshape(-1), want.cpu().numpy().reshape(-1)
-    if m > 16:
+    if m > 64:
         assert np.array_equal(got, want)
         return
     from velox_inferer_b200.weights import nvfp4_scale_offset
@@ -291,7 +291,8 @@ def _assert_atoms_equal(got, want, m, cols):
     assert np.array_equal(got[idx], want[idx])
 
 
-@pytest.mark.parametrize("n,k,m", [(256, 640, 37), (512, 1024, 300), (1024, 512, 513), (512, 1024, 1), (256, 5120, 13)])
+@pytest.mark.parametrize("n,k,m", [(256, 640, 37), (512, 1024, 300), (1024, 512, 513), (512, 1024, 1), (256, 5120, 13),
+                                   (256, 20480, 37)])   # (the last: a small batch on the streaming kernel)
 def test_linears_emit_the_next_linears_nvfp4_input(b, n, k, m):
     """linear_q4_to_q4 / linear_swiglu_q4_to_q4: the bf16 result is unchanged, and the codes and
     scale atoms written by the GEMM epilogue are bit for bit the stand-alone quantiser's output on

@@ -230,6 +230,47 @@ def test_linear_swiglu_decode_fp8_rows(b):
     assert O.max_err(out.cpu().numpy(), want) <= 5e-4
 
 
+# ---- small batches (17 to 64 tokens): streaming kernel where the GEMM would have few tiles --------
+
+@pytest.mark.parametrize("fmt,n,k,begin,rows,m,streams", [
+    (NV, 256, 25600, 0, 256, 37, True),      # two 128-row tiles, each cut over many CTAs
+    (NV, 384, 20480, 128, 200, 64, True),    # view inside its parent, full token capacity
+    (NV, 256, 25600, 0, 256, 17, True),      # second token chunk holds a single token
+    (F8, 256, 16384, 0, 256, 40, True),
+    (F8, 300, 16384, 20, 270, 33, True),
+    (NV, 512, 1024, 0, 512, 37, False),      # short K: the GEMM keeps it
+])
+def test_small_batches_take_the_streaming_kernel_where_it_wins(b, fmt, n, k, begin, rows, m, streams):
+    r = O.Rng(19)
+    payload = r.random_weight(FMT_O[fmt], n, k)
+    x = r.vec(m * k, 1.0)
+    policy = ActPolicy.allow_a4(600.0) if fmt == NV else ActPolicy.allow_a8()
+    view = make_view(b, payload, fmt, n, k, begin, rows, policy)
+    act = b.linear_act(view, m)
+    assert act == (ActQuant(ActQuant.NVFP4, 600.0) if fmt == NV else ActQuant(ActQuant.FP8_ROW))
+    want = oracle_linear(x, payload, fmt, n, k, begin, rows, m, act)
+    y = b.alloc(m * rows + 2)
+    yb = torch.zeros(m * rows, dtype=torch.bfloat16, device=y.device)
+    b.timing_enable(True)
+    b.timing_collect()
+    try:
+        for _ in range(2):                             # twice: the split counters return to zero
+            y.zero_()
+            b.linear(b.upload(x), view, y, m, yb=yb)
+            assert b.lib.velox_sm100_debug_status() == 0
+            got = y.cpu().numpy()
+            assert got[-2:].tolist() == [0.0, 0.0]
+            got = got[:-2].reshape(m, rows)
+            e_conf, e_rms = both_metrics(got, want)
+            assert e_conf <= LINEAR_TOL and e_rms <= RMS_TOL, (e_conf, e_rms)
+            assert np.array_equal(bf16_bits(yb).reshape(-1), f32_to_bf16_bits(got.reshape(-1)))
+        launches = {name: cnt for name, (_, cnt) in b.timing_collect().items()}
+    finally:
+        b.timing_enable(False)
+    gemm_class = "gemm_nvfp4" if fmt == NV else "gemm_fp8"
+    assert (launches["gemv"], launches[gemm_class]) == ((2, 0) if streams else (0, 2)), launches
+
+
 def test_portable_signature_entry_point(b):
     # velox_sm100_linear has velox_portable_linear's signature (portable.rs:81-91)
     n, k, m = 256, 512, 4

@@ -3,6 +3,7 @@
 // selection by (format, policy, m, k), and the launch-stream / scratch state the launchers share.
 #include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -108,6 +109,21 @@ static int fp8_tc_min_m() {
     return v;
 }
 
+// 17 <= m <= 64: true where the byte-balanced streaming kernel is expected to beat the GEMM.
+// VELOX_SM100_SMALL_BATCH = "stream" / "gemm" forces one of them.
+static bool small_batch_streams(const velox_sm100_view& v, int m) {
+    static const int forced = []() {
+        const char* e = getenv("VELOX_SM100_SMALL_BATCH");
+        return !e ? 0 : !strcmp(e, "stream") ? 1 : !strcmp(e, "gemm") ? 2 : 0;
+    }();
+    if (forced) return forced == 1;
+    const double row_bytes = v.format == VELOX_FMT_NVFP4 ? 0.5625 * (double)v.k : (double)v.k;
+    const long long gemm_tiles = (v.rows + 255) / 256;
+    const double gemm_us = (double)((gemm_tiles + 147) / 148) * 256.0 * row_bytes / 68e3;   // one CTA: about 68 GB/s
+    const double stream_us = (double)v.rows * row_bytes / 4.7e6 + 3.0 + 0.35 * m;           // all SMs: about 4.7 TB/s
+    return gemm_us > stream_us;
+}
+
 static Plan plan_for(const velox_sm100_view& v, int m) {
     Plan p{PATH_GENERIC, VELOX_ACT_EXACT, 0.0f};
     if (v.k % 64 != 0) return p;
@@ -133,6 +149,24 @@ static Plan plan_for(const velox_sm100_view& v, int m) {
         return p;
     }
     if (!gemm_available()) return p;
+    // Small batches (17 to 64 tokens) are still a weight stream. The GEMM gives a 256-row tile to one
+    // CTA, which then streams the whole K of those rows by itself: few tiles with a long K leave most
+    // of the machine idle. The streaming kernel cuts the same bytes evenly over all SMs but pays per
+    // token in its fix-up and stores. Measured models of both (microseconds) pick the kernel; the
+    // rounding is the same either way.
+    if (m <= 64 && small_batch_streams(v, m)) {
+        if (v.format == VELOX_FMT_NVFP4 && v.policy == VELOX_POLICY_ALLOW_A4 && v.divisor > 0.0f) {
+            p.path = PATH_GEMV_TC;
+            p.act = VELOX_ACT_NVFP4;
+            p.divisor = v.divisor;
+            return p;
+        }
+        if (v.format == VELOX_FMT_FP8_ROW_BF16 && v.policy != VELOX_POLICY_A16_ONLY && v.k % 128 == 0) {
+            p.path = PATH_GEMV_TC;
+            p.act = VELOX_ACT_FP8_ROW;
+            return p;
+        }
+    }
     if (v.format == VELOX_FMT_NVFP4 && v.policy == VELOX_POLICY_ALLOW_A4 && v.divisor > 0.0f) {
         p.path = PATH_GEMM_A4;
         p.act = VELOX_ACT_NVFP4;
@@ -156,7 +190,7 @@ static Plan plan_swiglu(const velox_sm100_view& both, const velox_sm100_view& ga
                         const velox_sm100_view& up, int m) {
     Plan p = plan_for(both, m);
     if ((p.path == PATH_GEMM_A4 || p.path == PATH_GEMV_TC) && (gate.row_begin - up.row_begin) % 128 != 0) {
-        p.path = p.path == PATH_GEMV_TC ? PATH_GEMV : PATH_GEMM_BF16;
+        p.path = p.path == PATH_GEMV_TC && m <= 16 ? PATH_GEMV : PATH_GEMM_BF16;
         p.act = VELOX_ACT_BF16;
         p.divisor = 0.0f;
     }
@@ -171,6 +205,8 @@ static int run(const LinearArgs& a, const Plan& p) {
             break;
         case PATH_GEMV_TC:
             rc = gemv_tc(a, p.act, p.divisor);
+            // (a small batch the streaming kernel declines has the same rounding on the GEMM)
+            if (rc == VELOX_ERR_UNSUPPORTED && a.m > 16) rc = gemm_linear(a, p.act, p.divisor);
             break;
         case PATH_GEMM_A4:
         case PATH_GEMM_A8:
@@ -214,7 +250,9 @@ static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.qo_divisor = qo_divisor;
     a.rs_maps = rs_maps;
     a.rs_rows_per_owner = rs_rows;
-    const Plan p = plan_for(*view, m);
+    Plan p = plan_for(*view, m);
+    // the scattering epilogue is the GEMM's (same rounding as the small-batch streaming kernel)
+    if (rs_maps && m > 16 && p.path == PATH_GEMV_TC && p.act == VELOX_ACT_NVFP4) p.path = PATH_GEMM_A4;
     if (rs_maps && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
     // pre-quantised input: the FP4 tensor-core paths only; and quantised output: the FP4 tensor-core paths only
     if (q_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;

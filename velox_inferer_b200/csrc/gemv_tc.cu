@@ -1,11 +1,11 @@
-// Decode linear (m <= 16 tokens) on the tensor cores: NVFP4 weights (block-scaled MMA) and FP8 rows.
+// Decode and small-batch linear (m <= 64 tokens) on the tensor cores: NVFP4 weights (block-scaled MMA) and FP8 rows.
 //
 // Decode is a byte stream: 0.5625 B per weight, every byte once. The SIMT/mma.sync GEMV spends
 // about 1.6 issue slots per weight on unpacking (E2M1 -> f16, times the block scale) and is bound
 // by instruction issue near half the copy rate. Here nothing is unpacked: a persistent CTA per SM
 // streams 128-row x 256-k tiles of the stored codes (16 KB, one tensor-map box) and their four
 // 512-byte scale atoms into shared memory, and tcgen05.mma kind::mxf4nvf4 consumes them as they
-// are - weight rows are the MMA M operand (128), the tokens the N operand (16, zero padded), the
+// are - weight rows are the MMA M operand (128), the tokens the N operand (16 or 64, zero padded), the
 // activations NVFP4 with the view's per-tensor divisor (ActQuant::Nvfp4, which the view's AllowA4
 // policy admits at any m). An MMA of this shape takes a few tens of cycles, so a CTA is idle
 // unless bytes arrive: the ring (eight 18 KB stages) is what sets the speed.
@@ -36,17 +36,25 @@ namespace vx {
 
 constexpr int DT_STAGES = 8;
 constexpr int DT_W_BYTES = 128 * 128;   // 128 weight rows x 128 bytes (256 k)
-constexpr int DT_X_BYTES = 16 * 128;    // 16 token rows x 128 bytes
-constexpr int DT_STAGE_BYTES = DT_W_BYTES + DT_X_BYTES;
 constexpr int DT_SF_STAGE_BYTES = 2048 + 2048;   // four W atoms, four x atoms
-constexpr int DT_OFF_SF = DT_STAGES * DT_STAGE_BYTES;
-constexpr int DT_OFF_BARS = DT_OFF_SF + DT_STAGES * DT_SF_STAGE_BYTES;
-constexpr int DT_SMEM_BYTES = DT_OFF_BARS + 1024 + 512;
 constexpr int DT_THREADS = 384;
 constexpr int DT_TMEM_COLS = 512;
-constexpr int DT_ACC_COLS = 32;      // per buffer: 16 token columns for each of up to two passes
-constexpr int DT_SF_COL = 64;        // scale sets follow the two accumulator buffers
 constexpr int DT_SF_SET = 32;        // per set: 16 columns of W scales, 16 of x scales
+
+// Sizes that depend on the token capacity NT of a launch (the MMA N extent): 16 for decode proper,
+// 64 for small batches (speculative decode, short prefills), which are still a weight stream.
+template <int NT>
+struct DtPlan {
+    static constexpr int X_BYTES = NT * 128;                    // NT token rows x 128 bytes
+    static constexpr int STAGE_BYTES = DT_W_BYTES + X_BYTES;    // 18 KB / 24 KB
+    static constexpr int OFF_SF = DT_STAGES * STAGE_BYTES;
+    static constexpr int OFF_BARS = OFF_SF + DT_STAGES * DT_SF_STAGE_BYTES;
+    static constexpr int SMEM_BYTES = OFF_BARS + 1024 + 512;
+    static constexpr int ACC_COLS = 2 * NT;                     // per buffer: NT token columns for each of two passes
+    static constexpr int SF_COL = 2 * ACC_COLS;                 // scale sets follow the two accumulator buffers
+    static_assert(SF_COL + DT_STAGES * DT_SF_SET <= DT_TMEM_COLS, "tensor memory plan");
+    static_assert(SMEM_BYTES <= 232448, "shared memory plan");
+};
 
 constexpr int DT_MAX_PARTS = 3;   // views served by one launch (q, k, v of one input)
 
@@ -81,23 +89,30 @@ struct DtParams {
     float alpha;                 // 1 / activation divisor
     const uint16_t* rowscale[DT_MAX_PARTS];   // FP8 rows: bf16 scale per weight row
     const float* tokscale;                     // FP8 rows: f32 scale per token
-    float* partial;              // [CTAs][2][V][128][16]: a CTA's first and last run can be partial tiles
+    float* partial;              // [CTAs][2][V][NT/16][128][16]: a CTA's first and last run can be partial tiles
     int* tickets;                // [tiles], zero between launches
     int* status;
+#ifdef VX_GEMM_PROFILE
+    int dbg;   // development only: 1 no result stores, 2 no fix-up loads, 8 no partial stores (4: host, one x row)
+#endif
 };
 
 __device__ int g_gemv_tc_status = 0;
 
-template <bool SWIGLU, int KIND>
+template <bool SWIGLU, int KIND, int NT>
 __global__ void __launch_bounds__(DT_THREADS, 1)
 gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_constant__ CUtensorMap map_w1,
                      const __grid_constant__ CUtensorMap map_w2, const __grid_constant__ CUtensorMap map_x,
                      const DtParams p) {
     constexpr int V = SWIGLU ? 2 : 1;
+    using PL = DtPlan<NT>;
+    constexpr int DT_STAGE_BYTES = PL::STAGE_BYTES;
+    constexpr int DT_ACC_COLS = PL::ACC_COLS;
+    constexpr int DT_SF_COL = PL::SF_COL;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t sf_ring = base + DT_OFF_SF;
-    const uint32_t bars = base + DT_OFF_BARS;
+    const uint32_t sf_ring = base + PL::OFF_SF;
+    const uint32_t bars = base + PL::OFF_BARS;
     auto op_full = [&](int s) { return bars + 8u * s; };
     auto op_empty = [&](int s) { return bars + 8u * (DT_STAGES + s); };
     auto sf_full = [&](int s) { return bars + 8u * (2 * DT_STAGES + s); };
@@ -228,7 +243,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         bool ok = true;
         const bool leader = elect_one();
         // M = 128, N = 16, E2M1 x E2M1 with UE4M3 block scales, K-major operands, f32 accumulate
-        const uint32_t shape = ((uint32_t)(16 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+        const uint32_t shape = ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
         const uint32_t idesc = KIND == KIND_MXF4 ? ((1u << 7) | (1u << 10) | shape)   // E2M1 x E2M1, UE4M3 scales
                                                  : ((1u << 4) | shape);                // E4M3 x E4M3 -> f32
         int n = 0;
@@ -242,7 +257,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                 break;
             }
             for (int v = 0; v < V && ok; v++) {
-                const uint32_t d = tmem + buf * DT_ACC_COLS + v * 16;
+                const uint32_t d = tmem + buf * DT_ACC_COLS + v * NT;
                 for (int kb = kb0; kb < kb1; kb++) {
                     if (!mbar_wait(op_full(stage), phase) || (KIND == KIND_MXF4 && !mbar_wait(tsf_full(stage), phase))) {
                         if (leader) atomicExch(p.status, 23);
@@ -385,36 +400,61 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                 break;
             }
             tc_fence_after();
-            uint32_t r[V][16];
             const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + buf * DT_ACC_COLS;
-#pragma unroll
-            for (int v = 0; v < V; v++) tc_ld16(taddr + v * 16, r[v]);
-            tc_wait_ld();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty(buf));
-            float acc[V][16];
-#pragma unroll
-            for (int v = 0; v < V; v++)
-#pragma unroll
-                for (int j = 0; j < 16; j++) acc[v][j] = __uint_as_float(r[v][j]);
+            constexpr int NC = NT / 16;                         // token chunks of 16 accumulator columns
+            const int chunks = (p.m + 15) / 16;                 // ... of which this many hold tokens
 
-            bool finish = true;
+            int lt = tile;
+            const int idx = SWIGLU ? 0 : part_of(tile, lt);
+            const DtOut& o = p.out[idx];
+            const long long row = (p.tile0[idx] + lt) * 128 + row_in_tile;
+            const bool row_ok = row >= o.valid_begin && row < o.valid_end;
+            const long long o0 = o.col + (row - o.valid_begin);
+            float f0, f1 = 0.0f;
+            if (KIND == KIND_MXF4) {
+                f0 = p.alpha / *p.wdiv[idx];
+                if (SWIGLU) f1 = p.alpha / *p.wdiv[1];
+            } else {
+                // row scales; the matching up row sits at the same offset from its view's start
+                f0 = row_ok ? bf16_bits_to_f32(p.rowscale[idx][row]) : 0.0f;
+                if (SWIGLU) f1 = row_ok ? bf16_bits_to_f32(p.rowscale[1][(p.tile0[1] + lt) * 128 + row_in_tile]) : 0.0f;
+            }
+            auto release_acc = [&]() {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty(buf));
+            };
+            // The code below runs once or twice per CTA, so it is written for few instructions
+            // rather than few cycles: fetching a cold instruction line costs about as much as a
+            // trip to memory, and an unrolled 16-token body was most of this kernel's per-token
+            // cost. Loops are kept rolled; the per-token values go through a small local array.
+            const size_t slot_floats = (size_t)V * NC * 128 * 16;
+            const long long t0 = (long long)tile * p.k_blocks, t1 = t0 + p.k_blocks;
+            const int c_first = (int)(t0 / p.per_cta), c_last = (int)((t1 - 1) / p.per_cta);
             if (!whole) {
-                // park this piece's partial sums; the CTA that arrives last at the tile adds the
-                // pieces in K order (which is CTA order) and finishes. The tile's pieces belong to
+                // Part of a tile's K: park the partial sums; the CTA that arrives last at the tile adds
+                // the pieces in K order (which is CTA order) and finishes. The tile's pieces belong to
                 // CTAs c_first .. c_last; a CTA's piece of a tile is its first piece exactly when its
                 // run starts inside that tile, otherwise it is its last.
-                const long long t0 = (long long)tile * p.k_blocks, t1 = t0 + p.k_blocks;
-                const int c_first = (int)(t0 / p.per_cta), c_last = (int)((t1 - 1) / p.per_cta);
-                float4* mine = reinterpret_cast<float4*>(
-                    p.partial + (((size_t)blockIdx.x * 2 + (first_piece ? 0 : 1)) * V * 128 + row_in_tile) * 16);
+                float* mine = p.partial + ((size_t)blockIdx.x * 2 + (first_piece ? 0 : 1)) * slot_floats;
+#pragma unroll 1
+                for (int c = 0; c < chunks; c++) {
+                    uint32_t r[V][16];
 #pragma unroll
-                for (int v = 0; v < V; v++)
+                    for (int v = 0; v < V; v++) tc_ld16(taddr + v * NT + c * 16, r[v]);
+                    tc_wait_ld();
+#ifdef VX_GEMM_PROFILE
+                    if (p.dbg & 8) continue;
+#endif
 #pragma unroll
-                    for (int q = 0; q < 4; q++)
-                        mine[(size_t)v * 128 * 4 + q] =
-                            make_float4(acc[v][4 * q], acc[v][4 * q + 1], acc[v][4 * q + 2], acc[v][4 * q + 3]);
+                    for (int v = 0; v < V; v++) {
+                        uint4* dstp = reinterpret_cast<uint4*>(mine + (((size_t)v * NC + c) * 128 + row_in_tile) * 16);
+#pragma unroll
+                        for (int q = 0; q < 4; q++)
+                            dstp[q] = make_uint4(r[v][4 * q], r[v][4 * q + 1], r[v][4 * q + 2], r[v][4 * q + 3]);
+                    }
+                }
+                release_acc();
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (warp == 4 && lane == 0) {
@@ -424,61 +464,105 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                     *flag_ptr = last ? 1u : 0u;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                finish = *flag_ptr != 0u;
+                const bool finish = *flag_ptr != 0u;
                 asm volatile("bar.sync 1, 128;" ::: "memory");   // the flag is read before it is rewritten
-                if (finish) {
-                    __threadfence();
+                if (!finish) continue;
+                __threadfence();
+            }
+
+            float* const oy = o.y;
+            uint16_t* const oyb = o.yb;
+            const long long old = o.ld;
+            uint8_t* const oq_codes = o.q_codes;
+            uint8_t* const oq_atoms = o.q_atoms;
+            const float oq_div = o.q_divisor;
+            const long long oq_ld = o.q_ld;
+#pragma unroll 1
+            for (int c = 0; c < chunks; c++) {
+                float sum[V][16];   // tokens 16 c .. 16 c + 15 of this lane's weight row
+                if (whole) {
+                    uint32_t r[V][16];
+#pragma unroll
+                    for (int v = 0; v < V; v++) tc_ld16(taddr + v * NT + c * 16, r[v]);
+                    tc_wait_ld();
+                    if (c == chunks - 1) release_acc();
 #pragma unroll
                     for (int v = 0; v < V; v++)
 #pragma unroll
-                        for (int j = 0; j < 16; j++) acc[v][j] = 0.0f;
-                    for (int c = c_first; c <= c_last; c++) {
-                        const int slot = (long long)c * p.per_cta >= t0 ? 0 : 1;
-                        const float4* theirs = reinterpret_cast<const float4*>(
-                            p.partial + (((size_t)c * 2 + slot) * V * 128 + row_in_tile) * 16);
+                        for (int j = 0; j < 16; j++) sum[v][j] = __uint_as_float(r[v][j]);
+                } else {
 #pragma unroll
-                        for (int v = 0; v < V; v++)
+                    for (int v = 0; v < V; v++)
 #pragma unroll
-                            for (int q = 0; q < 4; q++) {
-                                const float4 t = __ldcg(theirs + (size_t)v * 128 * 4 + q);
-                                acc[v][4 * q] += t.x;
-                                acc[v][4 * q + 1] += t.y;
-                                acc[v][4 * q + 2] += t.z;
-                                acc[v][4 * q + 3] += t.w;
+                        for (int j = 0; j < 16; j++) sum[v][j] = 0.0f;
+                    // several CTAs' slots per pass, so that their loads are in flight together
+                    constexpr int B = V == 1 ? 4 : 2;
+#pragma unroll 1
+                    for (int cta0 = c_first; cta0 <= c_last; cta0 += B) {
+#ifdef VX_GEMM_PROFILE
+                        if (p.dbg & 2) break;
+#endif
+                        float4 t[B][V][4];
+#pragma unroll
+                        for (int b = 0; b < B; b++) {
+                            const int cta = cta0 + b <= c_last ? cta0 + b : c_last;   // (a repeat is not added)
+                            const int slot = (long long)cta * p.per_cta >= t0 ? 0 : 1;
+                            const float* theirs = p.partial + ((size_t)cta * 2 + slot) * slot_floats;
+#pragma unroll
+                            for (int v = 0; v < V; v++) {
+                                const float4* src = reinterpret_cast<const float4*>(
+                                    theirs + (((size_t)v * NC + c) * 128 + row_in_tile) * 16);
+#pragma unroll
+                                for (int q = 0; q < 4; q++) t[b][v][q] = __ldcg(src + q);
+                            }
+                        }
+#pragma unroll
+                        for (int b = 0; b < B; b++)
+                            if (cta0 + b <= c_last) {
+#pragma unroll
+                                for (int v = 0; v < V; v++)
+#pragma unroll
+                                    for (int q = 0; q < 4; q++) {
+                                        sum[v][4 * q] += t[b][v][q].x;
+                                        sum[v][4 * q + 1] += t[b][v][q].y;
+                                        sum[v][4 * q + 2] += t[b][v][q].z;
+                                        sum[v][4 * q + 3] += t[b][v][q].w;
+                                    }
                             }
                     }
                 }
-            }
-            if (finish) {
-                int lt = tile;
-                const int idx = SWIGLU ? 0 : part_of(tile, lt);
-                const DtOut& o = p.out[idx];
-                const long long row = (p.tile0[idx] + lt) * 128 + row_in_tile;
-                const bool row_ok = row >= o.valid_begin && row < o.valid_end;
-                const long long o0 = o.col + (row - o.valid_begin);
-                float f0, f1 = 0.0f;
-                if (KIND == KIND_MXF4) {
-                    f0 = p.alpha / *p.wdiv[idx];
-                    if (SWIGLU) f1 = p.alpha / *p.wdiv[1];
-                } else {
-                    // row scales; the matching up row sits at the same offset from its view's start
-                    f0 = row_ok ? bf16_bits_to_f32(p.rowscale[idx][row]) : 0.0f;
-                    if (SWIGLU) f1 = row_ok ? bf16_bits_to_f32(p.rowscale[1][(p.tile0[1] + lt) * 128 + row_in_tile]) : 0.0f;
-                }
+                const int ntok = p.m - c * 16 < 16 ? p.m - c * 16 : 16;   // uniform across the warp
+#ifdef VX_GEMM_PROFILE
+                if (p.dbg & 1) continue;
+#endif
+                // Four tokens per pass of a rolled loop: a lone warp issues a dependent instruction
+                // every few cycles, so the body is kept short and its four tokens independent.
+                const long long tok0 = (long long)(c * 16) * old + o0;
+#pragma unroll 1
+                for (int g = 0; g < 4 && g * 4 < ntok; g++) {
+                    float a[V][4];
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    if (j < p.m) {   // uniform across the warp
-                        const float ts = KIND == KIND_MXF4 ? 1.0f : p.tokscale[j];
-                        float val = acc[0][j] * f0 * ts;
+                    for (int v = 0; v < V; v++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++)
+                            a[v][i] = g == 0 ? sum[v][i] : g == 1 ? sum[v][4 + i] : g == 2 ? sum[v][8 + i] : sum[v][12 + i];
+                    const long long at = tok0 + (long long)(g * 4) * old;
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        if (g * 4 + i >= ntok) break;
+                        const int j = c * 16 + g * 4 + i;
+                        float val = a[0][i] * f0;
+                        if (KIND != KIND_MXF4) val *= p.tokscale[j];
                         if (SWIGLU) {
-                            const float u = acc[V - 1][j] * f1 * ts;
+                            float u = a[V - 1][i] * f1;
+                            if (KIND != KIND_MXF4) u *= p.tokscale[j];
                             val = val / (1.0f + __expf(-val)) * u;
                         }
                         if (row_ok) {
-                            if (o.y) o.y[(long long)j * o.ld + o0] = val;
-                            if (o.yb) o.yb[(long long)j * o.ld + o0] = bf16_bits(val);
+                            if (oy) oy[at + i * old] = val;
+                            if (oyb) oyb[at + i * old] = bf16_bits(val);
                         }
-                        if (o.q_codes) {
+                        if (oq_codes) {
                             // The same value as the next linear's NVFP4 input: sixteen consecutive
                             // outputs of a token sit in sixteen consecutive lanes (the host side only
                             // allows views that start on a scale tile and hold whole groups).
@@ -487,14 +571,13 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
 #pragma unroll
                             for (int off = 8; off >= 1; off >>= 1)
                                 amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-                            const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(o.q_divisor, amax), 6.0f));
-                            const float q = sb ? __fdiv_rn(__fmul_rn(vb, o.q_divisor), e4m3_to_f32(sb)) : 0.0f;
+                            const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(oq_div, amax), 6.0f));
+                            const float q = sb ? __fdiv_rn(__fmul_rn(vb, oq_div), e4m3_to_f32(sb)) : 0.0f;
                             const float qn = __shfl_down_sync(0xffffffffu, q, 1);
                             if (row_ok) {
                                 if ((lane & 1) == 0)
-                                    o.q_codes[((long long)j * o.q_ld + o0) / 2] = (uint8_t)f32x2_to_e2m1x2(q, qn);
-                                if ((lane & 15) == 0)
-                                    o.q_atoms[nvfp4_scale_offset(j, o0 / 16, o.q_ld)] = (uint8_t)sb;
+                                    oq_codes[((long long)j * oq_ld + o0) / 2] = (uint8_t)f32x2_to_e2m1x2(q, qn);
+                                if ((lane & 15) == 0) oq_atoms[nvfp4_scale_offset(j, o0 / 16, oq_ld)] = (uint8_t)sb;
                             }
                         }
                     }
@@ -558,7 +641,8 @@ int gemv_tc_parts(const LinearArgs* parts, int n, int act, float divisor) {
     if (!f8 && act != VELOX_ACT_NVFP4) return VELOX_ERR_UNSUPPORTED;
     if (sw && n != 1) return VELOX_ERR_UNSUPPORTED;
     const long long k = a.w.k;
-    if (a.m < 1 || a.m > 16) return VELOX_ERR_UNSUPPORTED;
+    if (a.m < 1 || a.m > 64) return VELOX_ERR_UNSUPPORTED;
+    const int nt = a.m <= 16 ? 16 : 64;   // token capacity of the launch
     if (f8 ? (k % 128 != 0 || a.q_codes) : (k % 64 != 0 || !(divisor > 0.0f))) return VELOX_ERR_UNSUPPORTED;
 
     DtParams p{};
@@ -566,7 +650,7 @@ int gemv_tc_parts(const LinearArgs* parts, int n, int act, float divisor) {
     int rc;
     if (f8) {
         uint8_t* c = static_cast<uint8_t*>(scratch(SCRATCH_ACT_CODES, (size_t)a.m * k));
-        float* sc = static_cast<float*>(scratch(SCRATCH_ACT_SCALES, 16 * sizeof(float)));
+        float* sc = static_cast<float*>(scratch(SCRATCH_ACT_SCALES, 64 * sizeof(float)));
         if (!c || !sc) return (int)cudaErrorMemoryAllocation;
         if ((rc = quantize_act_fp8row(a.x, a.xb, a.m, k, c, sc)) != 0) return rc;
         codes = c;
@@ -646,7 +730,12 @@ int gemv_tc_parts(const LinearArgs* parts, int n, int act, float divisor) {
         for (int i = n; i < DT_MAX_PARTS; i++) mw[i] = mw[0];
         p.nparts = n;
     }
-    if ((rc = gemm_make_map_u8(&mx, codes, a.m, row_bytes, 16)) != 0) return rc;
+#ifdef VX_GEMM_PROFILE
+    p.dbg = getenv("VX_DT_DBG") ? atoi(getenv("VX_DT_DBG")) : 0;
+    if ((rc = gemm_make_map_u8(&mx, codes, (p.dbg & 4) ? 1 : a.m, row_bytes, nt)) != 0) return rc;
+#else
+    if ((rc = gemm_make_map_u8(&mx, codes, a.m, row_bytes, nt)) != 0) return rc;
+#endif
 
     static int sms = 0;
     if (sms == 0) {
@@ -662,7 +751,7 @@ int gemv_tc_parts(const LinearArgs* parts, int n, int act, float divisor) {
     p.per_cta = (total_steps + grid_l - 1) / grid_l;
     const int grid = (int)((total_steps + p.per_cta - 1) / p.per_cta);
     {
-        const size_t per_slot = (size_t)(sw ? 2 : 1) * 128 * 16 * sizeof(float);
+        const size_t per_slot = (size_t)(sw ? 2 : 1) * 128 * nt * sizeof(float);
         p.partial = static_cast<float*>(scratch(SCRATCH_Y_F32, (size_t)grid * 2 * per_slot));
         p.tickets = gemv_tc_tickets((size_t)p.tiles);
         if (!p.partial || !p.tickets) return (int)cudaErrorMemoryAllocation;
@@ -673,7 +762,7 @@ int gemv_tc_parts(const LinearArgs* parts, int n, int act, float divisor) {
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(DT_THREADS);
-    cfg.dynamicSmemBytes = DT_SMEM_BYTES;
+    cfg.dynamicSmemBytes = nt == 16 ? DtPlan<16>::SMEM_BYTES : DtPlan<64>::SMEM_BYTES;
     cfg.stream = stream();
     // Early start: this kernel's CTAs may become resident while the kernel before it in the
     // stream is still finishing; they fetch weights, and wait for that kernel before touching
@@ -685,14 +774,22 @@ int gemv_tc_parts(const LinearArgs* parts, int n, int act, float divisor) {
     cfg.attrs = attr;
     cfg.numAttrs = early ? 1 : 0;
     auto go = [&](auto kern) {
-        cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM_BYTES);
+        cudaError_t err =
+            cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cfg.dynamicSmemBytes);
         if (err != cudaSuccess) return err;
         return cudaLaunchKernelEx(&cfg, kern, mw[0], mw[1], mw[2], mx, p);
     };
-    if (f8)
-        e = sw ? go(gemv_nvfp4_tc_kernel<true, KIND_F8>) : go(gemv_nvfp4_tc_kernel<false, KIND_F8>);
-    else
-        e = sw ? go(gemv_nvfp4_tc_kernel<true, KIND_MXF4>) : go(gemv_nvfp4_tc_kernel<false, KIND_MXF4>);
+    if (nt == 16) {
+        if (f8)
+            e = sw ? go(gemv_nvfp4_tc_kernel<true, KIND_F8, 16>) : go(gemv_nvfp4_tc_kernel<false, KIND_F8, 16>);
+        else
+            e = sw ? go(gemv_nvfp4_tc_kernel<true, KIND_MXF4, 16>) : go(gemv_nvfp4_tc_kernel<false, KIND_MXF4, 16>);
+    } else {
+        if (f8)
+            e = sw ? go(gemv_nvfp4_tc_kernel<true, KIND_F8, 64>) : go(gemv_nvfp4_tc_kernel<false, KIND_F8, 64>);
+        else
+            e = sw ? go(gemv_nvfp4_tc_kernel<true, KIND_MXF4, 64>) : go(gemv_nvfp4_tc_kernel<false, KIND_MXF4, 64>);
+    }
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
