@@ -234,26 +234,29 @@ __device__ __forceinline__ void accum_q4k(const uint8_t* __restrict__ w, long lo
                 for (int j = 0; j < GEMV_R; j++) {
                     const uint4 q = qs[j][cc >> 1];
                     const uint32_t w0 = (cc & 1) ? q.z : q.x, w1 = (cc & 1) ? q.w : q.y;
-                    // the four nibbles of a word at once; each then becomes a float with one byte
-                    // permute (nibble into the mantissa of 2^23) and one subtraction, instead of
-                    // an integer-to-float conversion, which issues at a fraction of the FMA rate
-                    const uint32_t n0 = (half ? (w0 >> 4) : w0) & 0x0f0f0f0fu;
-                    const uint32_t n1 = (half ? (w1 >> 4) : w1) & 0x0f0f0f0fu;
+                    // The four nibbles of a word at once, each moved to the top of a mantissa: one
+                    // byte permute then makes the float 1 + q / 16 (bits 0x3F800000 | q << 19) with no
+                    // conversion and no subtraction. The sum below is therefore sum(x) + sum(q x) / 16;
+                    // the known sum(x) is taken off together with the block minimum.
+                    const uint32_t n0 = ((half ? (w0 >> 1) : (w0 << 3)) & 0x78787878u) | 0x80808080u;
+                    const uint32_t n1 = ((half ? (w1 >> 1) : (w1 << 3)) & 0x78787878u) | 0x80808080u;
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
-                        const float qv =
-                            __uint_as_float(__byte_perm(e < 4 ? n0 : n1, 0x4B000000u, 0x7440u | (uint32_t)(e & 3))) -
-                            8388608.0f;
+                        const float qv = __uint_as_float(
+                            __byte_perm(e < 4 ? n0 : n1, 0x3F000000u, 0x7044u | ((uint32_t)(e & 3) << 8)));
 #pragma unroll
                         for (int t = 0; t < MT; t++) qx[j][t] = fmaf(qv, xv[t][e], qx[j][t]);
                     }
                 }
             }
 #pragma unroll
-            for (int j = 0; j < GEMV_R; j++)
+            for (int j = 0; j < GEMV_R; j++) {
+                // d sc sum(q x) - dmin mn sum(x), with sum(q x) = 16 (qx - sum(x))
+                const float ds = 16.0f * (half ? d2[j] : d1[j]);
+                const float ms = ds + (half ? m2[j] : m1[j]);
 #pragma unroll
-                for (int t = 0; t < MT; t++)
-                    acc[j][t] += (half ? d2[j] : d1[j]) * qx[j][t] - (half ? m2[j] : m1[j]) * sx[t];
+                for (int t = 0; t < MT; t++) acc[j][t] += ds * qx[j][t] - ms * sx[t];
+            }
         }
     }
 }
@@ -263,6 +266,42 @@ __global__ void __launch_bounds__(GEMV_WARPS* VX_WARP)
 gemv_kernel(const GemvParams p) {
     extern __shared__ uint4 xs[];
     const int tiles = (int)(p.k / 64);
+    const int warp = threadIdx.x / VX_WARP, lane = threadIdx.x % VX_WARP;
+    const long long unit = (long long)blockIdx.x * GEMV_WARPS + warp;
+    long long prow[GEMV_R], urow[GEMV_R];
+    bool valid[GEMV_R];
+#pragma unroll
+    for (int j = 0; j < GEMV_R; j++) {
+        if (FMT == VELOX_FMT_NVFP4) {
+            const long long tile128 = p.row_begin / 128 + unit / 32;
+            prow[j] = tile128 * 128 + unit % 32 + 32 * j;
+        } else {
+            prow[j] = p.row_begin + unit * GEMV_R + j;
+        }
+        valid[j] = prow[j] >= p.row_begin && prow[j] < p.row_begin + p.rows;
+        urow[j] = p.row_begin2 + (prow[j] - p.row_begin);
+    }
+
+    // Ask for this warp's weight rows before anything else: the lines travel from HBM to L2 while
+    // the block stages its activations, and the loads further down then find them there.
+    if (FMT != VELOX_FMT_NVFP4) {
+        const long long row_bytes = FMT == VELOX_FMT_FP8_ROW_BF16 ? p.k : p.k / 256 * 144;
+#pragma unroll
+        for (int j = 0; j < GEMV_R; j++) {
+            if (!valid[j]) continue;
+            const uint8_t* r1 = p.w + prow[j] * row_bytes;
+            for (long long off = (long long)lane * 128 - (long long)(reinterpret_cast<uintptr_t>(r1) & 127); off < row_bytes;
+                 off += 32 * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(r1 + (off < 0 ? 0 : off)));
+            if (SWIGLU) {
+                const uint8_t* r2 = p.w2 + urow[j] * row_bytes;
+                for (long long off = (long long)lane * 128 - (long long)(reinterpret_cast<uintptr_t>(r2) & 127); off < row_bytes;
+                     off += 32 * 128)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(r2 + (off < 0 ? 0 : off)));
+            }
+        }
+    }
+
     // Stage this pass's tokens as bf16, chunk c of tile T at slot c ^ (T & 7) (conflict-free
     // 128-bit reads when consecutive lanes read the same chunk of consecutive tiles).
     for (int idx = threadIdx.x; idx < MT * tiles * 8; idx += blockDim.x) {
@@ -286,22 +325,6 @@ gemv_kernel(const GemvParams p) {
         xs[((long long)t * tiles + T) * 8 + (c ^ (T & 7))] = v;
     }
     __syncthreads();
-
-    const int warp = threadIdx.x / VX_WARP, lane = threadIdx.x % VX_WARP;
-    const long long unit = (long long)blockIdx.x * GEMV_WARPS + warp;
-    long long prow[GEMV_R], urow[GEMV_R];
-    bool valid[GEMV_R];
-#pragma unroll
-    for (int j = 0; j < GEMV_R; j++) {
-        if (FMT == VELOX_FMT_NVFP4) {
-            const long long tile128 = p.row_begin / 128 + unit / 32;
-            prow[j] = tile128 * 128 + unit % 32 + 32 * j;
-        } else {
-            prow[j] = p.row_begin + unit * GEMV_R + j;
-        }
-        valid[j] = prow[j] >= p.row_begin && prow[j] < p.row_begin + p.rows;
-        urow[j] = p.row_begin2 + (prow[j] - p.row_begin);
-    }
 
     float acc[GEMV_R][MT], acc2[GEMV_R][MT];
 #pragma unroll
@@ -425,7 +448,10 @@ int gemv(const LinearArgs& a) {
         case VELOX_FMT_FP8_ROW_BF16:
             return a.swiglu ? gemv_fmt<VELOX_FMT_FP8_ROW_BF16, true>(a)
                             : gemv_fmt<VELOX_FMT_FP8_ROW_BF16, false>(a);
-        case VELOX_FMT_GGML_Q4_K:
+        case VELOX_FMT_GGML_Q4_K: {
+            const int rc = gemv_q4k_mma(a);
+            if (rc != VELOX_ERR_UNSUPPORTED) return rc;
+        }
             return a.swiglu ? gemv_fmt<VELOX_FMT_GGML_Q4_K, true>(a)
                             : gemv_fmt<VELOX_FMT_GGML_Q4_K, false>(a);
         default:

@@ -1,0 +1,301 @@
+// Decode (m <= 16) on GGML Q4_K rows through the warp-level tensor-core MMA.
+//
+// A Q4_K weight is d * sc * q - dmin * mn with a 4-bit q and 6-bit sc, mn shared by 32 weights
+// (crates/velox-core/src/ggml.rs:159-210). Unpacking q to a float and multiplying it costs a general
+// ALU two to three instructions per weight and per token, which bounds the SIMT kernel well below the
+// memory rate as soon as there is more than one token. Here q goes to bf16 with one byte permute
+// per two weights (0x4300 | q is the bf16 number 128 + q, exactly) and mma.sync.m16n8k16 multiplies
+// sixteen rows by eight tokens at once, the tokens as the B operand in bf16 (ActQuant::Bf16, which
+// every policy admits). Per 32-weight group the MMA result c = sum((128 + q) x) is folded into the
+// running sums as d sc c - (128 d sc + dmin mn) sum(x); the group sums of x come from a small
+// kernel that runs first.
+//
+// Work split: a block owns 32 rows (two MMA row tiles); its four warps each take a quarter of K
+// and the parts are added in warp order at the end, so results do not depend on timing. Within a
+// warp, lane (g, t) loads 8 bytes of each of its four rows per 64-weight chunk: the dot product
+// does not care about the order along K, so the K slots of the MMA are assigned to whatever
+// bytes a lane holds and the activations are fetched in the matching order (one 16-byte load of
+// eight consecutive bf16 per group and token tile, from L1). Each warp asks for its weight bytes
+// with L2 prefetches before anything else.
+//
+// Reference counterpart: linear_gemv_ggml_kernel, crates/velox-cuda/kernels/portable_model.cu:1628-1716.
+#include <cstdlib>
+#include <type_traits>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace vx {
+
+constexpr int QM_WARPS = 4;   // K parts per block
+constexpr int QM_ROWS = 32;   // weight rows per block
+
+struct Q4kParams {
+    const uint8_t* w;
+    long long k, row_begin;
+    int rows;
+    const uint16_t* xb;   // [m, k] bf16
+    const float* sx;      // [k / 32][16]: sum of each 32-wide group of each token (0 beyond m)
+    int m;
+    float* y;
+    uint16_t* yb;
+    long long ld, col;
+};
+
+__global__ void q4k_group_sums_kernel(const uint16_t* __restrict__ xb, float* __restrict__ sx, int m, long long k) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= k / 32 * 16) return;
+    const int tok = (int)(idx % 16);
+    const long long s = idx / 16;
+    float sum = 0.0f;
+    if (tok < m) {
+        const uint4* src = reinterpret_cast<const uint4*>(xb + (long long)tok * k + s * 32);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint4 v = __ldg(src + q);
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) sum += __uint_as_float(u[i] << 16) + __uint_as_float(u[i] & 0xffff0000u);
+        }
+    }
+    sx[idx] = sum;
+}
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// What a lane keeps of one row's block header: d, dmin and the eight 6-bit (scale, min) pairs as
+// four words of bytes.
+struct Q4kHead {
+    float d, dmin, nd23, ndmin23;   // the last two: -d 2^23, -dmin 2^23
+    uint32_t sc03, sc47, mn03, mn47;
+};
+
+__device__ __forceinline__ Q4kHead q4k_head(const uint4& h) {
+    Q4kHead r;
+    r.d = f16_bits_to_f32(h.x & 0xffffu);
+    r.dmin = f16_bits_to_f32(h.x >> 16);
+    r.nd23 = -r.d * 8388608.0f;
+    r.ndmin23 = -r.dmin * 8388608.0f;
+    // ggml.rs:159-169, four bytes at a time
+    r.sc03 = h.y & 0x3f3f3f3fu;
+    r.mn03 = h.z & 0x3f3f3f3fu;
+    r.sc47 = (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u);
+    r.mn47 = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
+    return r;
+}
+
+// d sc and 128 d sc + dmin mn of group S (a compile-time index): byte -> float by placing it in the
+// mantissa of 2^23, the 2^23 taken off inside the multiply-add.
+template <int S>
+__device__ __forceinline__ void q4k_group_factors(const Q4kHead& h, float& ds, float& off) {
+    const uint32_t scw = S < 4 ? h.sc03 : h.sc47, mnw = S < 4 ? h.mn03 : h.mn47;
+    const float scf = __uint_as_float(__byte_perm(scw, 0x4B000000u, 0x7440u | (uint32_t)(S & 3)));
+    const float mnf = __uint_as_float(__byte_perm(mnw, 0x4B000000u, 0x7440u | (uint32_t)(S & 3)));
+    ds = fmaf(h.d, scf, h.nd23);
+    off = fmaf(128.0f, ds, fmaf(h.dmin, mnf, h.ndmin23));
+}
+
+template <int NB>
+__global__ void __launch_bounds__(QM_WARPS * 32) gemv_q4k_mma_kernel(const Q4kParams p) {
+    __shared__ float red[QM_WARPS - 1][2 * NB * 4][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const long long row_bytes = p.k / 256 * 144;
+    const int bt = (int)(p.k / 256);
+    const int kb0 = warp * bt / QM_WARPS, kb1 = (warp + 1) * bt / QM_WARPS;
+    const long long r_first = p.row_begin + (long long)blockIdx.x * QM_ROWS;
+    const long long r_last = p.row_begin + p.rows - 1;
+
+    // this warp's weight bytes: on their way from HBM to L2 before the first load needs them
+    {
+        const long long bytes = (long long)(kb1 - kb0) * 144;
+        for (int r = 0; r < QM_ROWS; r++) {
+            const long long row = r_first + r < r_last ? r_first + r : r_last;
+            const uint8_t* b = p.w + row * row_bytes + (long long)kb0 * 144;
+            for (long long off = (long long)lane * 128 - (long long)(reinterpret_cast<uintptr_t>(b) & 127); off < bytes;
+                 off += 32 * 128)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(b + (off < 0 ? 0 : off)));
+        }
+    }
+
+    // the lane's rows: tile mt, half h -> row r_first + 16 mt + 8 h + g (a row past the view reads the last one)
+    const uint8_t* rp[2][2];
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const long long r = r_first + 16 * mt + 8 * h + g;
+            rp[mt][h] = p.w + (r < r_last ? r : r_last) * row_bytes;
+        }
+
+    float acc[2][NB][4];
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+        for (int nb = 0; nb < NB; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[mt][nb][i] = 0.0f;
+
+    for (int blk = kb0; blk < kb1; blk++) {
+        uint4 raw_head[2][2];
+        uint2 qs[2][2][4];
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const uint8_t* b = rp[mt][h] + (long long)blk * 144;
+                raw_head[mt][h] = __ldcs(reinterpret_cast<const uint4*>(b));
+#pragma unroll
+                for (int c = 0; c < 4; c++) qs[mt][h][c] = __ldcs(reinterpret_cast<const uint2*>(b + 16 + 32 * c + 8 * t));
+            }
+        Q4kHead head[2][2];
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) head[mt][h] = q4k_head(raw_head[mt][h]);
+
+        auto chunk = [&](auto cc) {
+            constexpr int c = decltype(cc)::value;
+#pragma unroll
+            for (int half = 0; half < 2; half++) {   // low nibbles: group 2c, high nibbles: group 2c + 1
+                const long long k0 = (long long)blk * 256 + c * 64 + half * 32 + 8 * t;
+                const long long grp = (long long)blk * 8 + 2 * c + half;
+                uint4 bx[NB];
+                float2 sx[NB];
+#pragma unroll
+                for (int nb = 0; nb < NB; nb++) {
+                    const int tok = nb * 8 + g;
+                    bx[nb] = tok < p.m ? __ldg(reinterpret_cast<const uint4*>(p.xb + (long long)tok * p.k + k0))
+                                       : make_uint4(0, 0, 0, 0);
+                    sx[nb] = __ldg(reinterpret_cast<const float2*>(p.sx + grp * 16 + nb * 8 + 2 * t));
+                }
+#pragma unroll
+                for (int mt = 0; mt < 2; mt++) {
+                    const uint2 qa = qs[mt][0][c], qb = qs[mt][1][c];
+                    const uint32_t a_lo = (half ? (qa.x >> 4) : qa.x) & 0x0f0f0f0fu;   // values 8t .. 8t+3 of row g
+                    const uint32_t a_hi = (half ? (qa.y >> 4) : qa.y) & 0x0f0f0f0fu;   // values 8t+4 .. 8t+7
+                    const uint32_t b_lo = (half ? (qb.x >> 4) : qb.x) & 0x0f0f0f0fu;   // the same of row g + 8
+                    const uint32_t b_hi = (half ? (qb.y >> 4) : qb.y) & 0x0f0f0f0fu;
+                    // bf16 pairs 128 + q: K slots (2t, 2t+1) and (2t+8, 2t+9) of the first MMA take values
+                    // 8t .. 8t+3, those of the second take 8t+4 .. 8t+7
+                    const uint32_t a0 = __byte_perm(a_lo, 0x43434343u, 0x4140u), a2 = __byte_perm(a_lo, 0x43434343u, 0x4342u);
+                    const uint32_t a1 = __byte_perm(b_lo, 0x43434343u, 0x4140u), a3 = __byte_perm(b_lo, 0x43434343u, 0x4342u);
+                    const uint32_t e0 = __byte_perm(a_hi, 0x43434343u, 0x4140u), e2 = __byte_perm(a_hi, 0x43434343u, 0x4342u);
+                    const uint32_t e1 = __byte_perm(b_hi, 0x43434343u, 0x4140u), e3 = __byte_perm(b_hi, 0x43434343u, 0x4342u);
+                    float ds_a, off_a, ds_b, off_b;
+                    if (half == 0) {
+                        q4k_group_factors<2 * c>(head[mt][0], ds_a, off_a);
+                        q4k_group_factors<2 * c>(head[mt][1], ds_b, off_b);
+                    } else {
+                        q4k_group_factors<2 * c + 1>(head[mt][0], ds_a, off_a);
+                        q4k_group_factors<2 * c + 1>(head[mt][1], ds_b, off_b);
+                    }
+#pragma unroll
+                    for (int nb = 0; nb < NB; nb++) {
+                        float cfr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        mma_bf16_16816(cfr, a0, a1, a2, a3, bx[nb].x, bx[nb].y);
+                        mma_bf16_16816(cfr, e0, e1, e2, e3, bx[nb].z, bx[nb].w);
+                        acc[mt][nb][0] = fmaf(-off_a, sx[nb].x, fmaf(ds_a, cfr[0], acc[mt][nb][0]));
+                        acc[mt][nb][1] = fmaf(-off_a, sx[nb].y, fmaf(ds_a, cfr[1], acc[mt][nb][1]));
+                        acc[mt][nb][2] = fmaf(-off_b, sx[nb].x, fmaf(ds_b, cfr[2], acc[mt][nb][2]));
+                        acc[mt][nb][3] = fmaf(-off_b, sx[nb].y, fmaf(ds_b, cfr[3], acc[mt][nb][3]));
+                    }
+                }
+            }
+        };
+        chunk(std::integral_constant<int, 0>{});
+        chunk(std::integral_constant<int, 1>{});
+        chunk(std::integral_constant<int, 2>{});
+        chunk(std::integral_constant<int, 3>{});
+    }
+
+    // add the four K parts in warp order
+    if (warp > 0) {
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int nb = 0; nb < NB; nb++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) red[warp - 1][(mt * NB + nb) * 4 + i][lane] = acc[mt][nb][i];
+    }
+    __syncthreads();
+    if (warp != 0) return;
+#pragma unroll
+    for (int w = 0; w < QM_WARPS - 1; w++)
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int nb = 0; nb < NB; nb++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) acc[mt][nb][i] += red[w][(mt * NB + nb) * 4 + i][lane];
+
+    // lane (g, t) holds rows g and g + 8 of each tile for tokens 2t and 2t + 1 of each token tile
+#pragma unroll
+    for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const long long r = r_first + 16 * mt + 8 * h + g;
+            if (r > r_last) continue;
+#pragma unroll
+            for (int nb = 0; nb < NB; nb++)
+#pragma unroll
+                for (int i = 0; i < 2; i++) {
+                    const int tok = nb * 8 + 2 * t + i;
+                    if (tok >= p.m) continue;
+                    const float v = acc[mt][nb][2 * h + i];
+                    const long long o = (long long)tok * p.ld + p.col + (r - p.row_begin);
+                    if (p.y) p.y[o] = v;
+                    if (p.yb) p.yb[o] = bf16_bits(v);
+                }
+        }
+}
+
+int gemv_q4k_mma(const LinearArgs& a) {
+    static const bool off = getenv("VELOX_SM100_Q4K_SIMT") != nullptr;
+    if (off || a.swiglu || a.w.format != VELOX_FMT_GGML_Q4_K || a.w.k % 256 != 0 || a.m < 1 || a.m > 16 ||
+        a.w.rows < 1 || (reinterpret_cast<uintptr_t>(a.w.w) & 15))
+        return VELOX_ERR_UNSUPPORTED;
+    const long long k = a.w.k;
+    const uint16_t* xb = a.xb;
+    if (!xb) {
+        uint16_t* tmp = static_cast<uint16_t*>(scratch(SCRATCH_X_BF16, (size_t)a.m * k * sizeof(uint16_t)));
+        if (!tmp) return (int)cudaErrorMemoryAllocation;
+        const int rc = bf16_twin(a.x, tmp, (long long)a.m * k);
+        if (rc != 0) return rc;
+        xb = tmp;
+    }
+    if (reinterpret_cast<uintptr_t>(xb) & 15) return VELOX_ERR_UNSUPPORTED;
+    float* sx = static_cast<float*>(scratch(SCRATCH_ACT_SCALES, (size_t)(k / 32) * 16 * sizeof(float)));
+    if (!sx) return (int)cudaErrorMemoryAllocation;
+
+    Q4kParams p;
+    p.w = a.w.w;
+    p.k = k;
+    p.row_begin = a.w.row_begin;
+    p.rows = (int)a.w.rows;
+    p.xb = xb;
+    p.sx = sx;
+    p.m = a.m;
+    p.y = a.y;
+    p.yb = a.yb;
+    p.ld = a.ld;
+    p.col = a.col;
+
+    TimedRegion timed(TIMED_GEMV);
+    const long long cells = k / 32 * 16;
+    q4k_group_sums_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, stream()>>>(xb, sx, a.m, k);
+    const unsigned blocks = (unsigned)((a.w.rows + QM_ROWS - 1) / QM_ROWS);
+    if (a.m <= 8)
+        gemv_q4k_mma_kernel<1><<<blocks, QM_WARPS * 32, 0, stream()>>>(p);
+    else
+        gemv_q4k_mma_kernel<2><<<blocks, QM_WARPS * 32, 0, stream()>>>(p);
+    return launch_status();
+}
+
+}  // namespace vx

@@ -61,6 +61,8 @@ int add_bf16(float* acc, const uint16_t* xb, long long len);
 int add_rms_norm_twin(float* acc, const float* x, const uint16_t* xb, const float* weight, float* y,
                       uint16_t* yb, int rows, int dim, float eps, int offset);
 int bf16_twin(const float* x, uint16_t* xb, long long len);
+// Q4_K decode on the warp-level tensor-core MMA (plain form, m <= 16, k % 256 == 0); else VELOX_ERR_UNSUPPORTED.
+int gemv_q4k_mma(const LinearArgs& a);
 int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
                uint8_t* const* codes, uint8_t* const* atoms, int ndst, long long row0, int rows, int dim, float eps,
                int offset, float divisor);
