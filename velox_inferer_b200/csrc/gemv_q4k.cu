@@ -7,10 +7,10 @@
 // per two weights (0x4300 | q is the bf16 number 128 + q, exactly) and mma.sync.m16n8k16 multiplies
 // sixteen rows by eight tokens at once, the tokens as the B operand in bf16 (ActQuant::Bf16, which
 // every policy admits). Per 32-weight group the MMA result c = sum((128 + q) x) is folded into the
-// running sums as d sc c - (128 d sc + dmin mn) sum(x); the group sums of x come from a small
-// kernel that runs first.
+// running sums as d sc c - (128 d sc + dmin mn) sum(x); sum(x) per group and token comes from an MMA
+// whose A operand is all ones, which delivers it in the accumulator layout at once.
 //
-// Work split: a block owns 32 rows (two MMA row tiles); its four warps each take a quarter of K
+// Work split: a block owns 16 or 32 rows (one or two MMA row tiles); its four warps each take a quarter of K
 // and the parts are added in warp order at the end, so results do not depend on timing. Within a
 // warp, lane (g, t) loads 8 bytes of each of its four rows per 64-weight chunk: the dot product
 // does not care about the order along K, so the K slots of the MMA are assigned to whatever
@@ -27,43 +27,31 @@
 
 namespace vx {
 
-constexpr int QM_WARPS = 4;   // K parts per block
-constexpr int QM_ROWS = 32;   // weight rows per block
 
 struct Q4kParams {
     const uint8_t* w;
     long long k, row_begin;
     int rows;
     const uint16_t* xb;   // [m, k] bf16
-    const float* sx;      // [k / 32][16]: sum of each 32-wide group of each token (0 beyond m)
     int m;
     float* y;
     uint16_t* yb;
     long long ld, col;
 };
 
-__global__ void q4k_group_sums_kernel(const uint16_t* __restrict__ xb, float* __restrict__ sx, int m, long long k) {
-    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= k / 32 * 16) return;
-    const int tok = (int)(idx % 16);
-    const long long s = idx / 16;
-    float sum = 0.0f;
-    if (tok < m) {
-        const uint4* src = reinterpret_cast<const uint4*>(xb + (long long)tok * k + s * 32);
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const uint4 v = __ldg(src + q);
-            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int i = 0; i < 4; i++) sum += __uint_as_float(u[i] << 16) + __uint_as_float(u[i] & 0xffff0000u);
-        }
-    }
-    sx[idx] = sum;
+// d = a b (+ c): the first MMA of a group starts from zero constants, the second adds in place.
+__device__ __forceinline__ void mma_bf16_16816_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                     uint32_t b0, uint32_t b1) {
+    asm(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%10, %10, %10, %10};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
         "{%0, %1, %2, %3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -102,9 +90,10 @@ __device__ __forceinline__ void q4k_group_factors(const Q4kHead& h, float& ds, f
     off = fmaf(128.0f, ds, fmaf(h.dmin, mnf, h.ndmin23));
 }
 
-template <int NB>
-__global__ void __launch_bounds__(QM_WARPS * 32) gemv_q4k_mma_kernel(const Q4kParams p) {
-    __shared__ float red[QM_WARPS - 1][2 * NB * 4][32];
+template <int MT, int NB, int QM_WARPS, bool PIPE>
+__global__ void __launch_bounds__(QM_WARPS * 32, !PIPE ? 7 : QM_WARPS == 2 ? 7 : NB == 1 ? 4 : 2) gemv_q4k_mma_kernel(const Q4kParams p) {
+    constexpr int QM_ROWS = 16 * MT;   // weight rows per block: MT row tiles of the MMA; QM_WARPS: K parts, one per warp
+    __shared__ float red[QM_WARPS - 1][MT * NB * 4][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const long long row_bytes = p.k / 256 * 144;
     const int bt = (int)(p.k / 256);
@@ -125,100 +114,133 @@ __global__ void __launch_bounds__(QM_WARPS * 32) gemv_q4k_mma_kernel(const Q4kPa
     }
 
     // the lane's rows: tile mt, half h -> row r_first + 16 mt + 8 h + g (a row past the view reads the last one)
-    const uint8_t* rp[2][2];
+    const uint8_t* rp[MT][2];
 #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const long long r = r_first + 16 * mt + 8 * h + g;
             rp[mt][h] = p.w + (r < r_last ? r : r_last) * row_bytes;
         }
 
-    float acc[2][NB][4];
+    float acc[MT][NB][4];
 #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int nb = 0; nb < NB; nb++)
 #pragma unroll
             for (int i = 0; i < 4; i++) acc[mt][nb][i] = 0.0f;
 
-    for (int blk = kb0; blk < kb1; blk++) {
-        uint4 raw_head[2][2];
-        uint2 qs[2][2][4];
+    // token rows of this lane's B fragments
+    const uint16_t* xrow[NB];
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+    for (int nb = 0; nb < NB; nb++) xrow[nb] = p.xb + (nb * 8 + g < p.m ? (long long)(nb * 8 + g) * p.k : 0) + 8 * t;
+
+    // The next block's bytes are requested before the current block is worked on.
+    auto load_blk = [&](int blk, uint4 (&hd)[MT][2], uint2 (&q)[MT][2][4]) {
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int h = 0; h < 2; h++) {
                 const uint8_t* b = rp[mt][h] + (long long)blk * 144;
-                raw_head[mt][h] = __ldcs(reinterpret_cast<const uint4*>(b));
+                hd[mt][h] = __ldcs(reinterpret_cast<const uint4*>(b));
 #pragma unroll
-                for (int c = 0; c < 4; c++) qs[mt][h][c] = __ldcs(reinterpret_cast<const uint2*>(b + 16 + 32 * c + 8 * t));
+                for (int c = 0; c < 4; c++) q[mt][h][c] = __ldcs(reinterpret_cast<const uint2*>(b + 16 + 32 * c + 8 * t));
             }
-        Q4kHead head[2][2];
+    };
+    // B fragments of the step being worked on: eight consecutive bf16 of this lane's token per token
+    // tile. A token past m reads token 0; its accumulator columns are never stored.
+    auto load_b = [&](long long k0, uint4 (&b)[NB]) {
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+        for (int nb = 0; nb < NB; nb++) b[nb] = __ldg(reinterpret_cast<const uint4*>(xrow[nb] + k0));
+    };
+    uint4 bx[NB];
+    uint4 raw_head[MT][2];
+    uint2 qs[MT][2][4];
+    if (kb0 < kb1) {
+        if (PIPE) load_blk(kb0, raw_head, qs);
+        load_b((long long)kb0 * 256, bx);
+    }
+    for (int blk = kb0; blk < kb1; blk++) {
+        uint4 next_head[MT][2];
+        uint2 next_qs[MT][2][4];
+        if (PIPE)
+            load_blk(blk + 1 < kb1 ? blk + 1 : blk, next_head, next_qs);   // (the last pass repeats its own block: no branch)
+        else
+            load_blk(blk, raw_head, qs);
+        Q4kHead head[MT][2];
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int h = 0; h < 2; h++) head[mt][h] = q4k_head(raw_head[mt][h]);
 
-        auto chunk = [&](auto cc) {
-            constexpr int c = decltype(cc)::value;
+        // One step per 32-weight group: group S = 2c + half is the low (half = 0) or high nibbles of
+        // the 32 bytes of chunk c. The next step's activations are requested before this step's work.
+        auto step = [&](auto ss) {
+            constexpr int S = decltype(ss)::value, c = S / 2, half = S % 2;
+            uint4 nx[NB];
+            load_b(S < 7 ? (long long)blk * 256 + (S + 1) * 32 : (long long)(blk + 1 < kb1 ? blk + 1 : blk) * 256, nx);
+            float2 sx[NB];   // sum of the group's x for tokens 2t and 2t + 1: an MMA with ones as its A operand
 #pragma unroll
-            for (int half = 0; half < 2; half++) {   // low nibbles: group 2c, high nibbles: group 2c + 1
-                const long long k0 = (long long)blk * 256 + c * 64 + half * 32 + 8 * t;
-                const long long grp = (long long)blk * 8 + 2 * c + half;
-                uint4 bx[NB];
-                float2 sx[NB];
+            for (int nb = 0; nb < NB; nb++) {
+                float ones[4];
+                mma_bf16_16816_first(ones, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u, bx[nb].x, bx[nb].y);
+                mma_bf16_16816(ones, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u, bx[nb].z, bx[nb].w);
+                sx[nb] = make_float2(ones[0], ones[1]);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                const uint2 qa = qs[mt][0][c], qb = qs[mt][1][c];
+                const uint32_t a_lo = (half ? (qa.x >> 4) : qa.x) & 0x0f0f0f0fu;   // values 8t .. 8t+3 of row g
+                const uint32_t a_hi = (half ? (qa.y >> 4) : qa.y) & 0x0f0f0f0fu;   // values 8t+4 .. 8t+7
+                const uint32_t b_lo = (half ? (qb.x >> 4) : qb.x) & 0x0f0f0f0fu;   // the same of row g + 8
+                const uint32_t b_hi = (half ? (qb.y >> 4) : qb.y) & 0x0f0f0f0fu;
+                // bf16 pairs 128 + q: K slots (2t, 2t+1) and (2t+8, 2t+9) of the first MMA take values
+                // 8t .. 8t+3, those of the second take 8t+4 .. 8t+7
+                const uint32_t a0 = __byte_perm(a_lo, 0x43434343u, 0x4140u), a2 = __byte_perm(a_lo, 0x43434343u, 0x4342u);
+                const uint32_t a1 = __byte_perm(b_lo, 0x43434343u, 0x4140u), a3 = __byte_perm(b_lo, 0x43434343u, 0x4342u);
+                const uint32_t e0 = __byte_perm(a_hi, 0x43434343u, 0x4140u), e2 = __byte_perm(a_hi, 0x43434343u, 0x4342u);
+                const uint32_t e1 = __byte_perm(b_hi, 0x43434343u, 0x4140u), e3 = __byte_perm(b_hi, 0x43434343u, 0x4342u);
+                float ds_a, off_a, ds_b, off_b;
+                q4k_group_factors<S>(head[mt][0], ds_a, off_a);
+                q4k_group_factors<S>(head[mt][1], ds_b, off_b);
 #pragma unroll
                 for (int nb = 0; nb < NB; nb++) {
-                    const int tok = nb * 8 + g;
-                    bx[nb] = tok < p.m ? __ldg(reinterpret_cast<const uint4*>(p.xb + (long long)tok * p.k + k0))
-                                       : make_uint4(0, 0, 0, 0);
-                    sx[nb] = __ldg(reinterpret_cast<const float2*>(p.sx + grp * 16 + nb * 8 + 2 * t));
-                }
-#pragma unroll
-                for (int mt = 0; mt < 2; mt++) {
-                    const uint2 qa = qs[mt][0][c], qb = qs[mt][1][c];
-                    const uint32_t a_lo = (half ? (qa.x >> 4) : qa.x) & 0x0f0f0f0fu;   // values 8t .. 8t+3 of row g
-                    const uint32_t a_hi = (half ? (qa.y >> 4) : qa.y) & 0x0f0f0f0fu;   // values 8t+4 .. 8t+7
-                    const uint32_t b_lo = (half ? (qb.x >> 4) : qb.x) & 0x0f0f0f0fu;   // the same of row g + 8
-                    const uint32_t b_hi = (half ? (qb.y >> 4) : qb.y) & 0x0f0f0f0fu;
-                    // bf16 pairs 128 + q: K slots (2t, 2t+1) and (2t+8, 2t+9) of the first MMA take values
-                    // 8t .. 8t+3, those of the second take 8t+4 .. 8t+7
-                    const uint32_t a0 = __byte_perm(a_lo, 0x43434343u, 0x4140u), a2 = __byte_perm(a_lo, 0x43434343u, 0x4342u);
-                    const uint32_t a1 = __byte_perm(b_lo, 0x43434343u, 0x4140u), a3 = __byte_perm(b_lo, 0x43434343u, 0x4342u);
-                    const uint32_t e0 = __byte_perm(a_hi, 0x43434343u, 0x4140u), e2 = __byte_perm(a_hi, 0x43434343u, 0x4342u);
-                    const uint32_t e1 = __byte_perm(b_hi, 0x43434343u, 0x4140u), e3 = __byte_perm(b_hi, 0x43434343u, 0x4342u);
-                    float ds_a, off_a, ds_b, off_b;
-                    if (half == 0) {
-                        q4k_group_factors<2 * c>(head[mt][0], ds_a, off_a);
-                        q4k_group_factors<2 * c>(head[mt][1], ds_b, off_b);
-                    } else {
-                        q4k_group_factors<2 * c + 1>(head[mt][0], ds_a, off_a);
-                        q4k_group_factors<2 * c + 1>(head[mt][1], ds_b, off_b);
-                    }
-#pragma unroll
-                    for (int nb = 0; nb < NB; nb++) {
-                        float cfr[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                        mma_bf16_16816(cfr, a0, a1, a2, a3, bx[nb].x, bx[nb].y);
-                        mma_bf16_16816(cfr, e0, e1, e2, e3, bx[nb].z, bx[nb].w);
-                        acc[mt][nb][0] = fmaf(-off_a, sx[nb].x, fmaf(ds_a, cfr[0], acc[mt][nb][0]));
-                        acc[mt][nb][1] = fmaf(-off_a, sx[nb].y, fmaf(ds_a, cfr[1], acc[mt][nb][1]));
-                        acc[mt][nb][2] = fmaf(-off_b, sx[nb].x, fmaf(ds_b, cfr[2], acc[mt][nb][2]));
-                        acc[mt][nb][3] = fmaf(-off_b, sx[nb].y, fmaf(ds_b, cfr[3], acc[mt][nb][3]));
-                    }
+                    float cfr[4];
+                    mma_bf16_16816_first(cfr, a0, a1, a2, a3, bx[nb].x, bx[nb].y);
+                    mma_bf16_16816(cfr, e0, e1, e2, e3, bx[nb].z, bx[nb].w);
+                    acc[mt][nb][0] = fmaf(-off_a, sx[nb].x, fmaf(ds_a, cfr[0], acc[mt][nb][0]));
+                    acc[mt][nb][1] = fmaf(-off_a, sx[nb].y, fmaf(ds_a, cfr[1], acc[mt][nb][1]));
+                    acc[mt][nb][2] = fmaf(-off_b, sx[nb].x, fmaf(ds_b, cfr[2], acc[mt][nb][2]));
+                    acc[mt][nb][3] = fmaf(-off_b, sx[nb].y, fmaf(ds_b, cfr[3], acc[mt][nb][3]));
                 }
             }
+#pragma unroll
+            for (int nb = 0; nb < NB; nb++) bx[nb] = nx[nb];
         };
-        chunk(std::integral_constant<int, 0>{});
-        chunk(std::integral_constant<int, 1>{});
-        chunk(std::integral_constant<int, 2>{});
-        chunk(std::integral_constant<int, 3>{});
+        step(std::integral_constant<int, 0>{});
+        step(std::integral_constant<int, 1>{});
+        step(std::integral_constant<int, 2>{});
+        step(std::integral_constant<int, 3>{});
+        step(std::integral_constant<int, 4>{});
+        step(std::integral_constant<int, 5>{});
+        step(std::integral_constant<int, 6>{});
+        step(std::integral_constant<int, 7>{});
+        if (!PIPE) continue;
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                raw_head[mt][h] = next_head[mt][h];
+#pragma unroll
+                for (int c = 0; c < 4; c++) qs[mt][h][c] = next_qs[mt][h][c];
+            }
     }
 
     // add the four K parts in warp order
     if (warp > 0) {
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+        for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int nb = 0; nb < NB; nb++)
 #pragma unroll
@@ -229,7 +251,7 @@ __global__ void __launch_bounds__(QM_WARPS * 32) gemv_q4k_mma_kernel(const Q4kPa
 #pragma unroll
     for (int w = 0; w < QM_WARPS - 1; w++)
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++)
+        for (int mt = 0; mt < MT; mt++)
 #pragma unroll
             for (int nb = 0; nb < NB; nb++)
 #pragma unroll
@@ -237,7 +259,7 @@ __global__ void __launch_bounds__(QM_WARPS * 32) gemv_q4k_mma_kernel(const Q4kPa
 
     // lane (g, t) holds rows g and g + 8 of each tile for tokens 2t and 2t + 1 of each token tile
 #pragma unroll
-    for (int mt = 0; mt < 2; mt++)
+    for (int mt = 0; mt < MT; mt++)
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const long long r = r_first + 16 * mt + 8 * h + g;
@@ -271,8 +293,6 @@ int gemv_q4k_mma(const LinearArgs& a) {
         xb = tmp;
     }
     if (reinterpret_cast<uintptr_t>(xb) & 15) return VELOX_ERR_UNSUPPORTED;
-    float* sx = static_cast<float*>(scratch(SCRATCH_ACT_SCALES, (size_t)(k / 32) * 16 * sizeof(float)));
-    if (!sx) return (int)cudaErrorMemoryAllocation;
 
     Q4kParams p;
     p.w = a.w.w;
@@ -280,7 +300,6 @@ int gemv_q4k_mma(const LinearArgs& a) {
     p.row_begin = a.w.row_begin;
     p.rows = (int)a.w.rows;
     p.xb = xb;
-    p.sx = sx;
     p.m = a.m;
     p.y = a.y;
     p.yb = a.yb;
@@ -288,13 +307,29 @@ int gemv_q4k_mma(const LinearArgs& a) {
     p.col = a.col;
 
     TimedRegion timed(TIMED_GEMV);
-    const long long cells = k / 32 * 16;
-    q4k_group_sums_kernel<<<(unsigned)((cells + 255) / 256), 256, 0, stream()>>>(xb, sx, a.m, k);
-    const unsigned blocks = (unsigned)((a.w.rows + QM_ROWS - 1) / QM_ROWS);
-    if (a.m <= 8)
-        gemv_q4k_mma_kernel<1><<<blocks, QM_WARPS * 32, 0, stream()>>>(p);
-    else
-        gemv_q4k_mma_kernel<2><<<blocks, QM_WARPS * 32, 0, stream()>>>(p);
+    // One row tile per block while that still leaves the machine short of warps (and the tokens fit L1),
+    // two otherwise: the second tile halves what a block reads of the activations per weight byte.
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    static const int forced_mt = getenv("VELOX_SM100_Q4K_ROW_TILES") ? atoi(getenv("VELOX_SM100_Q4K_ROW_TILES")) : 0;
+    const bool one = forced_mt ? forced_mt == 1
+                               : ((a.w.rows + 31) / 32 < 6LL * sms && (size_t)a.m * k * sizeof(uint16_t) <= 160 * 1024);
+    const unsigned blocks = (unsigned)((a.w.rows + (one ? 16 : 32) - 1) / (one ? 16 : 32));
+    // Up to eight tokens: four K parts per block, loads at the top of each block of K (72 registers,
+    // seven blocks per SM). More tokens: the next block's weight bytes are requested a block ahead,
+    // which costs 24 registers per row tile, so two K parts per block keep every block resident.
+    if (a.m <= 8) {
+        if (one) gemv_q4k_mma_kernel<1, 1, 4, false><<<blocks, 128, 0, stream()>>>(p);
+        else gemv_q4k_mma_kernel<2, 1, 4, true><<<blocks, 128, 0, stream()>>>(p);
+    } else {
+        if (one) gemv_q4k_mma_kernel<1, 2, 2, true><<<blocks, 64, 0, stream()>>>(p);
+        else gemv_q4k_mma_kernel<2, 2, 4, true><<<blocks, 128, 0, stream()>>>(p);
+    }
     return launch_status();
 }
 
