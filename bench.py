@@ -469,6 +469,78 @@ def components(b, peaks, graph=True):
                                          "frac_of_measured_bf16_x4": tf / (peaks["bf16_tflops"] * FP4_OVER_BF16),
                                          "frac_of_nominal_fp4": tf / NOMINAL_FP4_TFLOPS,
                                          "timing": "CUDA-graph replay; includes the activation quantiser launch"}
+    del views
+    out.update(_decode_other_formats(b, peaks, graph))
+    return out
+
+
+def _decode_other_formats(b, peaks, graph=True):
+    """The same [25600, 5120] projection stored as FP8-E4M3 rows and as GGML Q4_K: decode launches at
+    1 and 8 tokens with bf16 activations (the rounding every policy admits), seeded synthetic bytes
+    (finite codes, sane scales), weight copies rotated so that they never sit in L2."""
+    import torch
+
+    from velox_inferer_b200 import ActPolicy, WeightFormat, WeightView
+
+    n, k = 25600, 5120
+    out = {}
+    gen = torch.Generator(device=b.device).manual_seed(1)
+    stream = torch.cuda.Stream()
+    for name, fmt, policies in (("fp8", WeightFormat.FP8_ROW_BF16, (("a16", ActPolicy.a16_only()), ("a8", ActPolicy.allow_a8()))),
+                                ("q4k", WeightFormat.GGML_Q4_K, (("a16", ActPolicy.a16_only()),))):
+        payload = fmt.payload_bytes(n, k)
+        copies = 4 if name == "fp8" else 6   # > 3 x the 126 MB L2 either way
+        bufs = []
+        for _ in range(copies):
+            buf = torch.randint(0, 120, (payload + 256,), generator=gen, dtype=torch.uint8, device=b.device)
+            if name == "fp8":
+                off = (n * k + 255) // 256 * 256
+                buf[off:off + 2 * n].view(torch.bfloat16).fill_(0.01)      # bf16 row scales
+            else:
+                blocks = buf[:payload].view(-1, 144)
+                blocks[:, 1] = 0x20                                        # f16 d and dmin: small, finite
+                blocks[:, 3] = 0x20
+            bufs.append(buf)
+        for pname, policy in policies:
+            views = [WeightView.full(buf, fmt, n, k).with_act(policy) for buf in bufs]
+            for m in (1, 8):
+                xb = torch.randn(m, k, device=b.device).to(torch.bfloat16)
+                yb = torch.empty(m, n, dtype=torch.bfloat16, device=b.device)
+                call = lambda v: b.linear_bf16(xb, v, None, m, yb=yb)
+                rounds = 4
+                with torch.cuda.stream(stream):
+                    for v in views:
+                        call(v)
+                torch.cuda.synchronize()
+
+                def burst():
+                    for _ in range(rounds):
+                        for v in views:
+                            call(v)
+                replay, g = burst, None
+                if graph:
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream):
+                        burst()
+                    replay = g.replay
+                replay()
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(3):
+                    replay()
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / (3 * rounds * copies)
+                byts = payload + 2 * m * k + 2 * m * n
+                gbs = byts / (us * 1e-6) / 1e9
+                act = b.linear_act(views[0], m)
+                out[f"decode_gemv_{name}_{pname}_m{m}"] = {
+                    "us_per_launch": us, "GB/s": gbs, "bytes": byts, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                    "activation_rounding": str(act),
+                    "timing": f"CUDA-graph replay of {rounds * copies} launches over {copies} rotated weight copies"}
+                del g
+        del bufs
     return out
 
 

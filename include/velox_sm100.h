@@ -135,8 +135,9 @@ int velox_sm100_linear_bf16(const uint16_t* xb, const velox_sm100_view* view, in
  * image (VELOX_SM100_STATIC_SCRATCH_BYTES; every GPU that loads the library carries it until the
  * process ends) and calls no cudaMalloc, cudaFree or other allocating routine, ever.
  *
- * Same result as velox_sm100_linear_bf16 for an NVFP4 view whose policy is AllowA4 at m > 16
- * (activations rounded as VELOX_ACT_NVFP4 with the view's divisor). Anything else returns
+ * Serves an NVFP4 view whose policy is AllowA4 at m > 16 on the prefill GEMM, activations rounded as
+ * VELOX_ACT_NVFP4 with the view's divisor: the bits velox_sm100_linear_bf16 gives wherever it takes
+ * the GEMM too (m > 64 always; 17..64 unless its cost model streams the shape). Anything else returns
  * VELOX_ERR_UNSUPPORTED. The call needs align256(m*k/2) + ceil(m/128)*128*k/16 bytes of the
  * array (m = 2048, k = 5120: 5.9 MiB); a larger call returns VELOX_ERR_STATIC_SCRATCH and does
  * nothing.
@@ -205,7 +206,8 @@ int velox_sm100_add_rms_norm_twin(float* acc, const float* x, const float* weigh
  * with `divisor` exactly as quant::quantize_activations(Nvfp4{divisor}) does - so the projections
  * that follow run without a quantisation pass. velox_sm100_linear_q4 / _swiglu_q4 take that blob
  * in place of x; they serve NVFP4 views whose policy is AllowA4 with the same divisor, at any m
- * (prefill GEMM above 16 tokens, tensor-core decode kernel up to 16), and return
+ * (tensor-core decode kernel up to 16 tokens and for small batches it streams faster, prefill GEMM
+ * otherwise), and return
  * VELOX_ERR_UNSUPPORTED otherwise (use the bf16 entry points then). */
 int velox_sm100_add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float* weight,
                                 uint16_t* yb, uint8_t* codes, uint8_t* atoms, int rows, int dim, float eps,

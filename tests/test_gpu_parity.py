@@ -109,6 +109,10 @@ GEMV_CASES = [
     (F8, 64, 512, 0, 64, 9), (F8, 64, 128, 0, 64, 2), (F8, 512, 2048, 64, 384, 8),
     (F8, 300, 192, 0, 300, 5), (F8, 160, 1024, 16, 128, 16),
     (Q4, 48, 512, 0, 48, 1), (Q4, 40, 1024, 3, 33, 8), (Q4, 64, 2560, 0, 64, 16),
+    # Q4_K on the MMA kernel: one K block for four K parts, ragged rows and tokens, both token-tile
+    # counts, and row counts large enough for two row tiles per block
+    (Q4, 100, 256, 5, 77, 11), (Q4, 72, 5120, 0, 72, 4), (Q4, 2100, 1024, 16, 2050, 2),
+    (Q4, 28700, 256, 0, 28700, 3), (Q4, 28700, 512, 9, 28650, 12),
 ]
 
 
