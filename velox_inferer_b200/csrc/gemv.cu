@@ -11,6 +11,8 @@
 //
 // Reference counterpart: linear_gemv_vec_kernel / linear_gemv_ggml_kernel,
 // crates/velox-cuda/kernels/portable_model.cu:1448-1716.
+#include <cstdlib>
+
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
 
@@ -280,26 +282,6 @@ gemv_kernel(const GemvParams p) {
         }
         valid[j] = prow[j] >= p.row_begin && prow[j] < p.row_begin + p.rows;
         urow[j] = p.row_begin2 + (prow[j] - p.row_begin);
-    }
-
-    // Ask for this warp's weight rows before anything else: the lines travel from HBM to L2 while
-    // the block stages its activations, and the loads further down then find them there.
-    if (FMT != VELOX_FMT_NVFP4) {
-        const long long row_bytes = FMT == VELOX_FMT_FP8_ROW_BF16 ? p.k : p.k / 256 * 144;
-#pragma unroll
-        for (int j = 0; j < GEMV_R; j++) {
-            if (!valid[j]) continue;
-            const uint8_t* r1 = p.w + prow[j] * row_bytes;
-            for (long long off = (long long)lane * 128 - (long long)(reinterpret_cast<uintptr_t>(r1) & 127); off < row_bytes;
-                 off += 32 * 128)
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(r1 + (off < 0 ? 0 : off)));
-            if (SWIGLU) {
-                const uint8_t* r2 = p.w2 + urow[j] * row_bytes;
-                for (long long off = (long long)lane * 128 - (long long)(reinterpret_cast<uintptr_t>(r2) & 127); off < row_bytes;
-                     off += 32 * 128)
-                    asm volatile("prefetch.global.L2 [%0];" ::"l"(r2 + (off < 0 ? 0 : off)));
-            }
-        }
     }
 
     // Stage this pass's tokens as bf16, chunk c of tile T at slot c ^ (T & 7) (conflict-free

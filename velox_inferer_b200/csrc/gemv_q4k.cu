@@ -15,8 +15,8 @@
 // warp, lane (g, t) loads 8 bytes of each of its four rows per 64-weight chunk: the dot product
 // does not care about the order along K, so the K slots of the MMA are assigned to whatever
 // bytes a lane holds and the activations are fetched in the matching order (one 16-byte load of
-// eight consecutive bf16 per group and token tile, from L1). Each warp asks for its weight bytes
-// with L2 prefetches before anything else.
+// eight consecutive bf16 per group and token tile, from L1). (Asking for the weight bytes with L2
+// prefetches at block start made the kernel slower, by 10 to 20 %, and is not done.)
 //
 // Reference counterpart: linear_gemv_ggml_kernel, crates/velox-cuda/kernels/portable_model.cu:1628-1716.
 #include <cstdlib>
@@ -91,7 +91,7 @@ __device__ __forceinline__ void q4k_group_factors(const Q4kHead& h, float& ds, f
 }
 
 template <int MT, int NB, int QM_WARPS, bool PIPE>
-__global__ void __launch_bounds__(QM_WARPS * 32, !PIPE ? 7 : QM_WARPS == 2 ? 7 : NB == 1 ? 4 : 2) gemv_q4k_mma_kernel(const Q4kParams p) {
+__global__ void __launch_bounds__(QM_WARPS * 32, QM_WARPS == 8 ? (NB == 1 ? 3 : 2) : !PIPE ? 7 : QM_WARPS == 2 ? 7 : NB == 1 ? 4 : 2) gemv_q4k_mma_kernel(const Q4kParams p) {
     constexpr int QM_ROWS = 16 * MT;   // weight rows per block: MT row tiles of the MMA; QM_WARPS: K parts, one per warp
     __shared__ float red[QM_WARPS - 1][MT * NB * 4][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -100,18 +100,6 @@ __global__ void __launch_bounds__(QM_WARPS * 32, !PIPE ? 7 : QM_WARPS == 2 ? 7 :
     const int kb0 = warp * bt / QM_WARPS, kb1 = (warp + 1) * bt / QM_WARPS;
     const long long r_first = p.row_begin + (long long)blockIdx.x * QM_ROWS;
     const long long r_last = p.row_begin + p.rows - 1;
-
-    // this warp's weight bytes: on their way from HBM to L2 before the first load needs them
-    {
-        const long long bytes = (long long)(kb1 - kb0) * 144;
-        for (int r = 0; r < QM_ROWS; r++) {
-            const long long row = r_first + r < r_last ? r_first + r : r_last;
-            const uint8_t* b = p.w + row * row_bytes + (long long)kb0 * 144;
-            for (long long off = (long long)lane * 128 - (long long)(reinterpret_cast<uintptr_t>(b) & 127); off < bytes;
-                 off += 32 * 128)
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(b + (off < 0 ? 0 : off)));
-        }
-    }
 
     // the lane's rows: tile mt, half h -> row r_first + 16 mt + 8 h + g (a row past the view reads the last one)
     const uint8_t* rp[MT][2];
@@ -323,6 +311,13 @@ int gemv_q4k_mma(const LinearArgs& a) {
     // Up to eight tokens: four K parts per block, loads at the top of each block of K (72 registers,
     // seven blocks per SM). More tokens: the next block's weight bytes are requested a block ahead,
     // which costs 24 registers per row tile, so two K parts per block keep every block resident.
+    // Few row tiles with a long K (a down projection): eight K parts per block, so that the machine
+    // still has warps to hide latency with.
+    if (one && (long long)blocks * 4 < 12LL * sms && k >= 8 * 256) {
+        if (a.m <= 8) gemv_q4k_mma_kernel<1, 1, 8, false><<<blocks, 256, 0, stream()>>>(p);
+        else gemv_q4k_mma_kernel<1, 2, 8, false><<<blocks, 256, 0, stream()>>>(p);
+        return launch_status();
+    }
     if (a.m <= 8) {
         if (one) gemv_q4k_mma_kernel<1, 1, 4, false><<<blocks, 128, 0, stream()>>>(p);
         else gemv_q4k_mma_kernel<2, 1, 4, true><<<blocks, 128, 0, stream()>>>(p);
