@@ -319,6 +319,8 @@ def _swiglu_want(x, payload_g, payload_u, fmt, ng, nu, k, bg, bu, w, m, act):
 @pytest.mark.parametrize("fmt,k,w,m,order", [
     (NV, 512, 256, 1, "gate_up"), (NV, 512, 256, 7, "up_gate"), (NV, 1024, 128, 16, "split"),
     (F8, 512, 96, 4, "gate_up"), (Q4, 512, 40, 3, "split"),
+    # Q4_K pairs on the MMA kernel: both row orders in one parent, ragged rows, one and two token tiles
+    (Q4, 1024, 72, 1, "gate_up"), (Q4, 2560, 100, 8, "up_gate"), (Q4, 512, 200, 13, "gate_up"),
 ])
 def test_linear_swiglu_fused_matches_composed_oracle(b, fmt, k, w, m, order):
     # both row orders in one parent and separate parents: conformance lib.rs:3856-3861

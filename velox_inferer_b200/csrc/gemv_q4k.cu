@@ -4,10 +4,11 @@
 // (crates/velox-core/src/ggml.rs:159-210). Unpacking q to a float and multiplying it costs a general
 // ALU two to three instructions per weight and per token, which bounds the SIMT kernel well below the
 // memory rate as soon as there is more than one token. Here q goes to bf16 with one byte permute
-// per two weights (0x4300 | q is the bf16 number 128 + q, exactly) and mma.sync.m16n8k16 multiplies
+// per two weights (0x4180 | q << 3 is the bf16 number 16 + q, exactly; a larger offset would be a plain
+// byte insert but costs accuracy: the offset's share of the sum cancels only in the epilogue) and mma.sync.m16n8k16 multiplies
 // sixteen rows by eight tokens at once, the tokens as the B operand in bf16 (ActQuant::Bf16, which
-// every policy admits). Per 32-weight group the MMA result c = sum((128 + q) x) is folded into the
-// running sums as d sc c - (128 d sc + dmin mn) sum(x); sum(x) per group and token comes from an MMA
+// every policy admits). Per 32-weight group the MMA result c = sum((16 + q) x) is folded into the
+// running sums as d sc c - (16 d sc + dmin mn) sum(x); sum(x) per group and token comes from an MMA
 // whose A operand is all ones, which delivers it in the accumulator layout at once.
 //
 // Work split: a block owns 16 or 32 rows (one or two MMA row tiles); its four warps each take a quarter of K
@@ -32,6 +33,8 @@ struct Q4kParams {
     const uint8_t* w;
     long long k, row_begin;
     int rows;
+    const uint8_t* w2;    // fused SwiGLU form: the up view (w is the gate view), same k and row count
+    long long row_begin2;
     const uint16_t* xb;   // [m, k] bf16
     int m;
     float* y;
@@ -79,7 +82,7 @@ __device__ __forceinline__ Q4kHead q4k_head(const uint4& h) {
     return r;
 }
 
-// d sc and 128 d sc + dmin mn of group S (a compile-time index): byte -> float by placing it in the
+// d sc and 16 d sc + dmin mn of group S (a compile-time index): byte -> float by placing it in the
 // mantissa of 2^23, the 2^23 taken off inside the multiply-add.
 template <int S>
 __device__ __forceinline__ void q4k_group_factors(const Q4kHead& h, float& ds, float& off) {
@@ -87,10 +90,10 @@ __device__ __forceinline__ void q4k_group_factors(const Q4kHead& h, float& ds, f
     const float scf = __uint_as_float(__byte_perm(scw, 0x4B000000u, 0x7440u | (uint32_t)(S & 3)));
     const float mnf = __uint_as_float(__byte_perm(mnw, 0x4B000000u, 0x7440u | (uint32_t)(S & 3)));
     ds = fmaf(h.d, scf, h.nd23);
-    off = fmaf(128.0f, ds, fmaf(h.dmin, mnf, h.ndmin23));
+    off = fmaf(16.0f, ds, fmaf(h.dmin, mnf, h.ndmin23));
 }
 
-template <int MT, int NB, int QM_WARPS, bool PIPE>
+template <int MT, int NB, int QM_WARPS, bool PIPE, bool SWIGLU = false>
 __global__ void __launch_bounds__(QM_WARPS * 32, QM_WARPS == 8 ? (NB == 1 ? 3 : 2) : !PIPE ? 7 : QM_WARPS == 2 ? 7 : NB == 1 ? 4 : 2) gemv_q4k_mma_kernel(const Q4kParams p) {
     constexpr int QM_ROWS = 16 * MT;   // weight rows per block: MT row tiles of the MMA; QM_WARPS: K parts, one per warp
     __shared__ float red[QM_WARPS - 1][MT * NB * 4][32];
@@ -101,23 +104,8 @@ __global__ void __launch_bounds__(QM_WARPS * 32, QM_WARPS == 8 ? (NB == 1 ? 3 : 
     const long long r_first = p.row_begin + (long long)blockIdx.x * QM_ROWS;
     const long long r_last = p.row_begin + p.rows - 1;
 
-    // the lane's rows: tile mt, half h -> row r_first + 16 mt + 8 h + g (a row past the view reads the last one)
+    float acc[MT][NB][4], gate[MT][NB][4];   // (gate: the first pass of the fused SwiGLU form)
     const uint8_t* rp[MT][2];
-#pragma unroll
-    for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            const long long r = r_first + 16 * mt + 8 * h + g;
-            rp[mt][h] = p.w + (r < r_last ? r : r_last) * row_bytes;
-        }
-
-    float acc[MT][NB][4];
-#pragma unroll
-    for (int mt = 0; mt < MT; mt++)
-#pragma unroll
-        for (int nb = 0; nb < NB; nb++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[mt][nb][i] = 0.0f;
 
     // token rows of this lane's B fragments
     const uint16_t* xrow[NB];
@@ -142,6 +130,26 @@ __global__ void __launch_bounds__(QM_WARPS * 32, QM_WARPS == 8 ? (NB == 1 ? 3 : 
 #pragma unroll
         for (int nb = 0; nb < NB; nb++) b[nb] = __ldg(reinterpret_cast<const uint4*>(xrow[nb] + k0));
     };
+    // Plain form: one pass over the view. Fused SwiGLU: the gate view, then the up view's rows at the
+    // same offsets; silu(gate) * up is formed after both sums are complete.
+#pragma unroll 1
+    for (int pass = 0; pass < (SWIGLU ? 2 : 1); pass++) {
+    const uint8_t* wbase = pass == 0 ? p.w : p.w2;
+    const long long shift = pass == 0 ? 0 : p.row_begin2 - p.row_begin;
+    // the lane's rows: tile mt, half h -> row r_first + 16 mt + 8 h + g (a row past the view reads the last one)
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const long long r = r_first + 16 * mt + 8 * h + g;
+            rp[mt][h] = wbase + ((r < r_last ? r : r_last) + shift) * row_bytes;
+        }
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+        for (int nb = 0; nb < NB; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[mt][nb][i] = 0.0f;
     uint4 bx[NB];
     uint4 raw_head[MT][2];
     uint2 qs[MT][2][4];
@@ -179,16 +187,18 @@ __global__ void __launch_bounds__(QM_WARPS * 32, QM_WARPS == 8 ? (NB == 1 ? 3 : 
 #pragma unroll
             for (int mt = 0; mt < MT; mt++) {
                 const uint2 qa = qs[mt][0][c], qb = qs[mt][1][c];
-                const uint32_t a_lo = (half ? (qa.x >> 4) : qa.x) & 0x0f0f0f0fu;   // values 8t .. 8t+3 of row g
-                const uint32_t a_hi = (half ? (qa.y >> 4) : qa.y) & 0x0f0f0f0fu;   // values 8t+4 .. 8t+7
-                const uint32_t b_lo = (half ? (qb.x >> 4) : qb.x) & 0x0f0f0f0fu;   // the same of row g + 8
-                const uint32_t b_hi = (half ? (qb.y >> 4) : qb.y) & 0x0f0f0f0fu;
-                // bf16 pairs 128 + q: K slots (2t, 2t+1) and (2t+8, 2t+9) of the first MMA take values
-                // 8t .. 8t+3, those of the second take 8t+4 .. 8t+7
-                const uint32_t a0 = __byte_perm(a_lo, 0x43434343u, 0x4140u), a2 = __byte_perm(a_lo, 0x43434343u, 0x4342u);
-                const uint32_t a1 = __byte_perm(b_lo, 0x43434343u, 0x4140u), a3 = __byte_perm(b_lo, 0x43434343u, 0x4342u);
-                const uint32_t e0 = __byte_perm(a_hi, 0x43434343u, 0x4140u), e2 = __byte_perm(a_hi, 0x43434343u, 0x4342u);
-                const uint32_t e1 = __byte_perm(b_hi, 0x43434343u, 0x4140u), e3 = __byte_perm(b_hi, 0x43434343u, 0x4342u);
+                // each nibble to the top of a bf16 mantissa: the byte 0x80 | q << 3 under the byte 0x41 is
+                // the bf16 number 16 + q
+                const uint32_t a_lo = ((half ? (qa.x >> 1) : (qa.x << 3)) & 0x78787878u) | 0x80808080u;   // values 8t .. 8t+3 of row g
+                const uint32_t a_hi = ((half ? (qa.y >> 1) : (qa.y << 3)) & 0x78787878u) | 0x80808080u;   // values 8t+4 .. 8t+7
+                const uint32_t b_lo = ((half ? (qb.x >> 1) : (qb.x << 3)) & 0x78787878u) | 0x80808080u;   // the same of row g + 8
+                const uint32_t b_hi = ((half ? (qb.y >> 1) : (qb.y << 3)) & 0x78787878u) | 0x80808080u;
+                // K slots (2t, 2t+1) and (2t+8, 2t+9) of the first MMA take values 8t .. 8t+3, those of
+                // the second take 8t+4 .. 8t+7
+                const uint32_t a0 = __byte_perm(a_lo, 0x41414141u, 0x4140u), a2 = __byte_perm(a_lo, 0x41414141u, 0x4342u);
+                const uint32_t a1 = __byte_perm(b_lo, 0x41414141u, 0x4140u), a3 = __byte_perm(b_lo, 0x41414141u, 0x4342u);
+                const uint32_t e0 = __byte_perm(a_hi, 0x41414141u, 0x4140u), e2 = __byte_perm(a_hi, 0x41414141u, 0x4342u);
+                const uint32_t e1 = __byte_perm(b_hi, 0x41414141u, 0x4140u), e3 = __byte_perm(b_hi, 0x41414141u, 0x4342u);
                 float ds_a, off_a, ds_b, off_b;
                 q4k_group_factors<S>(head[mt][0], ds_a, off_a);
                 q4k_group_factors<S>(head[mt][1], ds_b, off_b);
@@ -225,7 +235,39 @@ __global__ void __launch_bounds__(QM_WARPS * 32, QM_WARPS == 8 ? (NB == 1 ? 3 : 
             }
     }
 
-    // add the four K parts in warp order
+    if (SWIGLU && pass == 0) {
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+            for (int nb = 0; nb < NB; nb++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) gate[mt][nb][i] = acc[mt][nb][i];
+    }
+    }   // pass
+
+    // add the K parts in warp order (the gate sums first, through the same buffer)
+    if (SWIGLU) {
+        if (warp > 0) {
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                for (int nb = 0; nb < NB; nb++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) red[warp - 1][(mt * NB + nb) * 4 + i][lane] = gate[mt][nb][i];
+        }
+        __syncthreads();
+        if (warp == 0) {
+#pragma unroll
+            for (int w = 0; w < QM_WARPS - 1; w++)
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+                    for (int nb = 0; nb < NB; nb++)
+#pragma unroll
+                        for (int i = 0; i < 4; i++) gate[mt][nb][i] += red[w][(mt * NB + nb) * 4 + i][lane];
+        }
+        __syncthreads();
+    }
     if (warp > 0) {
 #pragma unroll
         for (int mt = 0; mt < MT; mt++)
@@ -258,7 +300,11 @@ __global__ void __launch_bounds__(QM_WARPS * 32, QM_WARPS == 8 ? (NB == 1 ? 3 : 
                 for (int i = 0; i < 2; i++) {
                     const int tok = nb * 8 + 2 * t + i;
                     if (tok >= p.m) continue;
-                    const float v = acc[mt][nb][2 * h + i];
+                    float v = acc[mt][nb][2 * h + i];
+                    if (SWIGLU) {
+                        const float gv = gate[mt][nb][2 * h + i];
+                        v = gv / (1.0f + expf(-gv)) * v;
+                    }
                     const long long o = (long long)tok * p.ld + p.col + (r - p.row_begin);
                     if (p.y) p.y[o] = v;
                     if (p.yb) p.yb[o] = bf16_bits(v);
@@ -268,7 +314,7 @@ __global__ void __launch_bounds__(QM_WARPS * 32, QM_WARPS == 8 ? (NB == 1 ? 3 : 
 
 int gemv_q4k_mma(const LinearArgs& a) {
     static const bool off = getenv("VELOX_SM100_Q4K_SIMT") != nullptr;
-    if (off || a.swiglu || a.w.format != VELOX_FMT_GGML_Q4_K || a.w.k % 256 != 0 || a.m < 1 || a.m > 16 ||
+    if (off || a.w.format != VELOX_FMT_GGML_Q4_K || a.w.k % 256 != 0 || a.m < 1 || a.m > 16 ||
         a.w.rows < 1 || (reinterpret_cast<uintptr_t>(a.w.w) & 15))
         return VELOX_ERR_UNSUPPORTED;
     const long long k = a.w.k;
@@ -287,6 +333,15 @@ int gemv_q4k_mma(const LinearArgs& a) {
     p.k = k;
     p.row_begin = a.w.row_begin;
     p.rows = (int)a.w.rows;
+    p.w2 = nullptr;
+    p.row_begin2 = 0;
+    if (a.swiglu) {
+        if (a.up.format != VELOX_FMT_GGML_Q4_K || a.up.k != k || a.up.rows != a.w.rows ||
+            (reinterpret_cast<uintptr_t>(a.up.w) & 15))
+            return VELOX_ERR_UNSUPPORTED;
+        p.w2 = a.up.w;
+        p.row_begin2 = a.up.row_begin;
+    }
     p.xb = xb;
     p.m = a.m;
     p.y = a.y;
@@ -311,6 +366,12 @@ int gemv_q4k_mma(const LinearArgs& a) {
     // Up to eight tokens: four K parts per block, loads at the top of each block of K (72 registers,
     // seven blocks per SM). More tokens: the next block's weight bytes are requested a block ahead,
     // which costs 24 registers per row tile, so two K parts per block keep every block resident.
+    if (a.swiglu) {
+        const unsigned gblocks = (unsigned)((a.w.rows + 15) / 16);
+        if (a.m <= 8) gemv_q4k_mma_kernel<1, 1, 4, false, true><<<gblocks, 128, 0, stream()>>>(p);
+        else gemv_q4k_mma_kernel<1, 2, 2, true, true><<<gblocks, 64, 0, stream()>>>(p);
+        return launch_status();
+    }
     // Few row tiles with a long K (a down projection): eight K parts per block, so that the machine
     // still has warps to hide latency with.
     if (one && (long long)blocks * 4 < 12LL * sms && k >= 8 * 256) {
