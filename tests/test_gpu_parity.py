@@ -113,6 +113,7 @@ GEMV_CASES = [
     # counts, and row counts large enough for two row tiles per block
     (Q4, 100, 256, 5, 77, 11), (Q4, 72, 5120, 0, 72, 4), (Q4, 2100, 1024, 16, 2050, 2),
     (Q4, 28700, 256, 0, 28700, 3), (Q4, 28700, 512, 9, 28650, 12),
+    (Q4, 48, 25600, 0, 48, 2),    # a down projection's K: eight K parts per block, the longest sums
 ]
 
 
