@@ -4,20 +4,23 @@
 // (crates/velox-core/src/ggml.rs:159-210). Unpacking q to a float and multiplying it costs a general
 // ALU two to three instructions per weight and per token, which bounds the SIMT kernel well below the
 // memory rate as soon as there is more than one token. Here q goes to bf16 with one byte permute
-// per two weights (0x4180 | q << 3 is the bf16 number 16 + q, exactly; a larger offset would be a plain
-// byte insert but costs accuracy: the offset's share of the sum cancels only in the epilogue) and mma.sync.m16n8k16 multiplies
-// sixteen rows by eight tokens at once, the tokens as the B operand in bf16 (ActQuant::Bf16, which
-// every policy admits). Per 32-weight group the MMA result c = sum((16 + q) x) is folded into the
-// running sums as d sc c - (16 d sc + dmin mn) sum(x); sum(x) per group and token comes from an MMA
-// whose A operand is all ones, which delivers it in the accumulator layout at once.
+// per two weights (0x4180 | q << 3 is the bf16 number 16 + q, exactly; an offset of 128 would be a
+// plain byte insert but costs accuracy, because the offset's share of the sum cancels only in the
+// epilogue) and mma.sync.m16n8k16 multiplies sixteen rows by eight tokens at once, the tokens as
+// the B operand in bf16 (ActQuant::Bf16, which every policy admits). Per 32-weight group the MMA
+// result c = sum((16 + q) x) is folded into the running sums as d sc c - (16 d sc + dmin mn) sum(x);
+// sum(x) per group and token comes from an MMA whose A operand is all ones, which delivers it in
+// the accumulator layout at once. The fused SwiGLU form runs the gate view and then the up view
+// through the same loop and forms silu(gate) * up from the two complete sums.
 //
-// Work split: a block owns 16 or 32 rows (one or two MMA row tiles); its four warps each take a quarter of K
-// and the parts are added in warp order at the end, so results do not depend on timing. Within a
-// warp, lane (g, t) loads 8 bytes of each of its four rows per 64-weight chunk: the dot product
-// does not care about the order along K, so the K slots of the MMA are assigned to whatever
-// bytes a lane holds and the activations are fetched in the matching order (one 16-byte load of
-// eight consecutive bf16 per group and token tile, from L1). (Asking for the weight bytes with L2
-// prefetches at block start made the kernel slower, by 10 to 20 %, and is not done.)
+// Work split: a block owns 16 or 32 rows (one or two MMA row tiles); its warps (two, four or eight)
+// each take a part of K and the parts are added in warp order at the end, so results do not depend
+// on timing. Within a warp, lane (g, t) loads 8 bytes of each of its rows per 64-weight chunk: the
+// dot product does not care about the order along K, so the K slots of the MMA are assigned to
+// whatever bytes a lane holds and the activations are fetched in the matching order (one 16-byte
+// load of eight consecutive bf16 per group and token tile, from L1, one step ahead). Asking for
+// the weight bytes with L2 prefetches at block start made the kernel 10 to 20 % slower and is not
+// done.
 //
 // Reference counterpart: linear_gemv_ggml_kernel, crates/velox-cuda/kernels/portable_model.cu:1628-1716.
 #include <cstdlib>
