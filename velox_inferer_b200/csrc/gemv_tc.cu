@@ -8,16 +8,20 @@
 // are - weight rows are the MMA M operand (128), the tokens the N operand (16 or 64, zero padded), the
 // activations NVFP4 with the view's per-tensor divisor (ActQuant::Nvfp4, which the view's AllowA4
 // policy admits at any m). An MMA of this shape takes a few tens of cycles, so a CTA is idle
-// unless bytes arrive: the ring (eight 18 KB stages) is what sets the speed.
+// unless bytes arrive: the ring (eight stages of 18 KB, or 24 KB with 64 token columns) is what sets
+// the speed.
 //
 // Work is cut by bytes, not by tiles: the (tile, k-block) steps of the whole matrix are laid end to
 // end and every CTA takes an equal contiguous run of them, so a run starts and ends inside tiles.
 // A CTA that holds only part of a tile's K parks f32 partial sums; the CTA that arrives last at
 // the tile adds the parts in K order, so the result does not depend on arrival order. Roles:
-//   warp 0      operand producer (TMA: W codes box + the x codes box, 16 rows);
+//   warp 0      operand producer (TMA: W codes box + the x codes box, 16 or 64 rows);
 //   warp 1      MMA issuer (one elected lane), accumulators double-buffered in tensor memory;
 //   warp 2      scale producer (bulk copies of whole atoms, W then x);
-//   warps 4-7   epilogue: tcgen05.ld, K-split fix-up, per-tensor factors, optional silu(gate)*up;
+//   warps 4-7   epilogue: tcgen05.ld, K-split fix-up, per-tensor factors, optional silu(gate)*up, and
+//               optionally the result as the next linear's NVFP4 input; one rolled code instance,
+//               because this code runs once or twice per CTA and cold instruction lines cost as
+//               much as memory round trips;
 //   warps 8-11  scale movers: shared memory -> tensor memory (tcgen05.st), one per lane quadrant.
 // FP8-E4M3 rows with FP8-row activations (ActQuant::Fp8Row, views that admit it) take the same
 // route without the scale roles: kind::f8f6f4, 128 k per stage, the bf16 row scale and the f32
@@ -242,7 +246,7 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
         uint32_t phase = 0;
         bool ok = true;
         const bool leader = elect_one();
-        // M = 128, N = 16, E2M1 x E2M1 with UE4M3 block scales, K-major operands, f32 accumulate
+        // M = 128, N = NT, E2M1 x E2M1 with UE4M3 block scales, K-major operands, f32 accumulate
         const uint32_t shape = ((uint32_t)(NT >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
         const uint32_t idesc = KIND == KIND_MXF4 ? ((1u << 7) | (1u << 10) | shape)   // E2M1 x E2M1, UE4M3 scales
                                                  : ((1u << 4) | shape);                // E4M3 x E4M3 -> f32
