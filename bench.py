@@ -416,14 +416,14 @@ def _time_replays(replay, launches_per_replay, gpu_index=0, warm_s=0.2, timed_s=
     e1.record()
     torch.cuda.synchronize()
     per_replay_s = max(e0.elapsed_time(e1) * 1e-3, 1e-6)
+    sampler = ClockSampler(gpu_index)   # (sees the warm-up too: the same work, and nvidia-smi takes a moment to start)
+    sampler.start()
     t_end = time.time() + warm_s
     while time.time() < t_end:
         for _ in range(8):
             replay()
         torch.cuda.synchronize()
     n = max(3, int(timed_s / per_replay_s))
-    sampler = ClockSampler(gpu_index)
-    sampler.start()
     e0.record()
     for _ in range(n):
         replay()
