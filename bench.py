@@ -13,7 +13,10 @@ tokens/s of the whole job. ``--workload decode`` runs the same stack at M = 1.
 One JSON line is printed by rank 0. ``value`` has inputs resident in HBM; ``e2e`` copies the
 step's activations from pinned host memory and reads the result back inside the timed region.
 ``roofline`` is for the dominant kernel (the tcgen05 NVFP4 GEMM at M = 2048, the streaming GEMV at
-M = 1), timed with CUDA events on its launch stream inside the timed region. ``cpu_baseline`` times
+M = 1), timed with CUDA events on its launch stream inside the timed region; at N = 1 its
+``components`` carry the rest of the headline metric (single-linear decode GEMV GB/s and prefill
+TFLOP/s, the M sweep, the MLP, the other stored formats, the decode stack). With N > 1 an untimed
+check of a two-layer stack runs first and is printed as ``config.tp_check``. ``cpu_baseline`` times
 the CPU oracle on a bounded sample of the same workload. Data is synthetic (seeded N(0, 0.02^2)
 weights, N(0, 1) activations).
 """
@@ -100,8 +103,9 @@ class ClockSampler:
 
 def cpu_baseline_sample(spec, m_tokens: int, seconds_target: float = 12.0, threads: int = 0):
     """The CPU oracle (row-parallel over all host threads, f64 accumulation, same arithmetic as the
-    reference's velox-cpu) on a bounded sample: a row slice of one gate projection. Returns
-    (tokens/s the whole stack would reach at that MAC rate, cores, description)."""
+    reference's velox-cpu) on a bounded sample: an NVFP4 linear of the stack's width K with 256
+    weight rows (a matrix of its own, built with the stack's weight construction) at up to 64
+    tokens. Returns (tokens/s the whole stack would reach at that MAC rate, cores, description)."""
     import numpy as np
     from oracle import oracle as O
 
@@ -131,8 +135,9 @@ def cpu_baseline_sample(spec, m_tokens: int, seconds_target: float = 12.0, threa
     # at decode width the oracle re-decodes the weights every call, exactly as velox-cpu does
     mac_per_token = spec.flops_per_token() / 2
     tok_s = (macs / dt) / mac_per_token * (1.0 if m_tokens > 16 else 1.0)
-    sample = (f"{reps} x oracle linear NVFP4 rows 256 of [25600,{k}] at m={m} ({macs / 1e9:.1f} GMAC in "
-              f"{dt:.1f} s), scaled by the stack's {mac_per_token / 1e9:.1f} GMAC per token")
+    sample = (f"{reps} x oracle linear on an NVFP4 [{n},{k}] matrix (the stack's K and weight construction; not a "
+              f"slice of a stack matrix) at m={m}: {macs / 1e9:.1f} GMAC in {dt:.1f} s, scaled to tokens/s by the "
+              f"stack's {mac_per_token / 1e9:.1f} GMAC per token (extrapolated, not a whole step)")
     return tok_s, cores, sample, dt / reps
 
 
@@ -156,7 +161,7 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * m / tok_s,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f64 accumulate over NVFP4",
         "data": "synthetic",
-        "config": workload_config(args, spec, m, args.gpus > 1 and args.tp == "fused"),
+        "config": workload_config(args, spec, m, args.tp if args.gpus > 1 and args.tp != "nccl" else False),
         "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -169,11 +174,67 @@ def workload_config(args, spec, m, fused_tp=False):
             "tokens_per_step": m, "layers": spec.layers,
             "parallelism": f"tp{args.gpus}: column-split q/k/v/gate/up, row-split o/down, "
                            + ("bf16 partial tiles stored into the owning rank's rows by the GEMM epilogue over NVLink "
-                              "(reduce-scatter), NVFP4 norm output stored into every rank (all-gather), "
-                              "signal-pad barriers" if fused_tp else "bf16 all-reduce (NCCL) after o and down"),
+                              "(reduce-scatter), NVFP4 norm output stored into every rank (all-gather), ordered by "
+                              "per-phase flags in peer memory (bounded waits)" if fused_tp == "flags" else
+                              "the same with signal-pad barrier kernels between the phases" if fused_tp == "barrier" else
+                              "bf16 all-reduce (NCCL) after o and down"),
             "activations": "NVFP4 tensor-core operands written by the producing kernels (ActQuant::Nvfp4, "
                            "per-use divisors 256/128/16); f32 residual stream; bf16 step input and output",
             "l2": "each step streams the layers' distinct weights, far larger than the 126 MB L2"}
+
+
+def tp_check(b, args, rank, world, m):
+    """Untimed correctness check of the sharded step at this rank count, on a two-layer stack of the
+    benchmark's geometry: the fused step equals the library-collective step with the same arithmetic
+    bit for bit (twice: buffers and flags are reused), every rank ends with the same output, and
+    both stay as close to the unsharded step (run on every rank's own GPU) as the all-reduce step."""
+    import torch
+    import torch.distributed as dist
+
+    from velox_inferer_b200.stack import LinearStack, StackSpec
+
+    spec = StackSpec(layers=2)
+    gen = torch.Generator().manual_seed(4321)
+    xb = torch.randn(m, spec.hidden, generator=gen).to(torch.bfloat16).to(b.device)
+    n = m * spec.hidden
+
+    def rel_rms(a, c):
+        return float(((a.float() - c.float()).pow(2).mean().sqrt() / c.float().pow(2).mean().sqrt()).item())
+
+    chk = LinearStack(b, spec, max_tokens=m, rank=rank, world=world, a4=True, seed=0)
+    allreduce = chk.forward(xb, m).view(-1)[:n].clone()
+    gathered = chk.forward_gathered(xb, m).view(-1)[:n].clone()
+    out = {"layers": spec.layers, "m": m}
+    fused_ok = None
+    if args.tp != "nccl" and chk.enable_fused_tp(m, sync_mode=args.tp):
+        fused_ok = True
+        for _ in range(2):
+            fused = chk.forward_fused_tp(xb).view(-1)[:n].clone()
+            torch.cuda.synchronize()
+            fused_ok = fused_ok and bool(torch.equal(fused, gathered)) and b.debug_status() == 0
+        mine = fused
+    else:
+        mine = gathered
+    flag = torch.tensor([1 if fused_ok in (True, None) else 0], device=b.device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    out["fused_equals_gathered_bitwise"] = None if fused_ok is None else bool(flag.item())
+    ref = mine.clone()
+    dist.broadcast(ref, src=0)
+    same = torch.tensor([1 if torch.equal(ref, mine) else 0], device=b.device)
+    dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    out["ranks_hold_equal_output"] = bool(same.item())
+    del chk
+    whole = LinearStack(b, spec, max_tokens=m, rank=0, world=1, a4=True, seed=0).forward(xb, m).view(-1)[:n].clone()
+    out["rel_rms_vs_unsharded"] = round(rel_rms(mine, whole), 5)
+    out["rel_rms_allreduce_vs_unsharded"] = round(rel_rms(allreduce, whole), 5)
+    out["note"] = ("sharded steps round each shard's partial sums to bf16 and NVFP4 activation quantisation reacts to "
+                   "last-bit differences, so agreement with the unsharded step is statistical; the exact check is "
+                   "fused == gathered")
+    out["ok"] = bool(out["ranks_hold_equal_output"] and out["fused_equals_gathered_bitwise"] is not False
+                     and out["rel_rms_vs_unsharded"] <= 2.0 * out["rel_rms_allreduce_vs_unsharded"] + 0.01)
+    del whole
+    torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -183,18 +244,24 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill", choices=["prefill", "decode", "linear"],
-                    help="prefill / decode: the layer stack at M = --m / M = 1; linear: only the single "
-                         "[25600, 5120] NVFP4 linear at M = 1 and M = 2048 (the profiling target)")
+                    help="prefill / decode: the layer stack at M = --m / M = 1; linear: only the single-linear "
+                         "components (the profiling target)")
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=64)
     ap.add_argument("--no-components", action="store_true", help="skip the single-linear GEMV / GEMM lines")
+    ap.add_argument("--components", default="all",
+                    help="comma-separated subset of: nvfp4,sweep,mlp,formats,decode_stack (default all)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--tp", choices=("fused", "nccl"), default="fused",
+    ap.add_argument("--no-tp-check", action="store_true")
+    ap.add_argument("--tp", choices=("flags", "barrier", "nccl", "fused"), default="flags",
                     help="N > 1: communication fused into the GEMM epilogue and the norm over symmetric memory, "
-                         "or one NCCL all-reduce after o and down")
+                         "ordered by flags in peer memory (flags; 'fused' is the same) or by barrier kernels "
+                         "(barrier), or one NCCL all-reduce after o and down (nccl)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
+    if args.tp == "fused":
+        args.tp = "flags"
 
     if args.impl == "reference":
         run_reference(args)
@@ -203,7 +270,7 @@ def main():
     import torch
     import torch.distributed as dist
 
-    from velox_inferer_b200 import ActPolicy, Sm100Backend, WeightFormat, WeightView
+    from velox_inferer_b200 import Sm100Backend
     from velox_inferer_b200.stack import LinearStack, StackSpec
 
     rank = int(os.environ.get("RANK", "0"))
@@ -216,13 +283,19 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     b = Sm100Backend(local)
+    peaks = measured_peaks()
     if args.workload == "linear":
         print(json.dumps({"metric": "nvfp4_single_linear", "n_gpus": 1, "data": "synthetic",
-                          "components": components(b, measured_peaks(), graph=not args.no_graph)}), flush=True)
+                          "components": components(b, peaks, None, args, graph=not args.no_graph)}), flush=True)
         return
     spec = StackSpec(layers=args.layers)
     m = 1 if args.workload == "decode" else args.m
-    peaks = measured_peaks()
+
+    check = None
+    if world > 1 and m > 16 and not args.no_tp_check:
+        check = tp_check(b, args, rank, world, m)
+        if not check["ok"]:
+            raise SystemExit(f"[bench] the sharded step failed its correctness check: {check}")
 
     stack = LinearStack(b, spec, max_tokens=m, rank=rank, world=world, a4=True, seed=0)
     gen = torch.Generator().manual_seed(1234)
@@ -236,9 +309,9 @@ def main():
         torch.cuda.synchronize()
 
     fused_tp = False
-    if world > 1 and args.tp == "fused":
+    if world > 1 and args.tp != "nccl":
         try:
-            fused_tp = stack.enable_fused_tp(m)
+            fused_tp = stack.enable_fused_tp(m, sync_mode=args.tp)
         except Exception as exc:  # symmetric memory not available here: the NCCL step still is
             print(f"[bench] fused tensor parallelism not available ({exc}); using NCCL all-reduce",
                   file=sys.stderr, flush=True)
@@ -247,18 +320,20 @@ def main():
         forward()
     barrier()
 
-    # A step is hundreds of launches (and, with several ranks, two all-reduces per layer): it is
-    # captured once and replayed as one CUDA graph, as the reference runs its step
-    # (crates/velox-cuda/src/lib.rs:2130-2204), unless --no-graph is given or capture fails. Event
-    # timing of single kernels is not possible inside a graph, so the roofline pass runs eagerly.
+    # A step is hundreds of launches: it is captured once and replayed as one CUDA graph, as the
+    # reference runs its step (crates/velox-cuda/src/lib.rs:2130-2204), unless --no-graph is given
+    # or capture fails. Event timing of single kernels is not possible inside a graph, so the
+    # roofline pass runs eagerly.
     step = forward
     use_graph = not args.no_graph
+    graph = None
     if use_graph:
         try:
             side = torch.cuda.Stream()
             with torch.cuda.stream(side):
                 forward()
             torch.cuda.synchronize()
+            barrier()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=side):
                 forward()
@@ -270,8 +345,8 @@ def main():
             use_graph = False
             step = forward
         barrier()
-    if b.lib.velox_sm100_debug_status() != 0:
-        raise SystemExit("tensor-core kernel reported a timed-out wait")
+    if b.debug_status() != 0:
+        raise SystemExit("a kernel reported a wait that ran out")
 
     # ---- device-resident timing ----
     sampler = ClockSampler(local)
@@ -297,43 +372,54 @@ def main():
     # ---- the same steps again with every main kernel bracketed by CUDA events on its launch
     #      stream (the library's timing hooks): per-kernel durations for the roofline ----
     b.timing_enable(True)
-    stack.kv_side_streams = False   # one stream: the event brackets of concurrent kernels would overlap
     barrier()
     for _ in range(args.steps):
         forward()
     barrier()
     timed = b.timing_collect()
     b.timing_enable(False)
-    stack.kv_side_streams = True
     clocks = sampler.stop() if rank == 0 else None
 
-    # ---- end to end: pinned host -> device, all layers, result back to the host ----
-    barrier()
-    e0.record()
-    for _ in range(args.steps):
-        x_dev.copy_(x_host, non_blocking=True)
-        if use_graph:
-            step()
-            out = stack.fabric.out if fused_tp else stack.outb
-        else:
-            out = forward()
-        y_host.copy_(out[: m * spec.hidden].view(m, spec.hidden), non_blocking=True)
-    e1.record()
-    barrier()
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=b.device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
+    # ---- end to end: pinned host -> device, all layers, result back to the host. The fused sharded
+    #      step reads only this rank's token rows and every rank ends with the whole output, so a rank
+    #      copies its own rows in and out (the job moves each byte once). ----
+    own = fused_tp and world > 1
+    rows = m // world if own else m
+    r0 = rank * rows if own else 0
+    x_src = x_host[r0:r0 + rows]
+    y_dst = y_host[r0:r0 + rows]
+    x_in = x_dev.view(-1)[r0 * spec.hidden:(r0 + rows) * spec.hidden]
+
+    def e2e_pass(with_step):
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            x_in.copy_(x_src.view(-1), non_blocking=True)
+            if with_step:
+                out = (step() or (stack.fabric.out if fused_tp else stack.outb)) if use_graph else forward()
+            else:
+                out = stack.fabric.out if fused_tp else stack.outb
+            y_dst.copy_(out.view(-1)[r0 * spec.hidden:(r0 + rows) * spec.hidden].view(rows, spec.hidden),
+                        non_blocking=True)
+        e1.record()
+        barrier()
+        tt = torch.tensor([e0.elapsed_time(e1) / args.steps], device=b.device)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    e2e_ms = e2e_pass(True)
+    copy_ms = e2e_pass(False)
 
     def shutdown():
         # A captured graph holds the communicator's kernels: drop it and drain the device before the
         # process group goes away, and never let teardown outlive the measurement by more than a
         # few seconds (a rank stuck here would keep the whole launcher alive).
-        nonlocal step
+        nonlocal step, graph
         if world > 1:
             threading.Timer(20.0, lambda: os._exit(0)).start()
             step = None
-            if use_graph:
+            if graph is not None:
                 graph.reset()
             torch.cuda.synchronize()
             dist.barrier()
@@ -353,39 +439,48 @@ def main():
         achieved = per_rank_flops * args.steps / (k_ms * 1e-3) / 1e12 if k_ms > 0 else 0.0
         roofline = {"bound": "tensor", "kernel": "gemm_kernel<mxf4nvf4> (tcgen05 block-scaled NVFP4)",
                     "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                    "peak_source": f"{peaks['source']} bf16 cuBLAS {peaks['bf16_tflops']} TFLOP/s x {FP4_OVER_BF16:g} "
-                                   "(no FP4 GEMM peak is measured on this pool; nominal dense FP4 : BF16 ratio)",
-                    "frac_of_nominal_fp4": achieved / NOMINAL_FP4_TFLOPS,
+                    "frac_is": "of 4 x measured bf16 cuBLAS burst",
+                    "peak_source": f"{peaks['source']} bf16 cuBLAS {peaks['bf16_tflops']} TFLOP/s x {FP4_OVER_BF16:g}: no "
+                                   "FP4 GEMM peak is measured on this pool, 4 is the nominal dense FP4 : BF16 ratio",
+                    "frac_of_nominal_fp4_9pf": achieved / NOMINAL_FP4_TFLOPS,
                     "launches": int(k_n), "avg_launch_us": 1e3 * k_ms / max(k_n, 1),
-                    # DRAM bytes of one [25600, 5120] M = 2048 launch from the committed ncu capture
-                    # (79.7 MB read + 71.8 MB written; algorithmic 79.6 MB + 104.9 MB of output)
-                    "traffic": 151.5e6, "traffic_of": "profiles/gemm_nvfp4_25600x5120_m2048.md",
+                    "traffic": STACK_GEMM_TRAFFIC_PER_LAUNCH if world == 1 else None,
+                    "traffic_of": STACK_GEMM_TRAFFIC_OF if world == 1 else
+                                  "no capture of the sharded step's launches (ncu runs on one GPU only)",
                     "act_quant_ms_per_step": timed["act_quant"][0] / args.steps}
     else:
         k_ms, k_n = timed["gemv"]
         achieved = per_rank_bytes * args.steps / (k_ms * 1e-3) / 1e9 if k_ms > 0 else 0.0
         roofline = {"bound": "hbm", "kernel": "gemv_nvfp4_tc_kernel (tcgen05 block-scaled decode)", "achieved": achieved,
                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                    "frac_is": "of measured copy bandwidth",
                     "peak_source": f"{peaks['source']} copy bandwidth",
-                    "frac_of_nominal_hbm": achieved / NOMINAL_HBM_GBS,
+                    "frac_of_nominal_hbm_8tbs": achieved / NOMINAL_HBM_GBS,
                     "launches": int(k_n), "avg_launch_us": 1e3 * k_ms / max(k_n, 1),
-                    # DRAM bytes of one [25600, 5120] M = 1 launch from the committed ncu capture
-                    "traffic": 75.9e6, "traffic_of": "profiles/gemv_nvfp4_tc_25600x5120_m1.md"}
+                    "traffic": None,
+                    "traffic_of": "single [25600, 5120] M = 1 launch: 75.9 MB per launch against 73.8 MB algorithmic "
+                                  "(profiles/gemv_nvfp4_tc_25600x5120_m1.md); the step's launches were not captured"}
 
+    cfg = workload_config(args, spec, m, args.tp if fused_tp else False)
+    if check is not None:
+        cfg["tp_check"] = check
     line = {
         "metric": METRIC, "value": m / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "nvfp4 x nvfp4 -> f32 accumulate (bf16 in/out)",
-        "data": "synthetic", "config": workload_config(args, spec, m, fused_tp),
+        "data": "synthetic", "config": cfg,
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+                "copy_only_ms_per_step": copy_ms,
+                "h2d_bytes_per_step": rows * spec.hidden * 2 * world, "d2h_bytes_per_step": rows * spec.hidden * 2 * world,
+                "copies": (f"each of the {world} ranks copies its own {rows} token rows in and out" if own
+                           else "the whole step input in, the whole output out")},
         "gpu_launches": int(launches), "cuda_graph": bool(use_graph), "clocks": clocks, "roofline": roofline,
         "tflops_per_gpu": per_rank_flops / (ms * 1e-3) / 1e12,
         "weights_gb_per_gpu": per_rank_bytes / 1e9,
     }
 
     if world == 1 and not args.no_components:
-        line["components"] = components(b, peaks)
+        roofline["components"] = components(b, peaks, stack, args)
     if world == 1 and not args.no_cpu_baseline:
         tok_s, cores, sample, _ = cpu_baseline_sample(spec, m)
         # the reference's own CPU backend is single-threaded: the same sample on one thread beside it
@@ -397,6 +492,13 @@ def main():
     print(json.dumps(line), flush=True)
     sys.stdout.flush()
     shutdown()
+
+
+# DRAM bytes per GEMM launch of the prefill step on one GPU, from an ncu capture of the step's own
+# launches (two layers of the same stack: the layers are identical, so the per-launch average is the
+# 64-layer step's); see the file named beside it.
+STACK_GEMM_TRAFFIC_PER_LAUNCH = None
+STACK_GEMM_TRAFFIC_OF = "profiles/stack_prefill_launch_list.md (no DRAM-byte capture of the step's launches yet)"
 
 
 def _time_replays(replay, launches_per_replay, gpu_index=0, warm_s=0.2, timed_s=0.3):
@@ -433,153 +535,242 @@ def _time_replays(replay, launches_per_replay, gpu_index=0, warm_s=0.2, timed_s=
     return e0.elapsed_time(e1) * 1e3 / (n * launches_per_replay), clocks
 
 
-def components(b, peaks, graph=True):
-    """Single NVFP4 linear [25600, 5120]: decode GEMV (M = 1, weight copies rotated so they never
-    sit in L2) and prefill GEMM (M = 2048), timed with CUDA events."""
+def _timed_cell(b, calls, graph=True, burst_only=False, rounds=None):
+    """`calls`: functions that each queue one unit of work on a rotated weight copy. They are run
+    back to back (a few rounds), captured as one CUDA graph so that host launch latency is not in
+    the measurement, and timed per unit. Returns (microseconds per unit, clock record)."""
     import torch
 
-    from velox_inferer_b200 import ActPolicy, WeightFormat, WeightView
-
-    n, k = 25600, 5120
-    copies = 6   # 6 x 73.7 MB > 3 x the 126 MB L2
-    views = []
-    gen = torch.Generator(device=b.device).manual_seed(0)
-    for _ in range(copies):
-        w = torch.randn(n, k, generator=gen, device=b.device) * 0.02
-        views.append(WeightView.full(b.encode_nvfp4(w), WeightFormat.NVFP4, n, k).with_act(ActPolicy.allow_a4(256.0)))
-        del w
-    out = {}
-    payload = WeightFormat.NVFP4.payload_bytes(n, k)
     stream = torch.cuda.Stream()
-    for m, twin in ((1, False), (1, True), (2048, False)):
-        xb = torch.randn(m, k, device=b.device).to(torch.bfloat16)
-        yb = torch.empty(m, n, dtype=torch.bfloat16, device=b.device)
-        rounds = 5 if m == 1 else 2
-        if twin:
-            # the FP4 activation twin a norm or a producing linear hands over: no quantiser launch
-            q4 = b.q4_blob(m, k)
-            b.add_rms_norm_q4(xb.float().reshape(-1).contiguous(), None, torch.ones(k, device=b.device), None, q4,
-                              m, k, 1e-6, 256.0)
-            call = lambda v: b.linear_q4(q4, 256.0, v, None, m, yb=yb)
-        else:
-            call = lambda v: b.linear_bf16(xb, v, None, m, yb=yb)
-        with torch.cuda.stream(stream):
-            for v in views:
-                call(v)
+    rounds = rounds or max(2, 24 // len(calls))
+    with torch.cuda.stream(stream):
+        for c in calls:
+            c()
+    torch.cuda.synchronize()
+
+    def burst():
+        for _ in range(rounds):
+            for c in calls:
+                c()
+    replay, g = burst, None
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            burst()
+        replay = g.replay
+    if burst_only:
+        replay()
         torch.cuda.synchronize()
-        # replayed as one CUDA graph so that host launch latency is not in the measurement
-        def burst():
-            for _ in range(rounds):
-                for v in views:
-                    call(v)
-        replay = burst
-        if graph:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                burst()
-            replay = g.replay
-        if m == 1:
-            us, clk = _time_replays(replay, rounds * copies, b.device.index or 0)
-        else:
-            # a burst: the kernel timed alone, against the burst peak; the sustained figure follows
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(3):
             replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(3):
-                replay()
-            e1.record()
-            torch.cuda.synchronize()
-            us, clk = e0.elapsed_time(e1) * 1e3 / (3 * rounds * copies), None
-        if m == 1:
-            byts = payload + 2 * m * k + 2 * m * n
-            gbs = byts / (us * 1e-6) / 1e9
-            out["decode_gemv_m1_fp4_twin_in" if twin else "decode_gemv_m1"] = {
-                "us_per_launch": us, "GB/s": gbs, "bytes": byts,
-                "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                "frac_of_nominal_8TBs": gbs / NOMINAL_HBM_GBS, "clocks": clk,
-                "timing": "CUDA-graph replay of 30 launches over 6 rotated weight copies, 0.2 s of the same work first"
-                          + ("; input is the NVFP4 blob a producer wrote" if twin
-                             else "; bf16 input, includes the activation quantiser launch")}
-        else:
-            tf = 2.0 * m * n * k / (us * 1e-6) / 1e12
-            out["prefill_gemm_m2048"] = {"us_per_launch": us, "TFLOP/s": tf,
-                                         "frac_of_measured_bf16_x4": tf / (peaks["bf16_tflops"] * FP4_OVER_BF16),
-                                         "frac_of_nominal_fp4": tf / NOMINAL_FP4_TFLOPS,
-                                         "timing": "CUDA-graph replay, a burst of 36 launches; includes the activation "
-                                                   "quantiser launch"}
-            us_s, clk_s = _time_replays(replay, rounds * copies, b.device.index or 0)
-            tf_s = 2.0 * m * n * k / (us_s * 1e-6) / 1e12
-            out["prefill_gemm_m2048_sustained"] = {
-                "us_per_launch": us_s, "TFLOP/s": tf_s,
-                "frac_of_measured_bf16_sustained_x4": tf_s / (peaks["bf16_tflops_sustained"] * FP4_OVER_BF16),
-                "frac_of_nominal_fp4": tf_s / NOMINAL_FP4_TFLOPS, "clocks": clk_s,
-                "timing": "the same graph replayed for 0.2 s, then timed for 0.3 s: under the power cap"}
-    del views
-    out.update(_decode_other_formats(b, peaks, graph))
-    return out
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (3 * rounds * len(calls)), None
+    return _time_replays(replay, rounds * len(calls), b.device.index or 0)
 
 
-def _decode_other_formats(b, peaks, graph=True):
-    """The same [25600, 5120] projection stored as FP8-E4M3 rows and as GGML Q4_K: decode launches at
-    1 and 8 tokens with bf16 activations (the rounding every policy admits), seeded synthetic bytes
-    (finite codes, sane scales), weight copies rotated so that they never sit in L2."""
+def _mhz(clk):
+    return None if not clk else clk.get("sm_mhz")
+
+
+def _hbm_cell(us, byts, peaks, clk, **extra):
+    gbs = byts / (us * 1e-6) / 1e9
+    d = {"us": round(us, 2), "GB/s": round(gbs, 1), "frac_measured_hbm": round(gbs / peaks["hbm_gbs"], 3),
+         "frac_nominal_8tbs": round(gbs / NOMINAL_HBM_GBS, 3), "sm_mhz": _mhz(clk)}
+    d.update(extra)
+    return d
+
+
+def _tensor_cell(us, flops, peaks, clk, fp4=True, sustained=False, **extra):
+    tf = flops / (us * 1e-6) / 1e12
+    base = peaks["bf16_tflops_sustained" if sustained else "bf16_tflops"]
+    d = {"us": round(us, 2), "TFLOP/s": round(tf, 1)}
+    if fp4:
+        d["frac_4x_measured_bf16" + ("_sustained" if sustained else "")] = round(tf / (base * FP4_OVER_BF16), 3)
+        d["frac_nominal_fp4_9pf"] = round(tf / NOMINAL_FP4_TFLOPS, 3)
+    else:
+        d["frac_measured_bf16" + ("_sustained" if sustained else "")] = round(tf / base, 3)
+    d["sm_mhz"] = _mhz(clk)
+    d.update(extra)
+    return d
+
+
+def _kernel_class(b, call):
+    """Which kernel family served a call: runs it once with the library's timing hooks on."""
+    import torch
+
+    torch.cuda.synchronize()
+    b.timing_collect()
+    b.timing_enable(True)
+    call()
+    t = b.timing_collect()
+    b.timing_enable(False)
+    names = [k for k in ("gemv", "gemm_nvfp4", "gemm_fp8", "gemm_bf16") if t[k][1] > 0]
+    return "+".join(names) or "other"
+
+
+def components(b, peaks, stack, args, graph=True):
+    """The rest of the headline metric, one GPU: single-linear decode GEMV and prefill GEMM on
+    [25600, 5120] (BASELINE configs 0 and 1, with the M sweep), the SwiGLU MLP (config 2), FP8 rows and
+    Q4_K on [14336, 4096] (config 3), and the decode stack (config 4 at M = 1). Weight copies are
+    rotated so that no launch finds its weights in L2; every cell is a CUDA-graph replay timed with
+    CUDA events after 0.2 s of the same work, with the SM clock seen meanwhile."""
     import torch
 
     from velox_inferer_b200 import ActPolicy, WeightFormat, WeightView
 
-    n, k = 25600, 5120
-    out = {}
-    gen = torch.Generator(device=b.device).manual_seed(1)
-    stream = torch.cuda.Stream()
-    for name, fmt, policies in (("fp8", WeightFormat.FP8_ROW_BF16, (("a16", ActPolicy.a16_only()), ("a8", ActPolicy.allow_a8()))),
-                                ("q4k", WeightFormat.GGML_Q4_K, (("a16", ActPolicy.a16_only()),))):
-        payload = fmt.payload_bytes(n, k)
-        copies = 4 if name == "fp8" else 6   # > 3 x the 126 MB L2 either way
-        bufs = []
-        for _ in range(copies):
-            buf = torch.randint(0, 120, (payload + 256,), generator=gen, dtype=torch.uint8, device=b.device)
-            if name == "fp8":
-                off = (n * k + 255) // 256 * 256
-                buf[off:off + 2 * n].view(torch.bfloat16).fill_(0.01)      # bf16 row scales
-            else:
-                blocks = buf[:payload].view(-1, 144)
-                blocks[:, 1] = 0x20                                        # f16 d and dmin: small, finite
-                blocks[:, 3] = 0x20
-            bufs.append(buf)
-        for pname, policy in policies:
-            views = [WeightView.full(buf, fmt, n, k).with_act(policy) for buf in bufs]
-            for m in (1, 8):
-                xb = torch.randn(m, k, device=b.device).to(torch.bfloat16)
-                yb = torch.empty(m, n, dtype=torch.bfloat16, device=b.device)
-                call = lambda v: b.linear_bf16(xb, v, None, m, yb=yb)
-                rounds = 4
-                with torch.cuda.stream(stream):
-                    for v in views:
-                        call(v)
-                torch.cuda.synchronize()
+    want = set((args.components if args else "all").split(","))
+    on = lambda name: "all" in want or name in want
+    NV, F8, Q4 = WeightFormat.NVFP4, WeightFormat.FP8_ROW_BF16, WeightFormat.GGML_Q4_K
+    dev = b.device
+    out = {"timing": "CUDA-graph replay over rotated weight copies (> 3 x L2 in total), 0.2 s of the same work first, "
+                     "CUDA events; us is per linear (per MLP / per token where said)"}
+    gen = torch.Generator(device=dev).manual_seed(0)
 
-                def burst():
-                    for _ in range(rounds):
-                        for v in views:
-                            call(v)
-                replay, g = burst, None
-                if graph:
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=stream):
-                        burst()
-                    replay = g.replay
-                us, clk = _time_replays(replay, rounds * copies, b.device.index or 0)
-                byts = payload + 2 * m * k + 2 * m * n
-                gbs = byts / (us * 1e-6) / 1e9
-                act = b.linear_act(views[0], m)
-                out[f"decode_gemv_{name}_{pname}_m{m}"] = {
-                    "us_per_launch": us, "GB/s": gbs, "bytes": byts, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
-                    "activation_rounding": str(act), "clocks": clk,
-                    "timing": f"CUDA-graph replay of {rounds * copies} launches over {copies} rotated weight copies, "
-                              "0.2 s of the same work first"}
-                del g
-        del bufs
+    def nvfp4_views(n, k, copies, div):
+        vs = []
+        for _ in range(copies):
+            w = torch.randn(n, k, generator=gen, device=dev) * 0.02
+            vs.append(WeightView.full(b.encode_nvfp4(w), NV, n, k).with_act(ActPolicy.allow_a4(div)))
+            del w
+        return vs
+
+    def blob_of(m, k, div):
+        q4 = b.q4_blob(m, k)
+        x = torch.randn(m, k, generator=gen, device=dev)
+        b.add_rms_norm_q4(x.reshape(-1).contiguous(), None, torch.ones(k, device=dev), None, q4, m, k, 1e-6, div)
+        return q4
+
+    if on("nvfp4") or on("sweep"):
+        n, k = 25600, 5120
+        views = nvfp4_views(n, k, 6, 256.0)   # 6 x 73.7 MB
+        payload = NV.payload_bytes(n, k)
+        byts = lambda m: payload + 2 * m * k + 2 * m * n
+        flops = lambda m: 2.0 * m * n * k
+        if on("nvfp4"):
+            c0 = {}
+            m = 1
+            xb = torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16)
+            yb = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            q4 = blob_of(m, k, 256.0)
+            us, clk = _timed_cell(b, [lambda v=v: b.linear_q4(q4, 256.0, v, None, m, yb=yb) for v in views], graph)
+            c0["fp4_blob_in"] = _hbm_cell(us, byts(m), peaks, clk, note="activations arrive as the NVFP4 blob a producer wrote")
+            us, clk = _timed_cell(b, [lambda v=v: b.linear_bf16(xb, v, None, m, yb=yb) for v in views], graph)
+            c0["bf16_in"] = _hbm_cell(us, byts(m), peaks, clk, note="bf16 x in, NVFP4 rounding (AllowA4): quantiser launch included")
+            a16 = [v.with_act(ActPolicy.a16_only()) for v in views]
+            us, clk = _timed_cell(b, [lambda v=v: b.linear_bf16(xb, v, None, m, yb=yb) for v in a16], graph)
+            c0["bf16_in_a16only"] = _hbm_cell(us, byts(m), peaks, clk, note="bf16 activations kept (A16Only view): unpacking GEMV")
+            out["config0_decode_gemv_nvfp4_25600x5120_m1"] = c0
+            m = 2048
+            xb = torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16)
+            yb = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+            calls = [lambda v=v: b.linear_bf16(xb, v, None, m, yb=yb) for v in views]
+            us, _ = _timed_cell(b, calls, graph, burst_only=True)
+            us_s, clk = _timed_cell(b, calls, graph)
+            out["config1_prefill_gemm_nvfp4_25600x5120_m2048"] = {
+                "burst": _tensor_cell(us, flops(m), peaks, None, note="bf16 x in: quantiser launch included; a burst of launches"),
+                "sustained": _tensor_cell(us_s, flops(m), peaks, clk, sustained=True, note="0.5 s under the power cap")}
+            del xb, yb
+        if on("sweep"):
+            sweep = {}
+            for m in (1, 4, 16, 64, 256, 2048):
+                xb = torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16)
+                yb = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+                q4 = blob_of(m, k, 256.0)
+                kern = _kernel_class(b, lambda: b.linear_q4(q4, 256.0, views[0], None, m, yb=yb))
+                us, clk = _timed_cell(b, [lambda v=v: b.linear_q4(q4, 256.0, v, None, m, yb=yb) for v in views], graph)
+                cell = _hbm_cell(us, byts(m), peaks, clk, kernel=kern)
+                cell["TFLOP/s"] = round(flops(m) / (us * 1e-6) / 1e12, 1)
+                sweep[f"m{m}"] = cell
+                del xb, yb
+            sweep["crossover"] = ("the dispatcher streams (decode kernel, weight rows as MMA M) up to 16 tokens and for "
+                                  "17-64 tokens where its cost model expects few GEMM tiles with a long K; otherwise the "
+                                  "GEMM (tokens as MMA M): 'kernel' says which ran")
+            out["config1_m_sweep_fp4_blob_in"] = sweep
+        del views
+        torch.cuda.empty_cache()
+
+    if on("mlp"):
+        w, k = 25600, 5120
+        mlps = []
+        for _ in range(2):   # 2 x 221 MB
+            gu = torch.randn(2 * w, k, generator=gen, device=dev) * 0.02
+            parent = WeightView.full(b.encode_nvfp4(gu), NV, 2 * w, k).with_act(ActPolicy.allow_a4(256.0))
+            del gu
+            dn = torch.randn(k, w, generator=gen, device=dev) * 0.02
+            down = WeightView.full(b.encode_nvfp4(dn), NV, k, w).with_act(ActPolicy.allow_a4(16.0))
+            del dn
+            mlps.append((parent.rows_view(0, w), parent.rows_view(w, w), down))
+        mlp_bytes = NV.payload_bytes(2 * w, k) + NV.payload_bytes(k, w)
+        cells = {}
+        for m in (1, 16, 2048):
+            q4 = blob_of(m, k, 256.0)
+            hq = b.q4_blob(m, w)
+            yb = torch.empty(m, k, dtype=torch.bfloat16, device=dev)
+
+            def mlp(g, u, d):
+                b.linear_swiglu_q4_to_q4(q4, 256.0, g, u, m, hq, 16.0)
+                b.linear_q4(hq, 16.0, d, None, m, yb=yb)
+            us, clk = _timed_cell(b, [lambda t=t: mlp(*t) for t in mlps], graph)
+            if m <= 16:
+                cells[f"m{m}"] = _hbm_cell(us, mlp_bytes + 2 * m * k * 2, peaks, clk, unit="per MLP (2 launches)")
+            else:
+                cells[f"m{m}"] = _tensor_cell(us, 6.0 * m * w * k, peaks, clk, sustained=True, unit="per MLP (2 launches)")
+        cells["form"] = ("norm-written NVFP4 blob -> fused gate|up SwiGLU whose epilogue emits down's NVFP4 input -> down "
+                         "(bf16 out); gate|up one [51200, 5120] parent")
+        out["config2_mlp_nvfp4"] = cells
+        del mlps
+        torch.cuda.empty_cache()
+
+    if on("formats"):
+        n, k = 14336, 4096
+        fm = {}
+        for name, fmt, copies, policies in (("fp8_rows", F8, 7, (("a16", ActPolicy.a16_only()), ("a8", ActPolicy.allow_a8()))),
+                                            ("q4_k", Q4, 12, (("a16", ActPolicy.a16_only()),))):
+            payload = fmt.payload_bytes(n, k)
+            bufs = []
+            for _ in range(copies):   # > 3 x L2 in total
+                buf = torch.randint(0, 120, (payload + 256,), generator=gen, dtype=torch.uint8, device=dev)
+                if fmt is F8:
+                    off = (n * k + 255) // 256 * 256
+                    buf[off:off + 2 * n].view(torch.bfloat16).fill_(0.01)      # bf16 row scales
+                else:
+                    blocks = buf[:payload].view(-1, 144)
+                    blocks[:, 1] = 0x20                                        # f16 d and dmin: small, finite
+                    blocks[:, 3] = 0x20
+                bufs.append(buf)
+            for pname, policy in policies:
+                views = [WeightView.full(buf, fmt, n, k).with_act(policy) for buf in bufs]
+                for m in (1, 8, 512):
+                    xb = torch.randn(m, k, generator=gen, device=dev).to(torch.bfloat16)
+                    yb = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+                    kern = _kernel_class(b, lambda: b.linear_bf16(xb, views[0], None, m, yb=yb))
+                    us, clk = _timed_cell(b, [lambda v=v: b.linear_bf16(xb, v, None, m, yb=yb) for v in views], graph)
+                    cell = _hbm_cell(us, payload + 2 * m * k + 2 * m * n, peaks, clk, kernel=kern,
+                                     act=str(b.linear_act(views[0], m)))
+                    if m > 16:
+                        cell["TFLOP/s"] = round(2.0 * m * n * k / (us * 1e-6) / 1e12, 1)
+                    fm[f"{name}_{pname}_m{m}"] = cell
+                    del xb, yb
+            del bufs
+        fm["data"] = "seeded random stored bytes with finite codes and sane scales; bf16 x in (quantiser launches included)"
+        out["config3_14336x4096"] = fm
+        torch.cuda.empty_cache()
+
+    if on("decode_stack") and stack is not None:
+        spec = stack.spec
+        x1 = torch.randn(1, spec.hidden, generator=gen, device=dev).to(torch.bfloat16)
+        fwd = lambda: stack.forward(x1, 1)
+        for _ in range(2):
+            fwd()
+        us, clk = _timed_cell(b, [fwd], graph, rounds=2)          # us per step = per token
+        cell = _hbm_cell(us, stack.weight_bytes, peaks, clk)
+        cell["tok/s"] = round(1e6 / us, 1)
+        cell["ms_per_token"] = round(us / 1e3, 3)
+        cell["launches_per_token"] = int(stack.launches_per_step)
+        out["config4_decode_stack_m1"] = cell
     return out
 
 

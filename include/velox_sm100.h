@@ -22,6 +22,15 @@
  * velox_sm100_set_stream. Launchers do not synchronise, read back or allocate, except for
  * grow-only private scratch on first use of a larger size (the reference's VeloxScratch rule,
  * velox_common.cuh:49-70).
+ *
+ * One stream per device at a time. The scratch is one set of pools per device, shared by every
+ * call: quantised activations, dequantised bf16 weights, the f32 partial sums and arrival counters
+ * of the K-split decode kernels, the words that elect a launch's last CTA. Two calls whose kernels
+ * can run at the same time on one device (different streams, or different threads with their
+ * per-thread streams) would overwrite each other's scratch and give wrong results without any
+ * error. Keep all calls on a device stream-ordered, as the reference's engine does (its scratch
+ * carries the same rule: "engine work is serialized", velox_common.cuh:49-70). The entry points
+ * that take pre-quantised activations (the _q4 family) at prefill width use no scratch.
  */
 #ifndef VELOX_SM100_H
 #define VELOX_SM100_H
@@ -80,9 +89,14 @@ typedef struct velox_sm100_part {
 int velox_sm100_abi_version(void);
 
 /* Debug aid with no counterpart in the reference: synchronises the device and returns the status
- * word of the tensor-core kernels: 0, or the code of the first bounded mbarrier wait that gave up
- * (the kernel then stopped early and its output is incomplete). Never call it on a hot path. */
+ * word of the kernels that wait on something: 0, or the code of the first bounded wait that gave up
+ * (1-5: an mbarrier inside a tensor-core kernel; 6: a peer's flag in a tensor-parallel step). The
+ * kernel then went on without what it waited for and its output is meaningless. The word is sticky
+ * until velox_sm100_debug_status_reset. Never call either on a hot path. */
 int velox_sm100_debug_status(void);
+/* Synchronises the device, then clears the status words and the per-device counters a kernel that
+ * gave up may have left non-zero (arrival tickets of the K-split fix-up, last-CTA tickets). */
+int velox_sm100_debug_status_reset(void);
 
 /* Kernel launches issued through this library since it was loaded (host counter). No counterpart
  * in the reference; the benchmark reports it. */
@@ -234,9 +248,11 @@ int velox_sm100_linear_swiglu_q4_to_q4(const uint8_t* codes, const uint8_t* atom
                                        float out_divisor);
 
 /* Several views of one width reading the same FP4 activations, each with its own destination: the
- * q4 form of Backend::linears (backend.rs:1001-1048). yb may be NULL when out_codes is given (the
- * result then exists only as the next linear's FP4 input). At decode sizes up to three views run
- * as one launch; otherwise one launch per view. */
+ * q4 form of Backend::linears (backend.rs:938-958, 1001-1048). yb may be NULL when out_codes is
+ * given (the result then exists only as the next linear's FP4 input). Up to three views run as one
+ * launch, at decode sizes on the streaming kernel and at prefill sizes on the GEMM (one persistent
+ * grid walks the tiles of all views); more views, or views the kernels group differently, run as
+ * one launch each. */
 typedef struct {
     velox_sm100_view view;
     uint16_t* yb;          /* [m, view.rows] bf16, or NULL */
@@ -250,26 +266,71 @@ int velox_sm100_linears_q4(const uint8_t* codes, const uint8_t* atoms, float div
 /* Tensor parallelism over one node (no counterpart in the reference, which is single-device).
  * Token rows are owned by ranks in equal blocks of `rows_per_owner` (a multiple of 128). Buffers
  * named "_ptrs" are arrays, one entry per rank, of device addresses valid on the calling GPU
- * (peer mappings of symmetric allocations); the caller orders the phases with its own barriers.
+ * (peer mappings of symmetric allocations).
+ *
+ * Ordering between ranks needs no barrier kernels: a kernel whose output other ranks read raises a
+ * flag on every rank when its last CTA is done, and a kernel that reads such data polls its own
+ * rank's flags before its first read. velox_sm100_tp_sync describes both for one launch:
+ *   flag_tables[r]   rank r's flag table as mapped on this GPU (entry [rank] is this rank's own):
+ *                    `phases` rows of 8 32-bit words, zero when allocated, never reset;
+ *   epoch            device address of this rank's 32-bit step counter; velox_sm100_tp_step_begin
+ *                    adds one at the start of every step (every rank runs the same steps);
+ *   wait_phase       row to wait on: the launch starts reading once flag_tables[rank][row][src] has
+ *                    reached the epoch for every src < n; -1: no wait;
+ *   signal_phase     row to raise: when the launch's stores are complete the epoch is written to
+ *                    flag_tables[d][row][rank] for every d < n; -1: no signal.
+ * A wait gives up after a wall-clock limit (2 s; velox_sm100_tp_set_wait_limit_ms), records code 6
+ * in the status word (velox_sm100_debug_status) and the kernel runs on and exits normally: a rank
+ * that never arrives costs the others a bounded delay and a reported error, not a hang.
+ * All launches of a step must be issued on one stream per rank.
+ *
  *  - velox_sm100_tp_make_maps: output maps for a row-split linear. slot_ptrs[o] is this rank's
  *    [rows_per_owner, cols] bf16 slot in rank o's memory; maps_dev receives n x 128 bytes.
+ *  - velox_sm100_tp_linears_q4 / _tp_linear_swiglu_q4_to_q4: velox_sm100_linears_q4 /
+ *    velox_sm100_linear_swiglu_q4_to_q4 at prefill width (m > 16) that wait for `sync` before
+ *    reading the activation blob (every rank's norm has written its rows).
  *  - velox_sm100_tp_linear_q4_scatter: linear_q4 whose bf16 result tiles are stored by the GEMM
  *    epilogue straight into the owners' slots (the reduce-scatter's data movement, fused into the
- *    linear). The view must be a whole parent with a multiple of 256 rows, m a multiple of
- *    rows_per_owner, m > 16.
- *  - velox_sm100_tp_norm_q4: acc (this rank's rows, f32) += the nslots slots in order; rms norm;
- *    the result as NVFP4 codes and scale atoms at rows row0.. of every rank's blob (the
- *    all-gather, fused into the norm). nslots = 0: no addend.
- *  - velox_sm100_tp_finish: acc += the slots; acc as bf16 at rows row0.. of every rank's output. */
+ *    linear), then signals. The view must be a whole parent with a multiple of 256 rows, m a
+ *    multiple of rows_per_owner, m > 16.
+ *  - velox_sm100_tp_norm_q4: waits; acc (this rank's rows, f32) += the nslots slots in order; rms
+ *    norm; the result as NVFP4 codes and scale atoms at rows row0.. of every rank's blob (the
+ *    all-gather, fused into the norm); signals. nslots = 0: no addend.
+ *  - velox_sm100_tp_finish: waits; acc += the slots; acc as bf16 at rows row0.. of every rank's
+ *    output; signals.
+ *  - velox_sm100_tp_wait: a one-thread kernel that only waits (the end of a step: every rank's
+ *    output rows are in place).
+ *  - velox_sm100_tp_signal: a one-thread kernel that only signals (tests).
+ * `sync` may be NULL everywhere except tp_wait / tp_signal (single rank, or the caller orders the
+ * ranks itself). */
+typedef struct velox_sm100_tp_sync {
+    unsigned long long flag_tables[8];
+    unsigned long long epoch;
+    int32_t n, rank;
+    int32_t wait_phase, signal_phase;
+} velox_sm100_tp_sync;
+int velox_sm100_tp_step_begin(unsigned int* epoch);
+int velox_sm100_tp_wait(const velox_sm100_tp_sync* sync);
+int velox_sm100_tp_signal(const velox_sm100_tp_sync* sync);
+int velox_sm100_tp_set_wait_limit_ms(int ms);
 int velox_sm100_tp_make_maps(void* maps_dev, const unsigned long long* slot_ptrs, int n, int rows_per_owner,
                              long long cols);
+int velox_sm100_tp_linears_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                              const velox_sm100_part_q4* parts, int nparts, int m, const velox_sm100_tp_sync* sync);
+int velox_sm100_tp_linear_swiglu_q4_to_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                                          const velox_sm100_view* gate, const velox_sm100_view* up, int m,
+                                          uint16_t* outb, uint8_t* out_codes, uint8_t* out_atoms, float out_divisor,
+                                          const velox_sm100_tp_sync* sync);
 int velox_sm100_tp_linear_q4_scatter(const uint8_t* codes, const uint8_t* atoms, float divisor,
-                                     const velox_sm100_view* view, int m, const void* maps_dev, int rows_per_owner);
+                                     const velox_sm100_view* view, int m, const void* maps_dev, int rows_per_owner,
+                                     const velox_sm100_tp_sync* sync);
 int velox_sm100_tp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
                            const unsigned long long* codes_ptrs, const unsigned long long* atoms_ptrs, int ndst,
-                           long long row0, int rows, int dim, float eps, int offset, float divisor);
+                           long long row0, int rows, int dim, float eps, int offset, float divisor,
+                           const velox_sm100_tp_sync* sync);
 int velox_sm100_tp_finish(float* acc, const uint16_t* slots, int nslots, long long slot_stride,
-                          const unsigned long long* out_ptrs, int ndst, long long row0, int rows, int dim);
+                          const unsigned long long* out_ptrs, int ndst, long long row0, int rows, int dim,
+                          const velox_sm100_tp_sync* sync);
 
 /* The same with a bf16 addend (the all-reduced partial sums of a row-split projection): acc += xb,
  * then the norm. No counterpart in the reference, which has no tensor parallelism. */

@@ -25,3 +25,18 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+# Lines a test wants shown after the run (measured distances that are reported, not asserted).
+_REPORT = []
+
+
+def report_line(text: str) -> None:
+    _REPORT.append(text)
+
+
+def pytest_terminal_summary(terminalreporter):
+    if _REPORT:
+        terminalreporter.section("reported by the tests")
+        for line in _REPORT:
+            terminalreporter.write_line(line)

@@ -337,9 +337,10 @@ def test_linears_emit_the_next_linears_nvfp4_input(b, n, k, m):
     _assert_atoms_equal(oq[1], want_atoms, m, half)
 
 
-@pytest.mark.parametrize("m", [1, 8, 40])
+@pytest.mark.parametrize("m", [1, 8, 40, 130, 300, 513])
 def test_linears_q4_equals_separate_calls(b, m):
-    """q, k and v of one input through linears_q4 (one launch at decode sizes) give the bits the
+    """q, k and v of one input through linears_q4 (one launch: the streaming kernel at decode
+    sizes, one persistent GEMM grid over all three views' tiles at prefill sizes) give the bits the
     per-view entry points give, including the FP4 hand-over of the first view."""
     r = O.Rng(53)
     k = 1024
@@ -365,3 +366,32 @@ def test_linears_q4_equals_separate_calls(b, m):
         assert torch.equal(g, w)
     assert torch.equal(oq[0], oq_ref[0])
     _assert_atoms_equal(oq[1], oq_ref[1], m, shapes[0])
+
+
+@pytest.mark.parametrize("m", [33, 257])
+def test_grouped_prefill_linears_on_ragged_views(b, m):
+    """The grouped GEMM launch with views that start inside a 128-row scale tile, have ragged row
+    counts and different parents: each part equals its own single launch bit for bit and matches
+    the oracle. Reference: Backend::linears, crates/velox-core/src/backend.rs:938-958."""
+    r = O.Rng(59)
+    k = 640
+    specs = ((640, 128, 384), (256, 7, 100), (384, 130, 250))      # (parent rows, row_begin, rows)
+    payloads = [r.random_weight(FMT_O[NV], n, k) for n, _, _ in specs]
+    views = [make_view(b, p, NV, n, k, r0, rows, ActPolicy.allow_a4(256.0)) for p, (n, r0, rows) in zip(payloads, specs)]
+    acc = b.upload(r.vec(m * k, 1.0))
+    hb = torch.zeros(m * k, dtype=torch.bfloat16, device=acc.device)
+    q4 = b.q4_blob(m, k)
+    b.add_rms_norm_q4(acc, None, b.upload(np.ones(k, np.float32)), hb, q4, m, k, 1e-6, 256.0)
+    want = []
+    for v in views:
+        yb = torch.zeros(m * v.rows, dtype=torch.bfloat16, device=acc.device)
+        b.linear_q4(q4, 256.0, v, None, m, yb=yb)
+        want.append(yb)
+    got = [torch.zeros_like(w) for w in want]
+    b.linears_q4(q4, 256.0, [(v, g, None, 0.0) for v, g in zip(views, got)], m)
+    assert b.lib.velox_sm100_debug_status() == 0
+    for g, w, v, p, (n, r0, rows) in zip(got, want, views, payloads, specs):
+        assert torch.equal(g, w)
+        ref = oracle_linear(hb.float().cpu().numpy(), p, NV, n, k, r0, rows, m, ActQuant(ActQuant.NVFP4, 256.0))
+        e_conf, e_rms = both_metrics(g.float().cpu().numpy().reshape(m, rows), ref)
+        assert e_rms <= RMS_TOL and e_conf <= 2.0 ** -8, (e_conf, e_rms)   # bf16 output: half an ulp of bf16

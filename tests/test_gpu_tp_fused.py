@@ -1,4 +1,5 @@
-"""Two-GPU check of the fused tensor-parallel step (needs two visible GPUs; skipped otherwise)."""
+"""Multi-GPU checks of the fused tensor-parallel step (two GPUs, and four where the box has them;
+skipped on fewer). Ranks run as child processes with NVLS off."""
 import os
 import subprocess
 import sys
@@ -9,12 +10,18 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_fused_tp_step_matches_all_reduce_step():
+def _gpus() -> int:
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_fused_tp_step_is_exact_and_matches_the_all_reduce_step(world):
+    if _gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
     here = os.path.dirname(os.path.abspath(__file__))
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-           "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(here, "tp_fused_worker.py")]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(world),
+           "--master-addr", "127.0.0.1", "--master-port", str(29533 + world), os.path.join(here, "tp_fused_worker.py")]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    out = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
-    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "TP_FUSED_OK" in out.stdout

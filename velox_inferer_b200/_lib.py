@@ -38,6 +38,12 @@ class PartQ4(C.Structure):
                 ("out_divisor", C.c_float)]
 
 
+class TpSync(C.Structure):
+    """``velox_sm100_tp_sync``: the flags one launch of a tensor-parallel step waits for and raises."""
+    _fields_ = [("flag_tables", C.c_uint64 * 8), ("epoch", C.c_uint64), ("n", C.c_int32), ("rank", C.c_int32),
+                ("wait_phase", C.c_int32), ("signal_phase", C.c_int32)]
+
+
 class Part(C.Structure):
     """``velox_sm100_part`` (include/velox_sm100.h)."""
 
@@ -51,6 +57,13 @@ SIGNATURES = {
     "velox_sm100_abi_version": (_I, []),
     "velox_sm100_set_stream": (_I, [_VP]),
     "velox_sm100_debug_status": (_I, []),
+    "velox_sm100_debug_status_reset": (_I, []),
+    "velox_sm100_tp_step_begin": (_I, [_VP]),
+    "velox_sm100_tp_wait": (_I, [_VP]),
+    "velox_sm100_tp_signal": (_I, [_VP]),
+    "velox_sm100_tp_set_wait_limit_ms": (_I, [_I]),
+    "velox_sm100_tp_linears_q4": (_I, [_VP, _VP, _F, _VP, _I, _I, _VP]),
+    "velox_sm100_tp_linear_swiglu_q4_to_q4": (_I, [_VP, _VP, _F, _PV, _PV, _I, _VP, _VP, _VP, _F, _VP]),
     "velox_sm100_launch_count": (C.c_longlong, []),
     "velox_sm100_timing_enable": (_I, [_I]),
     "velox_sm100_timing_collect": (_I, [_VP, _VP, _I]),
@@ -61,9 +74,9 @@ SIGNATURES = {
     "velox_sm100_linear_swiglu_q4": (_I, [_VP, _VP, _F, _PV, _PV, _I, _VP, _VP]),
     "velox_sm100_linears_q4": (_I, [_VP, _VP, _F, _VP, _I, _I]),
     "velox_sm100_tp_make_maps": (_I, [_VP, _VP, _I, _I, _LL]),
-    "velox_sm100_tp_linear_q4_scatter": (_I, [_VP, _VP, _F, _PV, _I, _VP, _I]),
-    "velox_sm100_tp_norm_q4": (_I, [_VP, _VP, _I, _LL, _VP, _VP, _VP, _I, _LL, _I, _I, _F, _I, _F]),
-    "velox_sm100_tp_finish": (_I, [_VP, _VP, _I, _LL, _VP, _I, _LL, _I, _I]),
+    "velox_sm100_tp_linear_q4_scatter": (_I, [_VP, _VP, _F, _PV, _I, _VP, _I, _VP]),
+    "velox_sm100_tp_norm_q4": (_I, [_VP, _VP, _I, _LL, _VP, _VP, _VP, _I, _LL, _I, _I, _F, _I, _F, _VP]),
+    "velox_sm100_tp_finish": (_I, [_VP, _VP, _I, _LL, _VP, _I, _LL, _I, _I, _VP]),
     "velox_sm100_linear_q4_to_q4": (_I, [_VP, _VP, _F, _PV, _I, _VP, _VP, _VP, _F]),
     "velox_sm100_linear_swiglu_q4_to_q4": (_I, [_VP, _VP, _F, _PV, _PV, _I, _VP, _VP, _VP, _F]),
     "velox_sm100_linear_act": (_I, [_PV, _I, C.POINTER(C.c_float)]),

@@ -282,43 +282,88 @@ class Sm100Backend:
             q4[0].data_ptr(), q4[1].data_ptr(), divisor, C.byref(_view_struct(gate)), C.byref(_view_struct(up)), m,
             _ptr(outb), out_q4[0].data_ptr(), out_q4[1].data_ptr(), out_divisor), "sm100 linear_swiglu_q4_to_q4")
 
-    def linears_q4(self, q4, divisor: float, parts, m: int) -> None:
-        """parts: (view, yb or None, out_q4 or None, out_divisor) per projection of the same input."""
-        self._bind()
+    @staticmethod
+    def _parts_q4(parts):
         arr = (_lib.PartQ4 * len(parts))()
         for i, (w, yb, oq, od) in enumerate(parts):
             arr[i] = _lib.PartQ4(_view_struct(w), _ptr(yb), None if oq is None else oq[0].data_ptr(),
                                  None if oq is None else oq[1].data_ptr(), od)
+        return arr
+
+    def linears_q4(self, q4, divisor: float, parts, m: int) -> None:
+        """parts: (view, yb or None, out_q4 or None, out_divisor) per projection of the same input."""
+        self._bind()
+        arr = self._parts_q4(parts)
         status(self.lib.velox_sm100_linears_q4(q4[0].data_ptr(), q4[1].data_ptr(), divisor, arr, len(parts), m),
                "sm100 linears_q4")
 
-    # -- tensor parallelism: reduce-scatter fused into the row-split linear, all-gather into the norm
+    # -- tensor parallelism: reduce-scatter fused into the row-split linear, all-gather into the norm;
+    #    `sync` (a _lib.TpSync or None) names the peers' flags a launch waits for and raises
+    @staticmethod
+    def _sync(sync):
+        return None if sync is None else C.byref(sync)
+
     def tp_make_maps(self, maps_dev: torch.Tensor, slot_ptrs, rows_per_owner: int, cols: int) -> None:
         self._bind()
         arr = (C.c_uint64 * len(slot_ptrs))(*slot_ptrs)
         status(self.lib.velox_sm100_tp_make_maps(maps_dev.data_ptr(), arr, len(slot_ptrs), rows_per_owner, cols),
                "sm100 tp_make_maps")
 
+    def tp_step_begin(self, epoch: torch.Tensor) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_tp_step_begin(epoch.data_ptr()), "sm100 tp_step_begin")
+
+    def tp_wait(self, sync) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_tp_wait(C.byref(sync)), "sm100 tp_wait")
+
+    def tp_signal(self, sync) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_tp_signal(C.byref(sync)), "sm100 tp_signal")
+
+    def tp_linears_q4(self, q4, divisor: float, parts, m: int, sync=None) -> None:
+        self._bind()
+        arr = self._parts_q4(parts)
+        status(self.lib.velox_sm100_tp_linears_q4(q4[0].data_ptr(), q4[1].data_ptr(), divisor, arr, len(parts), m,
+                                                  self._sync(sync)), "sm100 tp_linears_q4")
+
+    def tp_linear_swiglu_q4_to_q4(self, q4, divisor: float, gate: WeightView, up: WeightView, m: int, out_q4,
+                                  out_divisor: float, outb: Optional[torch.Tensor] = None, sync=None) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_tp_linear_swiglu_q4_to_q4(
+            q4[0].data_ptr(), q4[1].data_ptr(), divisor, C.byref(_view_struct(gate)), C.byref(_view_struct(up)), m,
+            _ptr(outb), out_q4[0].data_ptr(), out_q4[1].data_ptr(), out_divisor, self._sync(sync)),
+            "sm100 tp_linear_swiglu_q4_to_q4")
+
     def tp_linear_q4_scatter(self, q4, divisor: float, w: WeightView, m: int, maps_dev: torch.Tensor,
-                             rows_per_owner: int) -> None:
+                             rows_per_owner: int, sync=None) -> None:
         self._bind()
         status(self.lib.velox_sm100_tp_linear_q4_scatter(q4[0].data_ptr(), q4[1].data_ptr(), divisor,
                                                          C.byref(_view_struct(w)), m, maps_dev.data_ptr(),
-                                                         rows_per_owner), "sm100 tp_linear_q4_scatter")
+                                                         rows_per_owner, self._sync(sync)), "sm100 tp_linear_q4_scatter")
 
     def tp_norm_q4(self, acc, slots, nslots: int, slot_stride: int, weight, codes_ptrs, atoms_ptrs, row0: int,
-                   rows: int, dim: int, eps: float, divisor: float, offset=False) -> None:
+                   rows: int, dim: int, eps: float, divisor: float, offset=False, sync=None) -> None:
         self._bind()
         n = len(codes_ptrs)
         status(self.lib.velox_sm100_tp_norm_q4(acc.data_ptr(), _ptr(slots), nslots, slot_stride, weight.data_ptr(),
                                                (C.c_uint64 * n)(*codes_ptrs), (C.c_uint64 * n)(*atoms_ptrs), n, row0,
-                                               rows, dim, eps, 1 if offset else 0, divisor), "sm100 tp_norm_q4")
+                                               rows, dim, eps, 1 if offset else 0, divisor, self._sync(sync)),
+               "sm100 tp_norm_q4")
 
-    def tp_finish(self, acc, slots, nslots: int, slot_stride: int, out_ptrs, row0: int, rows: int, dim: int) -> None:
+    def tp_finish(self, acc, slots, nslots: int, slot_stride: int, out_ptrs, row0: int, rows: int, dim: int,
+                  sync=None) -> None:
         self._bind()
         n = len(out_ptrs)
         status(self.lib.velox_sm100_tp_finish(acc.data_ptr(), slots.data_ptr(), nslots, slot_stride,
-                                              (C.c_uint64 * n)(*out_ptrs), n, row0, rows, dim), "sm100 tp_finish")
+                                              (C.c_uint64 * n)(*out_ptrs), n, row0, rows, dim, self._sync(sync)),
+               "sm100 tp_finish")
+
+    def debug_status(self) -> int:
+        return int(self.lib.velox_sm100_debug_status())
+
+    def debug_status_reset(self) -> None:
+        status(self.lib.velox_sm100_debug_status_reset(), "sm100 debug_status_reset")
 
     def add_bf16(self, acc, xb, n) -> None:
         self._bind()

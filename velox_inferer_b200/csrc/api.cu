@@ -229,7 +229,7 @@ static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_v
                          float* y, uint16_t* yb, long long ld, long long col,
                          const uint8_t* q_codes = nullptr, const uint8_t* q_atoms = nullptr,
                          uint8_t* qo_codes = nullptr, uint8_t* qo_atoms = nullptr, float qo_divisor = 0.0f,
-                         const void* rs_maps = nullptr, int rs_rows = 0) {
+                         const void* rs_maps = nullptr, int rs_rows = 0, const velox_sm100_tp_sync* sync = nullptr) {
     if (m <= 0 || (!x && !xb && !q_codes) || (!y && !yb && !qo_codes && !rs_maps)) return VELOX_ERR_SHAPE;
     int rc = check_view(view);
     if (rc != 0) return rc;
@@ -250,10 +250,11 @@ static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.qo_divisor = qo_divisor;
     a.rs_maps = rs_maps;
     a.rs_rows_per_owner = rs_rows;
+    a.sync = sync;
     Plan p = plan_for(*view, m);
     // the scattering epilogue is the GEMM's (same rounding as the small-batch streaming kernel)
     if (rs_maps && m > 16 && p.path == PATH_GEMV_TC && p.act == VELOX_ACT_NVFP4) p.path = PATH_GEMM_A4;
-    if (rs_maps && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
+    if ((rs_maps || sync) && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
     // pre-quantised input: the FP4 tensor-core paths only; and quantised output: the FP4 tensor-core paths only
     if (q_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
     if (qo_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
@@ -263,7 +264,8 @@ static int linear_common(const float* x, const uint16_t* xb, const velox_sm100_v
 static int swiglu_common(const float* x, const uint16_t* xb, const velox_sm100_view* gate,
                          const velox_sm100_view* up, int m, float* out, uint16_t* outb,
                          const uint8_t* q_codes = nullptr, const uint8_t* q_atoms = nullptr,
-                         uint8_t* qo_codes = nullptr, uint8_t* qo_atoms = nullptr, float qo_divisor = 0.0f) {
+                         uint8_t* qo_codes = nullptr, uint8_t* qo_atoms = nullptr, float qo_divisor = 0.0f,
+                         const velox_sm100_tp_sync* sync = nullptr) {
     if (m <= 0 || (!x && !xb && !q_codes) || (!out && !outb && !qo_codes)) return VELOX_ERR_SHAPE;
     int rc = check_view(gate);
     if (rc != 0) return rc;
@@ -295,7 +297,11 @@ static int swiglu_common(const float* x, const uint16_t* xb, const velox_sm100_v
     a.qo_codes = qo_codes;
     a.qo_atoms = qo_atoms;
     a.qo_divisor = qo_divisor;
-    const Plan p = plan_swiglu(both, *gate, *up, m);
+    a.sync = sync;
+    Plan p = plan_swiglu(both, *gate, *up, m);
+    // (a launch that waits for peers is the GEMM's; same rounding as the small-batch streaming kernel)
+    if (sync && m > 16 && p.path == PATH_GEMV_TC && p.act == VELOX_ACT_NVFP4) p.path = PATH_GEMM_A4;
+    if (sync && p.path != PATH_GEMM_A4) return VELOX_ERR_UNSUPPORTED;
     if (q_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
     if (qo_codes && p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
     return run(a, p);
@@ -345,7 +351,19 @@ int velox_sm100_debug_status(void) {
     const int a = gemm_status_sync();
     if (a != 0) return a;
     const int b = gemv_status_sync();
-    return b != 0 ? b : gemv_tc_status_sync();
+    if (b != 0) return b;
+    const int c = gemv_tc_status_sync();
+    return c != 0 ? c : tp_status_sync();
+}
+
+int velox_sm100_debug_status_reset(void) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return (int)e;
+    int rc = gemm_status_reset();
+    if (rc == 0) rc = gemv_status_reset();
+    if (rc == 0) rc = gemv_tc_status_reset();
+    if (rc == 0) rc = tp_status_reset();
+    return rc;
 }
 
 long long velox_sm100_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
@@ -526,8 +544,8 @@ int velox_sm100_linear_swiglu_q4_to_q4(const uint8_t* codes, const uint8_t* atom
                          out_divisor);
 }
 
-int velox_sm100_linears_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
-                           const velox_sm100_part_q4* parts, int nparts, int m) {
+static int linears_q4_common(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                             const velox_sm100_part_q4* parts, int nparts, int m, const velox_sm100_tp_sync* sync) {
     if (!codes || !atoms || !parts || nparts < 1 || m <= 0) return VELOX_ERR_SHAPE;
     for (int i = 0; i < nparts; i++) {
         const velox_sm100_part_q4& q = parts[i];
@@ -549,15 +567,29 @@ int velox_sm100_linears_q4(const uint8_t* codes, const uint8_t* atoms, float div
         l.qo_codes = q.out_codes;
         l.qo_atoms = q.out_atoms;
         l.qo_divisor = q.out_divisor;
+        l.sync = sync;
         return l;
     };
-    // decode: one launch for up to three views; otherwise one launch per view
-    if (nparts <= 3 && plan_for(parts[0].view, m).path == PATH_GEMV_TC) {
+    // Up to three views as one launch: the streaming kernel where every view would take it (decode,
+    // and small batches of views it streams faster), the GEMM where every view would take that.
+    if (nparts <= 3) {
+        bool all_stream = !sync, all_gemm = m > 16;
+        for (int i = 0; i < nparts; i++) {
+            const Path path = plan_for(parts[i].view, m).path;
+            all_stream = all_stream && path == PATH_GEMV_TC;
+            all_gemm = all_gemm && (path == PATH_GEMM_A4 || (sync && path == PATH_GEMV_TC));
+        }
         LinearArgs l[3];
         for (int i = 0; i < nparts; i++) l[i] = args_of(parts[i]);
-        const int rc = gemv_nvfp4_tc_parts(l, nparts, divisor);
-        if (rc != VELOX_ERR_UNSUPPORTED) return rc;
+        if (all_stream && m <= 16) {
+            const int rc = gemv_nvfp4_tc_parts(l, nparts, divisor);
+            if (rc != VELOX_ERR_UNSUPPORTED) return rc;
+        } else if (all_gemm) {
+            const int rc = gemm_linears_q4(l, nparts, divisor, sync);
+            if (rc != VELOX_ERR_UNSUPPORTED) return rc;
+        }
     }
+    if (sync) return VELOX_ERR_UNSUPPORTED;
     for (int i = 0; i < nparts; i++) {
         const Plan p = plan_for(parts[i].view, m);
         if (p.path != PATH_GEMM_A4 && p.path != PATH_GEMV_TC) return VELOX_ERR_UNSUPPORTED;
@@ -567,22 +599,46 @@ int velox_sm100_linears_q4(const uint8_t* codes, const uint8_t* atoms, float div
     return 0;
 }
 
+int velox_sm100_linears_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                           const velox_sm100_part_q4* parts, int nparts, int m) {
+    return linears_q4_common(codes, atoms, divisor, parts, nparts, m, nullptr);
+}
+
+int velox_sm100_tp_linears_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                              const velox_sm100_part_q4* parts, int nparts, int m, const velox_sm100_tp_sync* sync) {
+    return linears_q4_common(codes, atoms, divisor, parts, nparts, m, sync);
+}
+
+int velox_sm100_tp_linear_swiglu_q4_to_q4(const uint8_t* codes, const uint8_t* atoms, float divisor,
+                                          const velox_sm100_view* gate, const velox_sm100_view* up, int m,
+                                          uint16_t* outb, uint8_t* out_codes, uint8_t* out_atoms, float out_divisor,
+                                          const velox_sm100_tp_sync* sync) {
+    if (!gate || !up || !codes || !atoms || !out_codes || !out_atoms) return VELOX_ERR_SHAPE;
+    if (gate->policy != VELOX_POLICY_ALLOW_A4 || gate->divisor != divisor || up->policy != VELOX_POLICY_ALLOW_A4 ||
+        up->divisor != divisor)
+        return VELOX_ERR_UNSUPPORTED;
+    return swiglu_common(nullptr, nullptr, gate, up, m, nullptr, outb, codes, atoms, out_codes, out_atoms,
+                         out_divisor, sync);
+}
+
 int velox_sm100_tp_make_maps(void* maps_dev, const unsigned long long* slot_ptrs, int n, int rows_per_owner,
                              long long cols) {
     return gemm_make_rs_maps(maps_dev, slot_ptrs, n, rows_per_owner, cols);
 }
 
 int velox_sm100_tp_linear_q4_scatter(const uint8_t* codes, const uint8_t* atoms, float divisor,
-                                     const velox_sm100_view* view, int m, const void* maps_dev, int rows_per_owner) {
+                                     const velox_sm100_view* view, int m, const void* maps_dev, int rows_per_owner,
+                                     const velox_sm100_tp_sync* sync) {
     if (!view || !codes || !atoms || !maps_dev) return VELOX_ERR_SHAPE;
     if (view->policy != VELOX_POLICY_ALLOW_A4 || view->divisor != divisor) return VELOX_ERR_UNSUPPORTED;
     return linear_common(nullptr, nullptr, view, m, nullptr, nullptr, view->rows, 0, codes, atoms, nullptr, nullptr,
-                         0.0f, maps_dev, rows_per_owner);
+                         0.0f, maps_dev, rows_per_owner, sync);
 }
 
 int velox_sm100_tp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
                            const unsigned long long* codes_ptrs, const unsigned long long* atoms_ptrs, int ndst,
-                           long long row0, int rows, int dim, float eps, int offset, float divisor) {
+                           long long row0, int rows, int dim, float eps, int offset, float divisor,
+                           const velox_sm100_tp_sync* sync) {
     if (!acc || !weight || !codes_ptrs || !atoms_ptrs || ndst < 1 || ndst > VX_MAX_PEERS) return VELOX_ERR_SHAPE;
     uint8_t* c[VX_MAX_PEERS];
     uint8_t* s[VX_MAX_PEERS];
@@ -591,18 +647,19 @@ int velox_sm100_tp_norm_q4(float* acc, const uint16_t* slots, int nslots, long l
         s[d] = reinterpret_cast<uint8_t*>(atoms_ptrs[d]);
         if (!c[d] || !s[d]) return VELOX_ERR_SHAPE;
     }
-    return sp_norm_q4(acc, slots, nslots, slot_stride, weight, c, s, ndst, row0, rows, dim, eps, offset, divisor);
+    return sp_norm_q4(acc, slots, nslots, slot_stride, weight, c, s, ndst, row0, rows, dim, eps, offset, divisor, sync);
 }
 
 int velox_sm100_tp_finish(float* acc, const uint16_t* slots, int nslots, long long slot_stride,
-                          const unsigned long long* out_ptrs, int ndst, long long row0, int rows, int dim) {
+                          const unsigned long long* out_ptrs, int ndst, long long row0, int rows, int dim,
+                          const velox_sm100_tp_sync* sync) {
     if (!acc || !slots || !out_ptrs || ndst < 1 || ndst > VX_MAX_PEERS) return VELOX_ERR_SHAPE;
     uint16_t* o[VX_MAX_PEERS];
     for (int d = 0; d < ndst; d++) {
         o[d] = reinterpret_cast<uint16_t*>(out_ptrs[d]);
         if (!o[d]) return VELOX_ERR_SHAPE;
     }
-    return sp_finish(acc, slots, nslots, slot_stride, o, ndst, row0, rows, dim);
+    return sp_finish(acc, slots, nslots, slot_stride, o, ndst, row0, rows, dim, sync);
 }
 
 int velox_sm100_add_bf16(float* acc, const uint16_t* xb, long long len) {

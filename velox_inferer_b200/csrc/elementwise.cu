@@ -7,6 +7,7 @@
 
 #include "common.cuh"
 #include "kernels.cuh"
+#include "tpsync.cuh"
 
 namespace vx {
 
@@ -176,14 +177,23 @@ __global__ void __launch_bounds__(MAXT)
 add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x, const uint16_t* __restrict__ xb,
                             int nslots, long long slot_stride, const float* __restrict__ weight,
                             uint16_t* __restrict__ yb, const Q4Dest dst, long long row0, int rows, int dim,
-                            float eps, float offset, float divisor) {
+                            float eps, float offset, float divisor, const __grid_constant__ TpSync sync) {
     __shared__ float red[32];
     const int T = (int)blockDim.x;   // a multiple of 32, at most 1024
     const long long row = blockIdx.x;
     if (threadIdx.x == 0) grid_launch_dependents();   // a decode linear behind this may start fetching weights
+    if (sync.wait_phase >= 0) {
+        // tensor parallel: the partial-sum slots are complete once every rank's linear has said so
+        if (threadIdx.x == 0) tp_wait_flags(sync);
+        __syncthreads();
+    }
     if (row >= rows) {
         for (int g = threadIdx.x; g < dim / 16; g += blockDim.x)
             for (int d = 0; d < dst.n; d++) dst.atoms[d][nvfp4_scale_offset(row0 + row, g, dim)] = 0;
+        if (sync.signal_phase >= 0) {
+            __syncthreads();
+            if (threadIdx.x == 0) tp_signal(sync, gridDim.x);
+        }
         return;
     }
     const long long base = row * dim;
@@ -268,8 +278,9 @@ add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x
     ss = warp_sum(ss);
     if (threadIdx.x % VX_WARP == 0) red[threadIdx.x / VX_WARP] = ss;
     __syncthreads();
-    float total = 0.0f;
-    for (int i = 0; i < T / VX_WARP; i++) total += red[i];
+    // the warps' sums go through the same shuffle tree as in the persistent forms below, so that a
+    // row gives the same bits whichever of these kernels takes it
+    const float total = warp_sum((int)(threadIdx.x % VX_WARP) < T / VX_WARP ? red[threadIdx.x % VX_WARP] : 0.0f);
     const float inv = 1.0f / sqrtf(total / (float)dim + eps);
     const long long obase = (row0 + row) * dim;
 #pragma unroll
@@ -317,6 +328,11 @@ add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x
                 dst.atoms[d][soff] = (uint8_t)sb;
             }
         }
+    }
+    if (sync.signal_phase >= 0) {
+        // this row is in place on every rank: the last block of the grid raises this rank's flag there
+        __syncthreads();
+        if (threadIdx.x == 0) tp_signal(sync, gridDim.x);
     }
 }
 
@@ -430,11 +446,16 @@ template <int NS>
 __global__ void __launch_bounds__(1024, 1)
 sp_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ slots, long long slot_stride,
                          const float* __restrict__ weight, const Q4Dest dst, long long row0, int rows, int dim,
-                         float eps, float offset, float divisor) {
+                         float eps, float offset, float divisor, const __grid_constant__ TpSync sync) {
     __shared__ float red[2][32];
     const int T = (int)blockDim.x, tid = (int)threadIdx.x;
     const int c0 = tid * 4, c1 = (T + tid) * 4;
     if (tid == 0) grid_launch_dependents();
+    if (sync.wait_phase >= 0) {
+        // the partial-sum slots are complete once every rank's row-split linear has said so
+        if (tid == 0) tp_wait_flags(sync);
+        __syncthreads();
+    }
     float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
     uint2 b0[NS], b1[NS];
     auto fetch = [&](long long r) {
@@ -526,13 +547,22 @@ sp_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ s
             }
         }
     }
+    if (sync.signal_phase >= 0) {
+        // this block's rows are in place on every rank: the last block of the grid raises the flag
+        __syncthreads();
+        if (tid == 0) tp_signal(sync, gridDim.x);
+    }
 }
 
 // x_own += sum of the slots, then the rows as bf16 to every destination (the last step of a
 // sequence-parallel stack: residual add and all-gather of the result in one pass).
 __global__ void __launch_bounds__(256)
 sp_finish_kernel(float* __restrict__ acc, const uint16_t* __restrict__ slots, int nslots, long long slot_stride,
-                 const Q4Dest dst, long long row0, long long len, int dim) {
+                 const Q4Dest dst, long long row0, long long len, int dim, const __grid_constant__ TpSync sync) {
+    if (sync.wait_phase >= 0) {
+        if (threadIdx.x == 0) tp_wait_flags(sync);
+        __syncthreads();
+    }
     for (long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 4; i < len;
          i += (long long)gridDim.x * blockDim.x * 4) {
         float4 a = *reinterpret_cast<const float4*>(acc + i);
@@ -549,22 +579,26 @@ sp_finish_kernel(float* __restrict__ acc, const uint16_t* __restrict__ slots, in
         for (int d = 0; d < dst.n; d++)
             *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(dst.codes[d]) + row0 * dim + i) = pk;
     }
+    if (sync.signal_phase >= 0) {
+        __syncthreads();
+        if (threadIdx.x == 0) tp_signal(sync, gridDim.x);
+    }
 }
 
 static int launch_norm_q4(float* acc, const float* x, const uint16_t* xb, int nslots, long long slot_stride,
                           const float* weight, uint16_t* yb, const Q4Dest& dst, long long row0, int rows,
-                          int rows_padded, int dim, float eps, int offset, float divisor) {
+                          int rows_padded, int dim, float eps, int offset, float divisor, const TpSync& sync) {
     const float off = offset ? 1.0f : 0.0f;
     if (dim % 256 == 0)
         // one block per row with dim / 8 threads: two 128-bit slices per thread, many warps in flight
         add_rms_norm_q4_rows_kernel<2, 1024><<<(unsigned)rows_padded, dim / 8, 0, stream()>>>(
-            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor);
+            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor, sync);
     else if (dim <= 2048)
         add_rms_norm_q4_rows_kernel<2, 256><<<(unsigned)rows_padded, 256, 0, stream()>>>(
-            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor);
+            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor, sync);
     else
         add_rms_norm_q4_rows_kernel<8, 256><<<(unsigned)rows_padded, 256, 0, stream()>>>(
-            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor);
+            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor, sync);
     return launch_status();
 }
 
@@ -623,7 +657,9 @@ int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float*
         dst.codes[0] = codes;
         dst.atoms[0] = atoms;
         dst.n = 1;
-        return launch_norm_q4(acc, x, xb, 1, 0, weight, yb, dst, 0, rows, rows_padded, dim, eps, offset, divisor);
+        TpSync none{};
+        none.wait_phase = none.signal_phase = -1;
+        return launch_norm_q4(acc, x, xb, 1, 0, weight, yb, dst, 0, rows, rows_padded, dim, eps, offset, divisor, none);
     }
     add_rms_norm_q4_kernel<<<(unsigned)rows_padded, 256, 0, stream()>>>(acc, x, xb, weight, yb, codes, atoms, rows,
                                                                          dim, eps, offset ? 1.0f : 0.0f, divisor);
@@ -632,7 +668,7 @@ int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float*
 
 int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
                uint8_t* const* codes, uint8_t* const* atoms, int ndst, long long row0, int rows, int dim, float eps,
-               int offset, float divisor) {
+               int offset, float divisor, const velox_sm100_tp_sync* sync) {
     if (rows < 1 || rows % 128 != 0 || row0 % 128 != 0 || dim < 64 || dim % 64 != 0 || dim > 8192 ||
         !(divisor > 0.0f) || ndst < 1 || ndst > VX_MAX_PEERS || nslots < 0 || (nslots > 0 && !slots))
         return VELOX_ERR_SHAPE;
@@ -642,6 +678,9 @@ int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_str
         dst.atoms[d] = atoms[d];
     }
     dst.n = ndst;
+    TpSync ts;
+    const int src = tp_sync_fill_elementwise(&ts, sync);
+    if (src != 0) return src;
     const bool aligned = ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0 &&
                          (reinterpret_cast<uintptr_t>(slots) & 7) == 0 && slot_stride % 4 == 0;
     if (aligned && dim % 256 == 0 && (nslots == 2 || nslots == 4 || nslots == 8)) {
@@ -656,27 +695,30 @@ int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_str
         const float off = offset ? 1.0f : 0.0f;
         if (nslots == 2)
             sp_norm_q4_stream_kernel<2><<<blocks, dim / 8, 0, stream()>>>(acc, slots, slot_stride, weight, dst, row0, rows,
-                                                                            dim, eps, off, divisor);
+                                                                            dim, eps, off, divisor, ts);
         else if (nslots == 4)
             sp_norm_q4_stream_kernel<4><<<blocks, dim / 8, 0, stream()>>>(acc, slots, slot_stride, weight, dst, row0, rows,
-                                                                            dim, eps, off, divisor);
+                                                                            dim, eps, off, divisor, ts);
         else
             sp_norm_q4_stream_kernel<8><<<blocks, dim / 8, 0, stream()>>>(acc, slots, slot_stride, weight, dst, row0, rows,
-                                                                            dim, eps, off, divisor);
+                                                                            dim, eps, off, divisor, ts);
         return launch_status();
     }
     return launch_norm_q4(acc, nullptr, nslots > 0 ? slots : nullptr, nslots, slot_stride, weight, nullptr, dst, row0,
-                          rows, rows, dim, eps, offset, divisor);
+                          rows, rows, dim, eps, offset, divisor, ts);
 }
 
 int sp_finish(float* acc, const uint16_t* slots, int nslots, long long slot_stride, uint16_t* const* out, int ndst,
-              long long row0, int rows, int dim) {
+              long long row0, int rows, int dim, const velox_sm100_tp_sync* sync) {
     if (rows < 1 || dim % 4 != 0 || ndst < 1 || ndst > VX_MAX_PEERS || nslots < 1 || !slots) return VELOX_ERR_SHAPE;
     Q4Dest dst{};
     for (int d = 0; d < ndst; d++) dst.codes[d] = reinterpret_cast<uint8_t*>(out[d]);
     dst.n = ndst;
     const long long len = (long long)rows * dim;
-    sp_finish_kernel<<<grid_1d(len / 4, 256), 256, 0, stream()>>>(acc, slots, nslots, slot_stride, dst, row0, len, dim);
+    TpSync ts;
+    const int src = tp_sync_fill_elementwise(&ts, sync);
+    if (src != 0) return src;
+    sp_finish_kernel<<<grid_1d(len / 4, 256), 256, 0, stream()>>>(acc, slots, nslots, slot_stride, dst, row0, len, dim, ts);
     return launch_status();
 }
 

@@ -39,6 +39,7 @@
 #include "common.cuh"
 #include "gemm.cuh"
 #include "tcgen.cuh"
+#include "tpsync.cuh"
 
 namespace vx {
 
@@ -77,58 +78,58 @@ constexpr int MOVER_WARP0 = 12;  // warps 12..15 move scales into tensor memory
 enum { ST_OK = 0, ST_TIMEOUT_EMPTY = 1, ST_TIMEOUT_FULL = 2, ST_TIMEOUT_ACC_EMPTY = 3,
        ST_TIMEOUT_ACC_FULL = 4, ST_TIMEOUT_SF = 5 };
 
+constexpr int MAX_PARTS = 3;   // views one launch can serve (q, k, v of one input)
+
+// What differs between the views of one launch. Index [2]: the two 128-row halves of a W tile
+// (the same view twice for a plain linear, gate and up for the fused SwiGLU form).
+struct PartParams {
+    long long b_row0[2];       // first row (tensor-map coordinates) of n-tile 0, per half
+    long long b_rows_total[2]; // rows the half's tensor map / scale plane holds
+    long long valid_begin[2], valid_end[2];  // rows of each half that belong to the view
+    long long out_row0;        // row (half-0 coordinates) that maps to output column `col`
+    const uint8_t* sfb[2];
+    const float* wdiv[2];
+    const uint16_t* col_scale[2];  // bf16 per row, indexed by the half's row coordinate
+    float* y;
+    uint16_t* yb;
+    long long ld, col;
+    uint8_t* q_codes;   // optional: the output also (or only) as NVFP4 activations, codes [m, q_ld / 2] ...
+    uint8_t* q_atoms;   // ... and scale atoms over ceil(m / 128) * 128 rows
+    long long q_ld;     // columns of the quantised matrix (a multiple of 64)
+    float q_divisor;
+    int b_tile_rows;    // rows advanced per n-tile
+    int tiles_n;
+    int tma_store;      // bf16-only output that the part's output tensor map describes
+    int tile_end;       // tiles of this and all earlier parts (work units are numbered part after part)
+};
+
 struct GemmParams {
     int m;
     int k_blocks;       // ceil(k_steps / 4)
     int k_steps;        // 32-byte MMA k-steps in a row
     int k_elems_per_block;  // tensor-map elements per 128-byte block (128 for byte maps, 64 bf16)
     int a_k_blocks;         // the activation operand wraps around after this many blocks
-    int tiles_m, tiles_n;
-    long long b_row0[2];       // first row (tensor-map coordinates) of n-tile 0, per half
-    int b_tile_rows;           // rows advanced per n-tile
-    long long b_rows_total[2]; // rows the half's tensor map / scale plane holds
-    long long valid_begin[2], valid_end[2];  // rows of each half that belong to the view
-    long long out_row0;        // row (half-0 coordinates) that maps to output column `col`
-    const uint8_t* sfa;
-    const uint8_t* sfb[2];
+    int tiles_m;
+    int nparts;
     int k_tiles64;
+    const uint8_t* sfa;
     float alpha;
-    const float* wdiv[2];
     const float* tok_scale;
-    const uint16_t* col_scale[2];  // bf16 per row, indexed by the half's row coordinate
-    float* y;
-    uint16_t* yb;
-    long long ld, col;
-    int tma_store;  // bf16-only output that a tensor map over yb + col describes
     const CUtensorMap* out_maps;   // optional (tensor parallel): one output map per owning rank, in global memory;
     int rows_per_owner;            // token rows [o * rows_per_owner, (o + 1) * rows_per_owner) go to out_maps[o]
-    uint8_t* q_codes;   // optional: the output also (or only) as NVFP4 activations, codes [m, q_ld / 2] ...
-    uint8_t* q_atoms;   // ... and scale atoms over ceil(m / 128) * 128 rows
-    float q_divisor;
-    long long q_ld;     // columns of the quantised matrix (a multiple of 64)
     int early;      // the launch may start before the kernel ahead of it has finished (see the producers)
     int* status;
-    int dbg;        // profiling builds only: 1 no epilogue at all, 2 loads only, 8 no operand loads, 16 no scale path, 32 no MMAs
+    PartParams part[MAX_PARTS];
+    TpSync sync;    // tensor parallel: flags to wait for before the first activation load, flags to raise at the end
+};
+
+// W operand maps (SwiGLU: [0] gate, [1] up; otherwise one per part) and bf16 output maps per part.
+struct GemmMaps {
+    CUtensorMap b[MAX_PARTS];
+    CUtensorMap out[MAX_PARTS];
 };
 
 __device__ int g_gemm_status = 0;
-
-#ifdef VX_GEMM_PROFILE
-// Per-CTA cycle counters of a profiling build: [0] producer waiting for a free stage, [1] producer
-// total, [2] MMA thread waiting for operands, [3] MMA thread waiting for the accumulator to drain,
-// [4] MMA thread total, [5] epilogue waiting for the accumulator, [6] epilogue total, [7] MMA
-// thread waiting for scales.
-__device__ long long g_gemm_prof[160][12];
-#define PROF_DECL long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}
-#define PROF_T0(var) const long long var = clock64()
-#define PROF_ADD(slot, t0) prof[slot] += clock64() - (t0)
-#define PROF_OUT(slot) g_gemm_prof[blockIdx.x][slot] = prof[slot]
-#else
-#define PROF_DECL
-#define PROF_T0(var)
-#define PROF_ADD(slot, t0)
-#define PROF_OUT(slot)
-#endif
 
 // Instruction descriptor: M = 128 (256 across a pair), N = 256, K-major operands, f32 accumulate.
 template <int KIND, int CG>
@@ -143,9 +144,8 @@ __device__ __forceinline__ constexpr uint32_t instr_desc() {
 
 template <int KIND, bool SWIGLU, int CG>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b0,
-            const __grid_constant__ CUtensorMap tmap_b1, const __grid_constant__ CUtensorMap tmap_out,
-            const GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmMaps maps,
+            const __grid_constant__ GemmParams p) {
     using PL = Plan<CG>;
     constexpr int OP_STAGES = PL::STAGES;
     constexpr int OP_STAGE_BYTES = PL::STAGE_BYTES;
@@ -200,9 +200,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         mbar_init(acc_empty, 8 * CG);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b0) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b1) : "memory");
-        if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_out) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.b[0]) : "memory");
+        if (SWIGLU) asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.b[1]) : "memory");
+        if (p.part[0].tma_store && !p.out_maps) asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.out[0]) : "memory");
     }
     if (warp == 1) {
         // tensor memory: in a pair both CTAs' warp 1 take part and both get the same address
@@ -228,7 +228,41 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int unit = CG == 2 ? (int)blockIdx.x / 2 : (int)blockIdx.x;
     const int units = (int)gridDim.x / CG;
     const int tiles_mu = (p.tiles_m + CG - 1) / CG;
-    const int num_tiles = tiles_mu * p.tiles_n;
+    const int num_tiles = p.part[p.nparts - 1].tile_end;
+    // Work unit -> (part, token tile, row tile). Token tiles vary fastest, so the CTAs working at
+    // the same time share W tiles in L2.
+    struct TileAt {
+        int pi, mt, nt;
+    };
+    auto tile_at = [&](int tile) {
+        TileAt t;
+        t.pi = 0;
+        int first = 0;
+        if (!SWIGLU) {
+            while (t.pi + 1 < p.nparts && tile >= p.part[t.pi].tile_end) {
+                first = p.part[t.pi].tile_end;
+                t.pi++;
+            }
+        }
+        const int local = tile - first;
+        t.mt = (local % tiles_mu) * CG + (int)rank;
+        t.nt = local / tiles_mu;
+        return t;
+    };
+    // Tensor parallel: the activations (and their scales) are complete once every rank's flag of
+    // this launch's wait row has reached the step's epoch. Polled by one lane, after the launch
+    // ahead in the stream has completed.
+    auto peers_ready = [&](bool leader) {
+        bool ok = true;
+        if (p.sync.wait_phase >= 0) {
+            if (leader) {
+                ok = tp_wait_flags(p.sync);
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+            }
+            ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, __ffs(__ballot_sync(0xffffffffu, leader)) - 1) != 0;
+        }
+        return ok;
+    };
 
     if (warp == 0) {
         // ---------------- operand producer: this CTA's x tile and W rows per k-block ----------------
@@ -238,59 +272,56 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t phase = 0;
             bool ok = true;
             const bool leader = elect_one();
-            PROF_DECL;
-            PROF_T0(t_all);
             // Weights that are read from their stored payload do not depend on the kernel ahead of
             // this one in the stream, the activations do: with early start allowed the first ring
             // pass requests its W boxes at once, then waits for that kernel and adds the x boxes.
             // (The bf16 path's W operand is scratch the kernel ahead wrote: it waits first.)
             int issued = 0, pend_x[OP_STAGES], pend_y[OP_STAGES];
             bool waited = !(p.early && KIND != KIND_BF16);
-            if (waited) grid_dependency_wait();
+            if (waited) {
+                grid_dependency_wait();
+                ok = peers_ready(leader);
+            }
             auto after_dependency = [&]() {
                 grid_dependency_wait();
+                ok = peers_ready(leader) && ok;
                 if (leader)
                     for (int i = 0; i < issued; i++)
                         tma_load_2d(base + i * OP_STAGE_BYTES, &tmap_a, op_full(i), pend_x[i], pend_y[i]);
                 waited = true;
             };
             for (int tile = unit; tile < num_tiles && ok; tile += units) {
-                const int mt = (tile % tiles_mu) * CG + (int)rank, nt = tile / tiles_mu;
-                const int r0 = (int)(p.b_row0[0] + (long long)nt * p.b_tile_rows);
-                const int r1 = (int)(p.b_row0[1] + (long long)nt * p.b_tile_rows);
-                for (int kb = 0; kb < p.k_blocks; kb++) {
+                const TileAt t = tile_at(tile);
+                const PartParams& pp = p.part[t.pi];
+                const int mt = t.mt;
+                const int r0 = (int)(pp.b_row0[0] + (long long)t.nt * pp.b_tile_rows);
+                const int r1 = (int)(pp.b_row0[1] + (long long)t.nt * pp.b_tile_rows);
+                const CUtensorMap* mb0 = SWIGLU ? &maps.b[0] : &maps.b[t.pi];
+                const CUtensorMap* mb1 = SWIGLU ? &maps.b[1] : mb0;
+                for (int kb = 0; kb < p.k_blocks && ok; kb++) {
                     if (!waited && issued == OP_STAGES) after_dependency();
-                    PROF_T0(t_w);
                     if (!mbar_wait(op_empty(stage), phase ^ 1u, 20)) {
                         if (leader) atomicExch(p.status, ST_TIMEOUT_EMPTY);
                         ok = false;
                         break;
                     }
-                    PROF_ADD(0, t_w);
                     const uint32_t sa = base + stage * OP_STAGE_BYTES;
                     const uint32_t sb = sa + A_BYTES;
                     const int kx = kb * p.k_elems_per_block;
                     if (leader) {
-#ifdef VX_GEMM_PROFILE
-                        if (p.dbg & 8) {   // timing only: operands are whatever the stage holds
-                            mbar_arrive(op_full(stage));
-                        } else
-#endif
-                        {
-                            mbar_arrive_expect_tx(op_full(stage), A_BYTES + PL::B_BYTES);
-                            if (waited)
-                                tma_load_2d(sa, &tmap_a, op_full(stage), (kb % p.a_k_blocks) * p.k_elems_per_block,
-                                            mt * BM);
-                            if (CG == 2) {
-                                // one half of the W tile; the MMA reads the other from the partner
-                                if (rank)
-                                    tma_load_2d(sb, &tmap_b1, op_full(stage), kx, r1);
-                                else
-                                    tma_load_2d(sb, &tmap_b0, op_full(stage), kx, r0);
-                            } else {
-                                tma_load_2d(sb, &tmap_b0, op_full(stage), kx, r0);
-                                tma_load_2d(sb + B_HALF_BYTES, &tmap_b1, op_full(stage), kx, r1);
-                            }
+                        mbar_arrive_expect_tx(op_full(stage), A_BYTES + PL::B_BYTES);
+                        if (waited)
+                            tma_load_2d(sa, &tmap_a, op_full(stage), (kb % p.a_k_blocks) * p.k_elems_per_block,
+                                        mt * BM);
+                        if (CG == 2) {
+                            // one half of the W tile; the MMA reads the other from the partner
+                            if (rank)
+                                tma_load_2d(sb, mb1, op_full(stage), kx, r1);
+                            else
+                                tma_load_2d(sb, mb0, op_full(stage), kx, r0);
+                        } else {
+                            tma_load_2d(sb, mb0, op_full(stage), kx, r0);
+                            tma_load_2d(sb + B_HALF_BYTES, mb1, op_full(stage), kx, r1);
                         }
                     }
                     if (!waited) {
@@ -306,11 +337,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
             if (!waited) after_dependency();
             if (!ok) __nanosleep(200000);  // let copies already in flight land before the CTA exits
-            PROF_ADD(1, t_all);
-            if (leader) {
-                PROF_OUT(0);
-                PROF_OUT(1);
-            }
         }
     } else if (warp == 1 && rank != 0) {
         // ---------------- pair, second CTA: tell the MMA issuer when this CTA's operands have landed ----------------
@@ -343,35 +369,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             bool ok = true;
             const uint32_t idesc = instr_desc<KIND, CG>();
             const bool leader = elect_one();
-            PROF_DECL;
-            PROF_T0(t_all);
-#ifdef VX_GEMM_PROFILE
-            const unsigned long long ns0 = global_timer_ns();
-#endif
             for (int tile = unit; tile < num_tiles && ok; tile += units) {
-                PROF_T0(t_acc);
                 if (!(CG == 2 ? mbar_wait_cluster(acc_empty, acc_phase ^ 1u) : mbar_wait(acc_empty, acc_phase ^ 1u))) {
                     if (leader) atomicExch(p.status, ST_TIMEOUT_ACC_EMPTY);
                     break;
                 }
-                PROF_ADD(3, t_acc);
                 for (int kb = 0; kb < p.k_blocks; kb++) {
-                    PROF_T0(t_w);
                     if (!mbar_wait(op_full(stage), phase) ||
                         (CG == 2 && !mbar_wait_cluster(peer_full(stage), phase))) {
                         if (leader) atomicExch(p.status, ST_TIMEOUT_FULL);
                         ok = false;
                         break;
                     }
-                    PROF_ADD(2, t_w);
-                    if (KIND == KIND_MXF4 && !(p.dbg & 16)) {
-                        PROF_T0(t_s);
+                    if (KIND == KIND_MXF4) {
                         if (!(CG == 2 ? mbar_wait_cluster(tsf_full(sstage), sphase) : mbar_wait(tsf_full(sstage), sphase))) {
                             if (leader) atomicExch(p.status, ST_TIMEOUT_SF);
                             ok = false;
                             break;
                         }
-                        PROF_ADD(7, t_s);
                     }
                     tc_fence_after();
                     const int steps = min(4, p.k_steps - 4 * kb);
@@ -379,15 +394,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t sb = sa + A_BYTES;
                     const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
                     const uint32_t tsf = tmem + TMEM_SF_COL + sstage * TMEM_SF_SET;
-                    PROF_T0(t_i);
-#ifdef VX_GEMM_PROFILE
-                    if (p.dbg & 32) {   // timing only: no MMAs, stages handed straight back (loads alone)
-                        if (leader) {
-                            mbar_arrive(op_empty(stage));
-                            if (CG == 2) mbar_arrive_cluster(map_to_cta(op_empty(stage), 1));
-                        }
-                    } else
-#endif
                     if (leader) {
                         // advancing 32 bytes along K inside the swizzle row: +2 in the address field
                         if (steps == 4) {
@@ -401,9 +407,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                                                  tsf + 4 * j, tsf + 16 + 8 * j);
                         }
                         commit(op_empty(stage));
-                        if (KIND == KIND_MXF4 && !(p.dbg & 16)) commit(tsf_empty(sstage));
+                        if (KIND == KIND_MXF4) commit(tsf_empty(sstage));
                     }
-                    PROF_ADD(11, t_i);
                     if (++stage == OP_STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -418,57 +423,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if (ok && leader) commit(acc_full);
                 acc_phase ^= 1u;
             }
-            PROF_ADD(4, t_all);
-#ifdef VX_GEMM_PROFILE
-            prof[9] = (long long)(global_timer_ns() - ns0);   // wall time of this warp's loop, ns
-#endif
-            if (leader) {
-                PROF_OUT(9);
-                PROF_OUT(2);
-                PROF_OUT(3);
-                PROF_OUT(4);
-                PROF_OUT(7);
-                PROF_OUT(11);
-            }
         }
     } else if (warp >= EPI_WARP0 && warp < EPI_WARP0 + 8) {
         // ---------------- epilogue: eight warps, two per lane quadrant, each taking half the columns ----------------
         const int quad = warp % 4;
         const int hsel = (warp - EPI_WARP0) / 4;
         uint32_t acc_phase = 0;
-        const float d0 = p.wdiv[0] ? *p.wdiv[0] : 1.0f;
-        const float d1 = p.wdiv[1] ? *p.wdiv[1] : 1.0f;
-        const float s0 = p.alpha / d0, s1 = p.alpha / d1;
-        const uint16_t* cs0 = p.col_scale[0];
-        const uint16_t* cs1 = p.col_scale[1];
-        const long long cs_rows0 = p.b_rows_total[0], cs_rows1 = p.b_rows_total[1];
-        const long long vb0 = p.valid_begin[0], ve0 = p.valid_end[0], vb1 = p.valid_begin[1], ve1 = p.valid_end[1];
         const bool store_thread = (warp - EPI_WARP0) % 4 == 0 && lane == 0;   // one per column half
         const uint32_t my_box = staging + (uint32_t)hsel * 16384u;
         const int bar_id = 1 + hsel;                                          // the four warps of a half
         constexpr int CHUNKS = SWIGLU ? 4 : 8;   // 32-column output chunks in a tile
         constexpr int MINE = CHUNKS / 2;         // ... of which this warp takes half
-        PROF_DECL;
-        PROF_T0(t_all);
         for (int tile = unit; tile < num_tiles; tile += units) {
-            const int mt = (tile % tiles_mu) * CG + (int)rank, nt = tile / tiles_mu;
-            PROF_T0(t_w);
+            const TileAt t = tile_at(tile);
+            const PartParams& pp = p.part[t.pi];
+            const int mt = t.mt, nt = t.nt;
+            // this part's factors (requested before the wait for the accumulator, which hides them)
+            const float d0 = pp.wdiv[0] ? __ldg(pp.wdiv[0]) : 1.0f;
+            const float d1 = pp.wdiv[1] ? __ldg(pp.wdiv[1]) : 1.0f;
+            const uint16_t* cs0 = pp.col_scale[0];
+            const uint16_t* cs1 = pp.col_scale[1];
+            const long long cs_rows0 = pp.b_rows_total[0], cs_rows1 = pp.b_rows_total[1];
+            const long long vb0 = pp.valid_begin[0], ve0 = pp.valid_end[0], vb1 = pp.valid_begin[1], ve1 = pp.valid_end[1];
             if (!mbar_wait(acc_full, acc_phase, 60)) {
                 if (lane == 0) atomicExch(p.status, ST_TIMEOUT_ACC_FULL);
                 break;
             }
-            PROF_ADD(5, t_w);
             tc_fence_after();
+            const float s0 = p.alpha / d0, s1 = p.alpha / d1;
             const int row_in_tile = quad * 32 + lane;
             const long long token = (long long)mt * BM + row_in_tile;
             const bool tok_ok = token < p.m;
             const float ts = (p.tok_scale && tok_ok) ? p.tok_scale[token] : 1.0f;
             const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16);
-            const long long rbase[2] = {p.b_row0[0] + (long long)nt * p.b_tile_rows,
-                                        p.b_row0[1] + (long long)nt * p.b_tile_rows};
+            const long long rbase[2] = {pp.b_row0[0] + (long long)nt * pp.b_tile_rows,
+                                        pp.b_row0[1] + (long long)nt * pp.b_tile_rows};
             // Whole-tile bf16 output through shared memory and a tensor-map store: taken when the
             // tile does not start left of the output's first column.
-            const bool staged = p.tma_store && rbase[0] >= p.out_row0;
+            const bool staged = pp.tma_store && rbase[0] >= pp.out_row0;
             const bool any_token = (long long)mt * BM < p.m;   // false only for a pair's second CTA past the end
             // chunk ch of the accumulator (and its partner in the up half) -> 32 finished values
             auto compute = [&](const int ch, const uint32_t (&r)[32], const uint32_t (&r2)[32], float (&v)[32]) {
@@ -512,10 +504,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if (!tok_ok) return;
                 const int half = SWIGLU ? 0 : ch / 4;
                 const long long row0 = rbase[half] + (ch % 4) * 32;
-                const long long o0 = token * p.ld + p.col + (row0 - p.out_row0);
+                const long long o0 = token * pp.ld + pp.col + (row0 - pp.out_row0);
                 const long long vb = half ? vb1 : vb0, ve = half ? ve1 : ve0;
                 const bool all = row0 >= vb && row0 + 32 <= ve;
-                if (all && p.yb && ((reinterpret_cast<uintptr_t>(p.yb + o0) & 15) == 0)) {
+                if (all && pp.yb && ((reinterpret_cast<uintptr_t>(pp.yb + o0) & 15) == 0)) {
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
                         uint4 pk;
@@ -523,22 +515,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         pk.y = pack_bf16(v[8 * q + 2], v[8 * q + 3]);
                         pk.z = pack_bf16(v[8 * q + 4], v[8 * q + 5]);
                         pk.w = pack_bf16(v[8 * q + 6], v[8 * q + 7]);
-                        *reinterpret_cast<uint4*>(p.yb + o0 + 8 * q) = pk;
+                        *reinterpret_cast<uint4*>(pp.yb + o0 + 8 * q) = pk;
                     }
-                } else if (p.yb) {
+                } else if (pp.yb) {
 #pragma unroll
                     for (int c = 0; c < 32; c++)
-                        if (row0 + c >= vb && row0 + c < ve) p.yb[o0 + c] = bf16_bits(v[c]);
+                        if (row0 + c >= vb && row0 + c < ve) pp.yb[o0 + c] = bf16_bits(v[c]);
                 }
-                if (all && p.y && ((reinterpret_cast<uintptr_t>(p.y + o0) & 15) == 0)) {
+                if (all && pp.y && ((reinterpret_cast<uintptr_t>(pp.y + o0) & 15) == 0)) {
 #pragma unroll
                     for (int q = 0; q < 8; q++)
-                        *reinterpret_cast<float4*>(p.y + o0 + 4 * q) =
+                        *reinterpret_cast<float4*>(pp.y + o0 + 4 * q) =
                             make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-                } else if (p.y) {
+                } else if (pp.y) {
 #pragma unroll
                     for (int c = 0; c < 32; c++)
-                        if (row0 + c >= vb && row0 + c < ve) p.y[o0 + c] = v[c];
+                        if (row0 + c >= vb && row0 + c < ve) pp.y[o0 + c] = v[c];
                 }
             };
             auto release_acc = [&]() {
@@ -547,15 +539,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 __syncwarp();
                 if (lane == 0) arrive_lead(acc_empty);
             };
-#ifdef VX_GEMM_PROFILE
-            if (p.dbg & 1) {
-                release_acc();
-                acc_phase ^= 1u;
-                continue;
-            }
-#endif
-            const bool emit_q = p.q_codes != nullptr && mt < p.tiles_m;
-            if (staged || p.q_codes != nullptr) {
+            const bool emit_q = pp.q_codes != nullptr && mt < p.tiles_m;
+            if (staged || pp.q_codes != nullptr) {
                 // Drain first: finish this warp's values and keep them as packed bf16 (16 registers
                 // per chunk), release tensor memory so the next tile's MMAs can start, and only then
                 // spend time on shared-memory staging and the tensor-map stores.
@@ -573,7 +558,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
                     for (int c = 0; c < 16; c++) pk[i][c] = pack_bf16(v[2 * c], v[2 * c + 1]);
                 }
-                PROF_T0(t_c);
                 if (emit_q) {
                     // The output as the next linear's NVFP4 activations, quantised from the bf16
                     // values exactly as the stand-alone quantiser does (quotients by the Markstein
@@ -581,7 +565,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     // rounded a / d when r is the correctly rounded 1 / d).
 #pragma unroll
                     for (int j = 0; j < MINE / 2; j++) {
-                        const long long col0 = (rbase[0] - p.out_row0) + (long long)(hsel * MINE + 2 * j) * 32;
+                        const long long col0 = (rbase[0] - pp.out_row0) + (long long)(hsel * MINE + 2 * j) * 32;
                         uint32_t sc = 0;
                         uint32_t cw[8];
 #pragma unroll
@@ -595,15 +579,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                                 v[2 * i + 1] = __uint_as_float(u & 0xffff0000u);
                                 amax = fmaxf(amax, fmaxf(fabsf(v[2 * i]), fabsf(v[2 * i + 1])));
                             }
-                            const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(p.q_divisor, amax), 6.0f));
+                            const uint32_t sb = f32_to_e4m3(__fdiv_rn(__fmul_rn(pp.q_divisor, amax), 6.0f));
                             uint32_t o0 = 0, o1 = 0;
                             if (sb != 0) {
                                 const float ds = e4m3_to_f32(sb);
                                 const float rc = __frcp_rn(ds);
 #pragma unroll
                                 for (int i = 0; i < 8; i++) {
-                                    const float a0 = __fmul_rn(v[2 * i], p.q_divisor);
-                                    const float a1 = __fmul_rn(v[2 * i + 1], p.q_divisor);
+                                    const float a0 = __fmul_rn(v[2 * i], pp.q_divisor);
+                                    const float a1 = __fmul_rn(v[2 * i + 1], pp.q_divisor);
                                     float q0 = __fmul_rn(a0, rc), q1 = __fmul_rn(a1, rc);
                                     q0 = __fmaf_rn(__fmaf_rn(-q0, ds, a0), rc, q0);
                                     q1 = __fmaf_rn(__fmaf_rn(-q1, ds, a1), rc, q1);
@@ -615,14 +599,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                             cw[2 * g + 1] = o1;
                             sc |= sb << (8 * g);
                         }
-                        if (col0 + 64 <= p.q_ld) {
+                        if (col0 + 64 <= pp.q_ld) {
                             if (tok_ok) {
-                                uint4* dst = reinterpret_cast<uint4*>(p.q_codes + (token * p.q_ld + col0) / 2);
+                                uint4* dst = reinterpret_cast<uint4*>(pp.q_codes + (token * pp.q_ld + col0) / 2);
                                 dst[0] = make_uint4(cw[0], cw[1], cw[2], cw[3]);
                                 dst[1] = make_uint4(cw[4], cw[5], cw[6], cw[7]);
                             }
                             // rows past m inside the last 128-row atom carry zero scales
-                            *reinterpret_cast<uint32_t*>(p.q_atoms + nvfp4_scale_offset(token, col0 / 16, p.q_ld)) =
+                            *reinterpret_cast<uint32_t*>(pp.q_atoms + nvfp4_scale_offset(token, col0 / 16, pp.q_ld)) =
                                 tok_ok ? sc : 0u;
                         }
                     }
@@ -650,19 +634,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     if (store_thread && any_token) {
                         // tensor parallel: the tile goes straight into the buffer of the rank that owns
                         // these token rows (a store over NVLink when that is not this rank)
-                        const CUtensorMap* omap = &tmap_out;
+                        const CUtensorMap* omap = &maps.out[t.pi];
                         int orow = mt * BM;
                         if (p.out_maps) {
                             const int owner = orow / p.rows_per_owner;
                             omap = p.out_maps + owner;
                             orow -= owner * p.rows_per_owner;
                         }
-                        tma_store_2d(omap, my_box, (int)(rbase[0] - p.out_row0) + (hsel * (MINE / 2) + bx) * 64, orow);
+                        tma_store_2d(omap, my_box, (int)(rbase[0] - pp.out_row0) + (hsel * (MINE / 2) + bx) * 64, orow);
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
                 }
                 }
-                PROF_ADD(10, t_c);
             } else {
                 for (int i = 0; i < MINE; i++) {
                     const int ch = hsel * MINE + i;
@@ -678,12 +661,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
             acc_phase ^= 1u;
         }
-        if (store_thread) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-        PROF_ADD(6, t_all);
-        if (warp == EPI_WARP0 && lane == 0) {
-            PROF_OUT(5);
-            PROF_OUT(6);
-            PROF_OUT(10);
+        if (store_thread) {
+            // all of this thread's tile stores are complete (written, not merely read from shared memory)
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            if (p.sync.signal_phase >= 0) {
+                asm volatile("fence.proxy.async.global;" ::: "memory");
+                __threadfence_system();
+            }
         }
     } else if (KIND == KIND_MXF4 && warp == 2) {
         // ---------------- scale producer: whole 512-byte atoms, x then the two W halves ----------------
@@ -693,13 +677,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t phase = 0;
             bool ok = true;
             const bool leader = elect_one();
-            if (p.dbg & 16) ok = false;   // profiling builds, timing only: no scales at all
-            grid_dependency_wait();   // the activation scales come from the kernel ahead of this one
+            grid_dependency_wait();   // the activation scales come from the kernel ahead of this one ...
+            ok = peers_ready(leader);  // ... or, tensor parallel, from every rank's norm
             for (int tile = unit; tile < num_tiles && ok; tile += units) {
-                const int mt = (tile % tiles_mu) * CG + (int)rank, nt = tile / tiles_mu;
-                const long long r0 = p.b_row0[0] + (long long)nt * p.b_tile_rows;
-                const long long r1 = p.b_row0[1] + (long long)nt * p.b_tile_rows;
-                const bool sf0 = r0 < p.b_rows_total[0], sf1 = r1 < p.b_rows_total[1];
+                const TileAt t = tile_at(tile);
+                const PartParams& pp = p.part[t.pi];
+                const int mt = t.mt;
+                const long long r0 = pp.b_row0[0] + (long long)t.nt * pp.b_tile_rows;
+                const long long r1 = pp.b_row0[1] + (long long)t.nt * pp.b_tile_rows;
+                const bool sf0 = r0 < pp.b_rows_total[0], sf1 = r1 < pp.b_rows_total[1];
                 const bool sfx = mt < p.tiles_m;   // false only for a pair's second CTA past the last token tile
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!mbar_wait(sf_empty(stage), phase ^ 1u, 50)) {
@@ -720,10 +706,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                                 bulk_load_1d(ssfa, p.sfa + ((long long)mt * p.k_tiles64 + atom) * 512, bytes,
                                              sf_full(stage));
                             if (sf0)
-                                bulk_load_1d(ssfb, p.sfb[0] + ((r0 / 128) * p.k_tiles64 + atom) * 512, bytes,
+                                bulk_load_1d(ssfb, pp.sfb[0] + ((r0 / 128) * p.k_tiles64 + atom) * 512, bytes,
                                              sf_full(stage));
                             if (sf1)
-                                bulk_load_1d(ssfb + 4 * 512, p.sfb[1] + ((r1 / 128) * p.k_tiles64 + atom) * 512,
+                                bulk_load_1d(ssfb + 4 * 512, pp.sfb[1] + ((r1 / 128) * p.k_tiles64 + atom) * 512,
                                              bytes, sf_full(stage));
                         }
                     }
@@ -733,7 +719,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
                 }
             }
-            if (!ok && !(p.dbg & 16)) __nanosleep(200000);
+            if (!ok) __nanosleep(200000);
         }
     } else if (KIND == KIND_MXF4 && warp >= MOVER_WARP0) {
         // ---------------- scale movers: shared memory -> tensor memory through registers ----------------
@@ -743,7 +729,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int quad = warp % 4;
         int stage = 0;
         uint32_t phase = 0;
-        bool ok = !(p.dbg & 16);
+        bool ok = true;
         for (int tile = unit; tile < num_tiles && ok; tile += units) {
             for (int kb = 0; kb < p.k_blocks; kb++) {
                 if (!mbar_wait(sf_full(stage), phase, 50)) {
@@ -798,6 +784,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS)
                          : "memory");
     }
+    // Tensor parallel: every CTA's stores are complete behind the barrier above; the last CTA of the
+    // grid to get here tells every rank that this rank's partial sums have landed.
+    if (threadIdx.x == 0) tp_signal(p.sync, gridDim.x);
 }
 
 // ---- host side -------------------------------------------------------------------------------------------
@@ -882,31 +871,46 @@ int gemm_make_rs_maps(void* maps_dev, const unsigned long long* ptrs, int n, int
     return e == cudaSuccess ? 0 : (int)e;
 }
 
-// Tensor map over the bf16 output columns [col, col + out_cols) of yb, for whole-tile stores.
-// Leaves p.tma_store at 0 when the output is not bf16-only or not 16-byte friendly.
-static void make_out_map(CUtensorMap* map, GemmParams& p, long long out_cols, long long first_row) {
-    p.tma_store = 0;
-    if (!p.yb || p.y || p.ld % 8 != 0 || p.col % 8 != 0 || first_row % 8 != 0) return;
-    uint16_t* basep = p.yb + p.col;
+// Tensor map over the bf16 output columns [col, col + out_cols) of a part's yb, for whole-tile
+// stores. Leaves tma_store at 0 when the output is not bf16-only or not 16-byte friendly.
+static void make_out_map(CUtensorMap* map, int m, PartParams& pp, long long out_cols, long long first_row) {
+    pp.tma_store = 0;
+    if (!pp.yb || pp.y || pp.ld % 8 != 0 || pp.col % 8 != 0 || first_row % 8 != 0) return;
+    uint16_t* basep = pp.yb + pp.col;
     if (reinterpret_cast<uintptr_t>(basep) & 15) return;
-    const cuuint64_t dims[2] = {(cuuint64_t)out_cols, (cuuint64_t)p.m};
-    const cuuint64_t strides[1] = {(cuuint64_t)p.ld * 2};
+    const cuuint64_t dims[2] = {(cuuint64_t)out_cols, (cuuint64_t)m};
+    const cuuint64_t strides[1] = {(cuuint64_t)pp.ld * 2};
     const cuuint32_t box[2] = {64u, 128u};
     const cuuint32_t estr[2] = {1, 1};
     if (encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, basep, dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
-        p.tma_store = 1;
+        pp.tma_store = 1;
+}
+
+static int sm_count() {
+    static int sms[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (sms[dev] == 0) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        sms[dev] = n > 0 ? n : 148;
+    }
+    return sms[dev];
 }
 
 template <int KIND, bool SWIGLU, int CG>
-static int launch_cfg(const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1, const CUtensorMap& mo,
-                      const GemmParams& p, int sms) {
+static int launch_cfg(const CUtensorMap& a, const GemmMaps& maps, GemmParams& p, int sms) {
     auto kern = gemm_kernel<KIND, SWIGLU, CG>;
     constexpr int smem = Plan<CG>::SMEM_BYTES;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    const int tiles = ((p.tiles_m + CG - 1) / CG) * p.tiles_n;
+    int tiles = 0;
+    for (int i = 0; i < p.nparts; i++) {
+        tiles += ((p.tiles_m + CG - 1) / CG) * p.part[i].tiles_n;
+        p.part[i].tile_end = tiles;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.blockDim = dim3(GEMM_THREADS);
     cfg.dynamicSmemBytes = smem;
@@ -942,59 +946,178 @@ static int launch_cfg(const CUtensorMap& a, const CUtensorMap& b0, const CUtenso
         attr[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
         cfg.numAttrs++;
     }
-#ifdef VX_GEMM_PROFILE
-    if (getenv("VX_GEMM_VERBOSE")) fprintf(stderr, "gemm launch: CG=%d units=%d tiles=%d smem=%d\n", CG, units, tiles, smem);
-#endif
-    e = cudaLaunchKernelEx(&cfg, kern, a, b0, b1, mo, p);
+    e = cudaLaunchKernelEx(&cfg, kern, a, maps, p);
     if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
 
+// out_cols / first_row per part: the view's width and the parent row its output column 0 stands for.
 template <int KIND>
-static int launch(bool swiglu, const CUtensorMap& a, const CUtensorMap& b0, const CUtensorMap& b1,
-                  GemmParams& p, long long out_cols, long long first_row) {
-    CUtensorMap mo = a;
-    if (p.out_maps)
-        p.tma_store = 1;   // every tile is stored through the owner's map
-    else
-        make_out_map(&mo, p, out_cols, first_row);
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
+static int launch(bool swiglu, const CUtensorMap& a, GemmMaps& maps, GemmParams& p, const long long* out_cols,
+                  const long long* first_row) {
+    for (int i = 0; i < p.nparts; i++) {
+        maps.out[i] = a;   // a valid map even where none is used
+        if (p.out_maps)
+            p.part[i].tma_store = 1;   // every tile is stored through the owner's map
+        else
+            make_out_map(&maps.out[i], p.m, p.part[i], out_cols[i], first_row[i]);
     }
+    for (int i = p.nparts; i < MAX_PARTS; i++) {
+        maps.b[i] = maps.b[0];
+        maps.out[i] = a;
+    }
+    const int sms = sm_count();
     TimedRegion timed(KIND == KIND_MXF4 ? TIMED_GEMM_FP4 : KIND == KIND_F8 ? TIMED_GEMM_FP8 : TIMED_GEMM_BF16);
     // More than one token tile: CTA pairs (256 tokens per unit, half the W traffic per CTA).
-    const bool pair = p.tiles_m > 1 && !getenv("VELOX_SM100_NO_PAIRS");
-    if (swiglu) return pair ? launch_cfg<KIND, true, 2>(a, b0, b1, mo, p, sms) : launch_cfg<KIND, true, 1>(a, b0, b1, mo, p, sms);
-    return pair ? launch_cfg<KIND, false, 2>(a, b0, b1, mo, p, sms) : launch_cfg<KIND, false, 1>(a, b0, b1, mo, p, sms);
+    const bool pair = p.tiles_m > 1;
+    if (swiglu) return pair ? launch_cfg<KIND, true, 2>(a, maps, p, sms) : launch_cfg<KIND, true, 1>(a, maps, p, sms);
+    return pair ? launch_cfg<KIND, false, 2>(a, maps, p, sms) : launch_cfg<KIND, false, 1>(a, maps, p, sms);
 }
 
-// Device address of the status word, per device ordinal (a __device__ variable has one instance
-// per device).
+// Device addresses of the status word and of the signalling ticket, per device ordinal (a
+// __device__ variable has one instance per device).
+__device__ unsigned int g_gemm_tp_ticket = 0;
+static std::mutex g_sym_mu;
 static int* status_ptr() {
     static int* ptrs[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_sym_mu);
     if (!ptrs[dev] && cudaGetSymbolAddress(reinterpret_cast<void**>(&ptrs[dev]), g_gemm_status) != cudaSuccess) {
         cudaGetLastError();
         return nullptr;
     }
     return ptrs[dev];
 }
-
-#ifdef VX_GEMM_PROFILE
-extern "C" int velox_sm100_debug_profile(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, g_gemm_prof, sizeof(long long) * 160 * 12);
+static unsigned int* ticket_ptr() {
+    static unsigned int* ptrs[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_sym_mu);
+    if (!ptrs[dev] && cudaGetSymbolAddress(reinterpret_cast<void**>(&ptrs[dev]), g_gemm_tp_ticket) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return ptrs[dev];
 }
-#endif
 
 int gemm_status_sync() {
     int v = -1;
     if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
     return v;
+}
+
+int gemm_status_reset() {
+    const int zero = 0;
+    const unsigned int uzero = 0;
+    cudaError_t e = cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_gemm_tp_ticket, &uzero, sizeof(unsigned int));
+    return (int)e;
+}
+
+static void common_params(GemmParams& p, int m) {
+    p.m = m;
+    p.tiles_m = (m + BM - 1) / BM;
+    p.nparts = 1;
+    p.status = status_ptr();
+    p.alpha = 1.0f;
+    p.sync.wait_phase = p.sync.signal_phase = -1;
+    static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
+    p.early = early ? 1 : 0;
+}
+
+// One NVFP4 view (or a gate / up pair) as part `pi` of a block-scaled launch: W geometry on parent
+// row coordinates rounded down to a scale tile, outputs, and the optional NVFP4 producer epilogue.
+static int nvfp4_part(const LinearArgs& a, GemmParams& p, GemmMaps& maps, int pi) {
+    const velox_sm100_view& w = a.w;
+    const bool sw = a.swiglu != 0;
+    const velox_sm100_view& w1 = sw ? a.up : a.w;
+    const long long k = w.k;
+    PartParams& pp = p.part[pi];
+    if (w.format != VELOX_FMT_NVFP4 || w1.format != VELOX_FMT_NVFP4) return VELOX_ERR_UNSUPPORTED;
+    if (sw && (w.row_begin - w1.row_begin) % 128 != 0) return VELOX_ERR_UNSUPPORTED;
+    pp.y = a.y;
+    pp.yb = a.yb;
+    pp.ld = a.ld;
+    pp.col = a.col;
+    const velox_sm100_view* hv[2] = {&w, &w1};
+    for (int h = 0; h < 2; h++) {
+        const velox_sm100_view& v = *hv[h];
+        const long long plane = align256(v.n * k / 2);
+        pp.sfb[h] = v.w + plane;
+        pp.wdiv[h] = reinterpret_cast<const float*>(v.w + plane + v.n * k / 16);
+        pp.b_rows_total[h] = v.n;
+        pp.valid_begin[h] = v.row_begin;
+        pp.valid_end[h] = v.row_begin + v.rows;
+    }
+    const long long base0 = w.row_begin / 128 * 128;
+    if (sw) {
+        pp.b_row0[0] = base0;
+        pp.b_row0[1] = w1.row_begin - (w.row_begin - base0);
+        pp.b_tile_rows = 128;
+        pp.tiles_n = (int)((w.row_begin + w.rows - base0 + 127) / 128);
+    } else {
+        pp.b_row0[0] = base0;
+        pp.b_row0[1] = base0 + 128;
+        pp.b_tile_rows = 256;
+        pp.tiles_n = (int)((w.row_begin + w.rows - base0 + 255) / 256);
+    }
+    pp.out_row0 = w.row_begin;
+    if (a.qo_codes) {
+        // whole 64-column pieces of whole rows of the quantised matrix, starting at column 0
+        if (!a.qo_atoms || !(a.qo_divisor > 0.0f) || a.col != 0 || w.row_begin % 128 != 0 || w.rows % 64 != 0 ||
+            (a.y != nullptr))
+            return VELOX_ERR_UNSUPPORTED;
+        pp.q_codes = a.qo_codes;
+        pp.q_atoms = a.qo_atoms;
+        pp.q_divisor = a.qo_divisor;
+        pp.q_ld = w.rows;
+    }
+    int rc;
+    if (sw) {
+        if ((rc = make_map(&maps.b[0], w.w, false, w.n, k / 2)) != 0) return rc;
+        if ((rc = make_map(&maps.b[1], w1.w, false, w1.n, k / 2)) != 0) return rc;
+    } else {
+        if ((rc = make_map(&maps.b[pi], w.w, false, w.n, k / 2)) != 0) return rc;
+    }
+    return 0;
+}
+
+// Several NVFP4 views of one width reading the same pre-quantised activations, as one launch: the
+// tiles of the views are numbered one view after the other and walked by one persistent grid
+// (Backend::linears, crates/velox-core/src/backend.rs:938-958, for the FP4 activation twins).
+int gemm_linears_q4(const LinearArgs* parts, int n, float divisor, const velox_sm100_tp_sync* sync) {
+    if (!gemm_available() || n < 1 || n > MAX_PARTS) return VELOX_ERR_UNSUPPORTED;
+    const LinearArgs& a0 = parts[0];
+    const long long k = a0.w.k;
+    if (k % 64 != 0 || a0.m < 1 || !a0.q_codes || !a0.q_atoms) return VELOX_ERR_UNSUPPORTED;
+    GemmParams p{};
+    common_params(p, a0.m);
+    if (!p.status) return VELOX_ERR_UNSUPPORTED;
+    p.nparts = n;
+    p.k_steps = (int)(k / 64);
+    p.k_elems_per_block = 128;
+    p.k_tiles64 = (int)(k / 64);
+    p.k_blocks = (p.k_steps + 3) / 4;
+    p.a_k_blocks = p.k_blocks;
+    p.sfa = a0.q_atoms;
+    p.alpha = 1.0f / divisor;
+    int rc = tp_sync_fill(&p.sync, sync, ticket_ptr(), p.status);
+    if (rc != 0) return rc;
+    if (p.sync.signal_phase >= 0) return VELOX_ERR_UNSUPPORTED;   // only the scattering linear signals
+    GemmMaps maps;
+    CUtensorMap ma;
+    long long out_cols[MAX_PARTS], first_row[MAX_PARTS];
+    for (int i = 0; i < n; i++) {
+        const LinearArgs& a = parts[i];
+        if (a.swiglu || a.rs_maps || a.w.k != k || a.m != a0.m || a.q_codes != a0.q_codes || a.q_atoms != a0.q_atoms)
+            return VELOX_ERR_UNSUPPORTED;
+        if ((rc = nvfp4_part(a, p, maps, i)) != 0) return rc;
+        out_cols[i] = a.w.rows;
+        first_row[i] = a.w.row_begin;
+    }
+    if ((rc = make_map(&ma, a0.q_codes, false, a0.m, k / 2)) != 0) return rc;
+    return launch<KIND_MXF4>(false, ma, maps, p, out_cols, first_row);
 }
 
 int gemm_linear(const LinearArgs& a, int act, float divisor) {
@@ -1006,31 +1129,25 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
     const velox_sm100_view& w1 = sw ? a.up : a.w;
 
     GemmParams p{};
-    p.m = a.m;
-    p.tiles_m = (a.m + BM - 1) / BM;
-    p.y = a.y;
-    p.yb = a.yb;
-    p.ld = a.ld;
-    p.col = a.col;
-    p.status = status_ptr();
-    p.alpha = 1.0f;
-    static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
-    p.early = early ? 1 : 0;
-#ifdef VX_GEMM_PROFILE
-    if (const char* e = getenv("VX_GEMM_DBG")) p.dbg = atoi(e);
-#endif
-
+    common_params(p, a.m);
     if (!p.status) return VELOX_ERR_UNSUPPORTED;
+    PartParams& pp = p.part[0];
+    pp.y = a.y;
+    pp.yb = a.yb;
+    pp.ld = a.ld;
+    pp.col = a.col;
 
-    CUtensorMap ma, mb0, mb1;
+    CUtensorMap ma;
+    GemmMaps maps;
     int rc;
+    if ((rc = tp_sync_fill(&p.sync, a.sync, ticket_ptr(), p.status)) != 0) return rc;
+    if (a.sync && act != VELOX_ACT_NVFP4) return VELOX_ERR_UNSUPPORTED;
 
     if (act == VELOX_ACT_NVFP4) {
-        if (w.format != VELOX_FMT_NVFP4) return VELOX_ERR_UNSUPPORTED;
-        if (sw && (w.row_begin - w1.row_begin) % 128 != 0) return VELOX_ERR_UNSUPPORTED;
         const int mp = p.tiles_m * BM;
         const uint8_t* codes = a.q_codes;
         const uint8_t* atoms = a.q_atoms;
+        if ((rc = nvfp4_part(a, p, maps, 0)) != 0) return rc;
         if (!codes || !atoms) {
             // no producer has quantised x already: do it here, into scratch
             uint8_t* c = static_cast<uint8_t*>(scratch(SCRATCH_ACT_CODES, (size_t)a.m * k / 2));
@@ -1046,29 +1163,6 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
         p.k_tiles64 = (int)(k / 64);
         p.sfa = atoms;
         p.alpha = 1.0f / divisor;
-        const velox_sm100_view* hv[2] = {&w, &w1};
-        for (int h = 0; h < 2; h++) {
-            const velox_sm100_view& v = *hv[h];
-            const long long plane = align256(v.n * k / 2);
-            p.sfb[h] = v.w + plane;
-            p.wdiv[h] = reinterpret_cast<const float*>(v.w + plane + v.n * k / 16);
-            p.b_rows_total[h] = v.n;
-            p.valid_begin[h] = v.row_begin;
-            p.valid_end[h] = v.row_begin + v.rows;
-        }
-        const long long base0 = w.row_begin / 128 * 128;
-        if (sw) {
-            p.b_row0[0] = base0;
-            p.b_row0[1] = w1.row_begin - (w.row_begin - base0);
-            p.b_tile_rows = 128;
-            p.tiles_n = (int)((w.row_begin + w.rows - base0 + 127) / 128);
-        } else {
-            p.b_row0[0] = base0;
-            p.b_row0[1] = base0 + 128;
-            p.b_tile_rows = 256;
-            p.tiles_n = (int)((w.row_begin + w.rows - base0 + 255) / 256);
-        }
-        p.out_row0 = w.row_begin;
         if (a.rs_maps) {
             // whole tiles of whole rows into per-owner buffers: nothing ragged
             if (a.y || a.yb || a.qo_codes || a.col != 0 || w.row_begin != 0 || w.rows % 256 != 0 ||
@@ -1076,23 +1170,14 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
                 return VELOX_ERR_UNSUPPORTED;
             p.out_maps = static_cast<const CUtensorMap*>(a.rs_maps);
             p.rows_per_owner = a.rs_rows_per_owner;
-        }
-        if (a.qo_codes) {
-            // whole 64-column pieces of whole rows of the quantised matrix, starting at column 0
-            if (!a.qo_atoms || !(a.qo_divisor > 0.0f) || a.col != 0 || w.row_begin % 128 != 0 || w.rows % 64 != 0 ||
-                (a.y != nullptr))
-                return VELOX_ERR_UNSUPPORTED;
-            p.q_codes = a.qo_codes;
-            p.q_atoms = a.qo_atoms;
-            p.q_divisor = a.qo_divisor;
-            p.q_ld = w.rows;
+        } else if (p.sync.signal_phase >= 0) {
+            return VELOX_ERR_UNSUPPORTED;   // only the scattering linear signals
         }
         if ((rc = make_map(&ma, codes, false, a.m, k / 2)) != 0) return rc;
-        if ((rc = make_map(&mb0, w.w, false, w.n, k / 2)) != 0) return rc;
-        if ((rc = make_map(&mb1, w1.w, false, w1.n, k / 2)) != 0) return rc;
         p.k_blocks = (p.k_steps + 3) / 4;
         p.a_k_blocks = p.k_blocks;
-        return launch<KIND_MXF4>(sw, ma, mb0, mb1, p, w.rows, w.row_begin);
+        const long long oc = w.rows, fr = w.row_begin;
+        return launch<KIND_MXF4>(sw, ma, maps, p, &oc, &fr);
     }
 
     if (act == VELOX_ACT_FP8_ROW) {
@@ -1108,22 +1193,23 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
         const velox_sm100_view* hv[2] = {&w, &w1};
         for (int h = 0; h < 2; h++) {
             const velox_sm100_view& v = *hv[h];
-            p.col_scale[h] = reinterpret_cast<const uint16_t*>(v.w + align256(v.n * k));
-            p.b_rows_total[h] = v.n;
-            p.valid_begin[h] = v.row_begin;
-            p.valid_end[h] = v.row_begin + v.rows;
+            pp.col_scale[h] = reinterpret_cast<const uint16_t*>(v.w + align256(v.n * k));
+            pp.b_rows_total[h] = v.n;
+            pp.valid_begin[h] = v.row_begin;
+            pp.valid_end[h] = v.row_begin + v.rows;
         }
-        p.b_row0[0] = w.row_begin;
-        p.b_row0[1] = sw ? w1.row_begin : w.row_begin + 128;
-        p.b_tile_rows = sw ? 128 : 256;
-        p.tiles_n = (int)((w.rows + p.b_tile_rows - 1) / p.b_tile_rows);
-        p.out_row0 = w.row_begin;
+        pp.b_row0[0] = w.row_begin;
+        pp.b_row0[1] = sw ? w1.row_begin : w.row_begin + 128;
+        pp.b_tile_rows = sw ? 128 : 256;
+        pp.tiles_n = (int)((w.rows + pp.b_tile_rows - 1) / pp.b_tile_rows);
+        pp.out_row0 = w.row_begin;
         if ((rc = make_map(&ma, codes, false, a.m, k)) != 0) return rc;
-        if ((rc = make_map(&mb0, w.w, false, w.n, k)) != 0) return rc;
-        if ((rc = make_map(&mb1, w1.w, false, w1.n, k)) != 0) return rc;
+        if ((rc = make_map(&maps.b[0], w.w, false, w.n, k)) != 0) return rc;
+        if ((rc = make_map(&maps.b[1], w1.w, false, w1.n, k)) != 0) return rc;
         p.k_blocks = (p.k_steps + 3) / 4;
         p.a_k_blocks = p.k_blocks;
-        return launch<KIND_F8>(sw, ma, mb0, mb1, p, w.rows, 0);
+        const long long oc = w.rows, fr = 0;
+        return launch<KIND_F8>(sw, ma, maps, p, &oc, &fr);
     }
 
     if (act != VELOX_ACT_BF16) return VELOX_ERR_UNSUPPORTED;
@@ -1156,23 +1242,24 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
     for (int h = 0; h < 2; h++) {
         const velox_sm100_view& v = *hv[h];
         if (v.format == VELOX_FMT_NVFP4)
-            p.wdiv[h] = reinterpret_cast<const float*>(v.w + align256(v.n * k / 2) + v.n * k / 16);
+            pp.wdiv[h] = reinterpret_cast<const float*>(v.w + align256(v.n * k / 2) + v.n * k / 16);
         if (v.format == VELOX_FMT_FP8_ROW_BF16)
-            p.col_scale[h] = reinterpret_cast<const uint16_t*>(v.w + align256(v.n * k)) + v.row_begin;
-        p.b_rows_total[h] = v.rows;
-        p.valid_begin[h] = 0;
-        p.valid_end[h] = v.rows;
+            pp.col_scale[h] = reinterpret_cast<const uint16_t*>(v.w + align256(v.n * k)) + v.row_begin;
+        pp.b_rows_total[h] = v.rows;
+        pp.valid_begin[h] = 0;
+        pp.valid_end[h] = v.rows;
     }
-    p.b_row0[0] = 0;
-    p.b_row0[1] = sw ? 0 : 128;
-    p.b_tile_rows = sw ? 128 : 256;
-    p.tiles_n = (int)((w.rows + p.b_tile_rows - 1) / p.b_tile_rows);
-    p.out_row0 = 0;
+    pp.b_row0[0] = 0;
+    pp.b_row0[1] = sw ? 0 : 128;
+    pp.b_tile_rows = sw ? 128 : 256;
+    pp.tiles_n = (int)((w.rows + pp.b_tile_rows - 1) / pp.b_tile_rows);
+    pp.out_row0 = 0;
     if ((rc = make_map(&ma, xb, true, a.m, k)) != 0) return rc;
-    if ((rc = make_map(&mb0, wq, true, w.rows, kw)) != 0) return rc;
-    if ((rc = make_map(&mb1, sw ? wq + (size_t)w.rows * kw : wq, true, w.rows, kw)) != 0) return rc;
+    if ((rc = make_map(&maps.b[0], wq, true, w.rows, kw)) != 0) return rc;
+    if ((rc = make_map(&maps.b[1], sw ? wq + (size_t)w.rows * kw : wq, true, w.rows, kw)) != 0) return rc;
     p.k_blocks = (p.k_steps + 3) / 4;
-    return launch<KIND_BF16>(sw, ma, mb0, mb1, p, w.rows, 0);
+    const long long oc = w.rows, fr = 0;
+    return launch<KIND_BF16>(sw, ma, maps, p, &oc, &fr);
 }
 
 }  // namespace vx
@@ -1245,11 +1332,9 @@ extern "C" int velox_sm100_linear_nvfp4_a4_static(const uint16_t* xb, const velo
     GemmParams p{};
     p.m = m;
     p.tiles_m = tiles_m;
-    p.y = y;
-    p.yb = yb;
-    p.ld = w.rows;
-    p.col = 0;
+    p.nparts = 1;
     p.status = status;
+    p.sync.wait_phase = p.sync.signal_phase = -1;
     p.k_steps = (int)(k / 64);
     p.k_blocks = (p.k_steps + 3) / 4;
     p.a_k_blocks = p.k_blocks;
@@ -1257,32 +1342,30 @@ extern "C" int velox_sm100_linear_nvfp4_a4_static(const uint16_t* xb, const velo
     p.k_tiles64 = (int)(k / 64);
     p.sfa = atoms;
     p.alpha = 1.0f / w.divisor;
-    const long long plane = align256(w.n * k / 2);
-    const long long base0 = w.row_begin / 128 * 128;
-    for (int h = 0; h < 2; h++) {
-        p.sfb[h] = w.w + plane;
-        p.wdiv[h] = reinterpret_cast<const float*>(w.w + plane + w.n * k / 16);
-        p.b_rows_total[h] = w.n;
-        p.valid_begin[h] = w.row_begin;
-        p.valid_end[h] = w.row_begin + w.rows;
-    }
-    p.b_row0[0] = base0;
-    p.b_row0[1] = base0 + 128;
-    p.b_tile_rows = 256;
-    p.tiles_n = (int)((w.row_begin + w.rows - base0 + 255) / 256);
-    p.out_row0 = w.row_begin;
-    CUtensorMap ma, mb, mo;
+    LinearArgs a{};
+    a.w = w;
+    a.m = m;
+    a.y = y;
+    a.yb = yb;
+    a.ld = w.rows;
+    a.col = 0;
+    GemmMaps maps;
+    CUtensorMap ma;
+    if ((rc = nvfp4_part(a, p, maps, 0)) != 0) return rc;
     if ((rc = make_map(&ma, codes, false, m, k / 2)) != 0) return rc;
-    if ((rc = make_map(&mb, w.w, false, w.n, k / 2)) != 0) return rc;
-    mo = ma;
-    make_out_map(&mo, p, w.rows, w.row_begin);
+    for (int i = 0; i < MAX_PARTS; i++) {
+        maps.b[i] = maps.b[0];
+        maps.out[i] = ma;
+    }
+    make_out_map(&maps.out[0], m, p.part[0], w.rows, w.row_begin);
     int sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (sms <= 0) sms = 148;
-    const int tiles = p.tiles_m * p.tiles_n;
+    const int tiles = p.tiles_m * p.part[0].tiles_n;
+    p.part[0].tile_end = tiles;
     auto kern = gemm_kernel<KIND_MXF4, false, 1>;
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Plan<1>::SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    kern<<<tiles < sms ? tiles : sms, GEMM_THREADS, Plan<1>::SMEM_BYTES, stream()>>>(ma, mb, mb, mo, p);
+    kern<<<tiles < sms ? tiles : sms, GEMM_THREADS, Plan<1>::SMEM_BYTES, stream()>>>(ma, maps, p);
     return launch_status();
 }

@@ -16,6 +16,10 @@ bool gemm_available();
 // SwiGLU form. Returns VELOX_ERR_UNSUPPORTED for shapes it does not take.
 int gemm_linear(const LinearArgs& a, int act, float divisor);
 
+// Up to three NVFP4 views of one width that read the same pre-quantised activations (a.q_codes /
+// a.q_atoms), as one launch. `sync` (may be NULL): tensor-parallel flags to wait for.
+int gemm_linears_q4(const LinearArgs* parts, int n, float divisor, const velox_sm100_tp_sync* sync);
+
 // 2-D tensor map over a row-major byte matrix [rows, row_bytes]: boxes of 128 bytes x box_rows rows,
 // 128-byte swizzle.
 int gemm_make_map_u8(CUtensorMap* map, const void* ptr, long long rows, long long row_bytes, int box_rows);
@@ -32,5 +36,7 @@ int gemv_nvfp4_tc_parts(const LinearArgs* parts, int n, float divisor);
 // Synchronises the device and returns the tensor-core kernels' status word: 0, or the code of the
 // first bounded wait that gave up.
 int gemm_status_sync();
+// Clears it (and the words that elect a launch's last CTA), after a synchronise by the caller.
+int gemm_status_reset();
 
 }  // namespace vx

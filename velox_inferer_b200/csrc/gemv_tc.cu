@@ -30,6 +30,7 @@
 //
 // Reference counterpart: linear_gemv_vec_kernel, crates/velox-cuda/kernels/portable_model.cu:1448-1626.
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 #include "gemm.cuh"
@@ -96,9 +97,6 @@ struct DtParams {
     float* partial;              // [CTAs][2][V][NT/16][128][16]: a CTA's first and last run can be partial tiles
     int* tickets;                // [tiles], zero between launches
     int* status;
-#ifdef VX_GEMM_PROFILE
-    int dbg;   // development only: 1 no result stores, 2 no fix-up loads, 8 no partial stores (4: host, one x row)
-#endif
 };
 
 __device__ int g_gemv_tc_status = 0;
@@ -447,9 +445,6 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
 #pragma unroll
                     for (int v = 0; v < V; v++) tc_ld16(taddr + v * NT + c * 16, r[v]);
                     tc_wait_ld();
-#ifdef VX_GEMM_PROFILE
-                    if (p.dbg & 8) continue;
-#endif
 #pragma unroll
                     for (int v = 0; v < V; v++) {
                         uint4* dstp = reinterpret_cast<uint4*>(mine + (((size_t)v * NC + c) * 128 + row_in_tile) * 16);
@@ -503,9 +498,6 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                     constexpr int B = V == 1 ? 4 : 2;
 #pragma unroll 1
                     for (int cta0 = c_first; cta0 <= c_last; cta0 += B) {
-#ifdef VX_GEMM_PROFILE
-                        if (p.dbg & 2) break;
-#endif
                         float4 t[B][V][4];
 #pragma unroll
                         for (int b = 0; b < B; b++) {
@@ -536,9 +528,6 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                     }
                 }
                 const int ntok = p.m - c * 16 < 16 ? p.m - c * 16 : 16;   // uniform across the warp
-#ifdef VX_GEMM_PROFILE
-                if (p.dbg & 1) continue;
-#endif
                 // Four tokens per pass of a rolled loop: a lone warp issues a dependent instruction
                 // every few cycles, so the body is kept short and its four tokens independent.
                 const long long tok0 = (long long)(c * 16) * old + o0;
@@ -600,21 +589,25 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
 
 // ---- host side ----
 
+static std::mutex g_gemv_tc_mu;
 static int* gemv_tc_status_ptr() {
     static int* ptrs[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_gemv_tc_mu);
     if (!ptrs[dev]) cudaGetSymbolAddress(reinterpret_cast<void**>(&ptrs[dev]), g_gemv_tc_status);
     return ptrs[dev];
 }
 
 // Arrival counters of the K-split fix-up: zeroed when (re)allocated, returned to zero by the kernel.
+// One array per device, shared by every launch: launches on a device must be stream-ordered.
+static int* g_gemv_tc_ticket_ptrs[64] = {};
+static size_t g_gemv_tc_ticket_caps[64] = {};
 static int* gemv_tc_tickets(size_t count) {
-    static int* ptrs[64] = {};
-    static size_t caps[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (count > caps[dev]) {
+    std::lock_guard<std::mutex> lock(g_gemv_tc_mu);
+    if (count > g_gemv_tc_ticket_caps[dev]) {
         const size_t n = count < 4096 ? 4096 : count * 2;
         int* q = nullptr;
         if (cudaMalloc(&q, n * sizeof(int)) != cudaSuccess) {
@@ -622,10 +615,24 @@ static int* gemv_tc_tickets(size_t count) {
             return nullptr;
         }
         if (cudaMemsetAsync(q, 0, n * sizeof(int), stream()) != cudaSuccess) return nullptr;
-        ptrs[dev] = q;   // the old block stays allocated: queued work may still use it
-        caps[dev] = n;
+        g_gemv_tc_ticket_ptrs[dev] = q;   // the old block stays allocated: queued work may still use it
+        g_gemv_tc_ticket_caps[dev] = n;
     }
-    return ptrs[dev];
+    return g_gemv_tc_ticket_ptrs[dev];
+}
+
+// Clears the status word and the arrival counters (a launch that gave up leaves them non-zero).
+// The caller has synchronised the device.
+int gemv_tc_status_reset() {
+    const int zero = 0;
+    cudaError_t e = cudaMemcpyToSymbol(g_gemv_tc_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    std::lock_guard<std::mutex> lock(g_gemv_tc_mu);
+    if (g_gemv_tc_ticket_ptrs[dev])
+        e = cudaMemset(g_gemv_tc_ticket_ptrs[dev], 0, g_gemv_tc_ticket_caps[dev] * sizeof(int));
+    return (int)e;
 }
 
 int gemv_tc_status_sync() {
@@ -734,12 +741,7 @@ int gemv_tc_parts(const LinearArgs* parts, int n, int act, float divisor) {
         for (int i = n; i < DT_MAX_PARTS; i++) mw[i] = mw[0];
         p.nparts = n;
     }
-#ifdef VX_GEMM_PROFILE
-    p.dbg = getenv("VX_DT_DBG") ? atoi(getenv("VX_DT_DBG")) : 0;
-    if ((rc = gemm_make_map_u8(&mx, codes, (p.dbg & 4) ? 1 : a.m, row_bytes, nt)) != 0) return rc;
-#else
     if ((rc = gemm_make_map_u8(&mx, codes, a.m, row_bytes, nt)) != 0) return rc;
-#endif
 
     static int sms = 0;
     if (sms == 0) {

@@ -25,6 +25,7 @@
 //
 // Reference counterpart: linear_gemv_vec_kernel, crates/velox-cuda/kernels/portable_model.cu:1448-1626.
 #include <cstdlib>
+#include <mutex>
 
 #include <cuda.h>
 #include <cuda_fp4.h>
@@ -60,7 +61,6 @@ struct TmaGemvParams {
     float* partial;        // [items][V][64 rows][NT*8] partial sums when splits > 1
     int* tickets;          // [units] arrival counters, zero between launches
     int* status;
-    int dbg;   // profiling builds only: 1 no arithmetic, 2 no mma, 4 no unpack
 };
 
 __device__ int g_gemv_status = 0;
@@ -329,11 +329,7 @@ gemv_nvfp4_tma_kernel(const __grid_constant__ CUtensorMap map_codes0, const __gr
 #pragma unroll
                     for (int sp = 0; sp < 2; sp++) {
                         const long long k0 = (long long)ks * 256 + sp * 128;   // this step
-#ifdef VX_GEMM_PROFILE
-                        if (k0 >= k || (p.dbg & 1)) continue;
-#else
                         if (k0 >= k) continue;
-#endif
                         const int piece = sp * 4 + t;
                         // rows of the box: band (0 = lo, 1 = hi) * 32 + chunk row 8 warp + rho
                         uint4 codes[2];
@@ -523,32 +519,50 @@ static int launch_tma_gemv(const CUtensorMap (&maps)[2], const TmaGemvParams& p)
     return launch_status();
 }
 
+static std::mutex g_gemv_mu;
 static int* gemv_status_ptr() {
     static int* ptrs[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_gemv_mu);
     if (!ptrs[dev]) cudaGetSymbolAddress(reinterpret_cast<void**>(&ptrs[dev]), g_gemv_status);
     return ptrs[dev];
 }
 
 // Arrival counters of the K-split fix-up: zeroed when (re)allocated, returned to zero by the kernel.
+// One array per device, shared by every launch: launches on a device must be stream-ordered.
+static int* g_gemv_ticket_ptrs[64] = {};
+static size_t g_gemv_ticket_caps[64] = {};
 static int* gemv_tickets(size_t count) {
-    static int* ptrs[64] = {};
-    static size_t caps[64] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    if (count > caps[dev]) {
-        size_t n = count < 4096 ? 4096 : count * 2;
+    std::lock_guard<std::mutex> lock(g_gemv_mu);
+    if (count > g_gemv_ticket_caps[dev]) {
+        const size_t n = count < 4096 ? 4096 : count * 2;
         int* q = nullptr;
         if (cudaMalloc(&q, n * sizeof(int)) != cudaSuccess) {
             cudaGetLastError();
             return nullptr;
         }
         if (cudaMemsetAsync(q, 0, n * sizeof(int), stream()) != cudaSuccess) return nullptr;
-        ptrs[dev] = q;   // the old block stays allocated: queued work may still use it
-        caps[dev] = n;
+        g_gemv_ticket_ptrs[dev] = q;   // the old block stays allocated: queued work may still use it
+        g_gemv_ticket_caps[dev] = n;
     }
-    return ptrs[dev];
+    return g_gemv_ticket_ptrs[dev];
+}
+
+// Clears the status word and the arrival counters (a launch that gave up leaves them non-zero).
+// The caller has synchronised the device.
+int gemv_status_reset() {
+    const int zero = 0;
+    cudaError_t e = cudaMemcpyToSymbol(g_gemv_status, &zero, sizeof(int));
+    if (e != cudaSuccess) return (int)e;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    std::lock_guard<std::mutex> lock(g_gemv_mu);
+    if (g_gemv_ticket_ptrs[dev])
+        e = cudaMemset(g_gemv_ticket_ptrs[dev], 0, g_gemv_ticket_caps[dev] * sizeof(int));
+    return (int)e;
 }
 
 int gemv_status_sync() {
@@ -600,9 +614,6 @@ int gemv_nvfp4_tma(const LinearArgs& a) {
         }
     }
     p.status = gemv_status_ptr();
-#ifdef VX_GEMM_PROFILE
-    if (const char* e = getenv("VX_GEMV_DBG")) p.dbg = atoi(e);
-#endif
     if (!p.status) return VELOX_ERR_UNSUPPORTED;
     if (a.m <= 8) return a.swiglu ? launch_tma_gemv<1, true>(maps, p) : launch_tma_gemv<1, false>(maps, p);
     return a.swiglu ? launch_tma_gemv<2, true>(maps, p) : launch_tma_gemv<2, false>(maps, p);

@@ -27,6 +27,7 @@ struct LinearArgs {
     int rs_rows_per_owner;   // the token rows each owner holds; replaces y / yb
     long long ld;            // row stride of y / yb in elements
     long long col;           // first column written
+    const velox_sm100_tp_sync* sync;  // optional (tensor parallel): flags to wait for / to raise
 };
 
 int dequant_rows_f32(const velox_sm100_view* v, float* out);
@@ -41,7 +42,10 @@ int gemv_nvfp4_mma(const LinearArgs& a);
 int gemv_nvfp4_tma(const LinearArgs& a);
 int gemv_status_sync();
 int gemv_tc_status_sync();
-int gemv_tc_status_sync();
+int gemv_status_reset();
+int gemv_tc_status_reset();
+int tp_status_sync();
+int tp_status_reset();
 // Any shape, any m: one warp per output row, per-element decode. Slow but total.
 int linear_generic(const LinearArgs& a);
 
@@ -65,9 +69,9 @@ int bf16_twin(const float* x, uint16_t* xb, long long len);
 int gemv_q4k_mma(const LinearArgs& a);
 int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
                uint8_t* const* codes, uint8_t* const* atoms, int ndst, long long row0, int rows, int dim, float eps,
-               int offset, float divisor);
+               int offset, float divisor, const velox_sm100_tp_sync* sync);
 int sp_finish(float* acc, const uint16_t* slots, int nslots, long long slot_stride, uint16_t* const* out, int ndst,
-              long long row0, int rows, int dim);
+              long long row0, int rows, int dim, const velox_sm100_tp_sync* sync);
 int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float* weight, uint16_t* yb,
                     uint8_t* codes, uint8_t* atoms, int rows, int dim, float eps, int offset, float divisor);
 

@@ -97,25 +97,66 @@ def slice_k_nvfp4(payload: torch.Tensor, n: int, k: int, k_begin: int, k_len: in
     return out
 
 
+def fused_step_schedule(layers: int):
+    """The launches of one fused tensor-parallel step in stream order, each with the flag row it
+    waits on and the flag row it raises (-1: none): ``(op, layer, wait, signal)``.
+
+    Rows per layer: 4l norm -> q|k|v ("blob rows written"), 4l+1 o -> norm ("partial sums landed"),
+    4l+2 norm -> gate|up, 4l+3 down -> next norm; row 4*layers: finish -> end of step ("output rows
+    written"). Every buffer another rank writes is protected in both directions by these waits: a
+    norm overwrites the blob on all ranks only after each rank's row-split linear (which follows
+    that rank's readers of the blob in its stream) has signalled, and a row-split linear
+    overwrites the slots only after the norm that read them has signalled through the blob row."""
+    P = TpFabric.PHASES_PER_LAYER
+    ops = []
+    for li in range(layers):
+        p0 = P * li
+        ops.append(("norm", li, p0 - 1 if li > 0 else -1, p0))
+        ops.append(("qkv", li, p0, -1))
+        ops.append(("o_scatter", li, -1, p0 + 1))
+        ops.append(("norm", li, p0 + 1, p0 + 2))
+        ops.append(("gate_up", li, p0 + 2, -1))
+        ops.append(("down_scatter", li, -1, p0 + 3))
+    last = P * layers
+    ops.append(("finish", layers, last - 1, last))
+    ops.append(("wait", layers, last, -1))
+    return ops
+
+
 class TpFabric:
     """Symmetric memory of a tensor-parallel group for the fused scatter / gather path: on every
     rank, one slot per source rank for bf16 partial sums of the rows this rank owns, the norm's
-    NVFP4 blob for all rows, and the final output. Peers' copies are mapped into this process
-    (torch symmetric memory: cuMem allocations exchanged once at set-up), so kernels store into
-    them with ordinary addresses; phases are separated by signal-pad barriers on the stream."""
+    NVFP4 blob for all rows, the final output, and a table of flags. Peers' copies are mapped into
+    this process (torch symmetric memory: cuMem allocations exchanged once at set-up), so kernels
+    store into them with ordinary addresses.
 
-    def __init__(self, backend: Sm100Backend, group, rank: int, world: int, m: int, hidden: int):
+    Ordering between ranks: every kernel that writes into other ranks' memory raises a flag there
+    when it is done, every kernel that reads such data polls its own flags first (bounded waits,
+    include/velox_sm100.h). ``sync_mode="barrier"`` uses signal-pad barrier kernels between the
+    phases instead (the form the flags replaced; kept for comparison)."""
+
+    PHASES_PER_LAYER = 4    # norm -> q|k|v, o -> norm, norm -> gate|up, down -> norm
+
+    def __init__(self, backend: Sm100Backend, group, rank: int, world: int, m: int, hidden: int, layers: int,
+                 sync_mode: str = "flags"):
         import torch.distributed._symmetric_memory as symm
 
-        assert m % (world * 128) == 0
+        from . import _lib
+
+        assert m % (world * 128) == 0 and world <= 8
+        assert sync_mode in ("flags", "barrier")
         self.rank, self.world, self.m, self.hidden = rank, world, m, hidden
+        self.sync_mode = sync_mode
         self.rows = m // world                               # token rows each rank owns
+        self.phases = self.PHASES_PER_LAYER * layers + 1     # + "output rows written"
         slots_b, codes_b = world * self.rows * hidden * 2, m * hidden // 2
         atoms_b, out_b = m * hidden // 16, m * hidden * 2
+        flags_b = self.phases * 8 * 4
         self.off_slots, self.off_codes = 0, align256(slots_b)
         self.off_atoms = self.off_codes + align256(codes_b)
         self.off_out = self.off_atoms + align256(atoms_b)
-        total = self.off_out + align256(out_b)
+        self.off_flags = self.off_out + align256(out_b)
+        total = self.off_flags + align256(flags_b)
         self.buf = symm.empty(total, dtype=torch.uint8, device=backend.device)
         self.buf.zero_()
         self.hdl = symm.rendezvous(self.buf, group)
@@ -126,19 +167,41 @@ class TpFabric:
         self.codes_ptrs = [p + self.off_codes for p in base]
         self.atoms_ptrs = [p + self.off_atoms for p in base]
         self.out_ptrs = [p + self.off_out for p in base]
+        self.flag_ptrs = [p + self.off_flags for p in base]
         # this rank's slot in every owner's memory
         self.slot_ptrs = [p + self.off_slots + rank * self.rows * hidden * 2 for p in base]
         self.slots = self.buf[self.off_slots:self.off_slots + slots_b].view(torch.bfloat16)
         self.codes = self.buf[self.off_codes:self.off_codes + codes_b]
         self.atoms = self.buf[self.off_atoms:self.off_atoms + atoms_b]
         self.out = self.buf[self.off_out:self.off_out + out_b].view(torch.bfloat16)
+        self.flags = self.buf[self.off_flags:self.off_flags + flags_b].view(torch.int32)
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=backend.device)   # this rank's step counter
         self.maps = torch.zeros(world * 128, dtype=torch.uint8, device=backend.device)
         backend.tp_make_maps(self.maps, self.slot_ptrs, self.rows, hidden)
+        self._lib = _lib
+        self._syncs = {}
         torch.cuda.synchronize()
         self.hdl.barrier(channel=0)
+        torch.cuda.synchronize()
+
+    def sync(self, wait: int = -1, signal: int = -1):
+        """The flags of one launch (row to wait on, row to raise; -1 none); None in barrier mode."""
+        if self.sync_mode != "flags":
+            return None
+        key = (wait, signal)
+        if key not in self._syncs:
+            t = self._lib.TpSync()
+            for i, p in enumerate(self.flag_ptrs):
+                t.flag_tables[i] = p
+            t.epoch = self.epoch.data_ptr()
+            t.n, t.rank, t.wait_phase, t.signal_phase = self.world, self.rank, wait, signal
+            self._syncs[key] = t
+        return self._syncs[key]
 
     def barrier(self) -> None:
-        self.hdl.barrier(channel=0)
+        """Barrier mode only: a signal-pad barrier kernel on the stream."""
+        if self.sync_mode == "barrier":
+            self.hdl.barrier(channel=0)
 
 
 @dataclass
@@ -206,9 +269,6 @@ class LinearStack:
         self.qq = backend.q4_blob(m, s.q_dim // world)                  # q projection as NVFP4 (o's input)
         self.gq = backend.q4_blob(m, s.intermediate // world)           # silu(gate)*up as NVFP4 (down's input)
         self.fabric: Optional[TpFabric] = None
-        self.kv_side_streams = True
-        self._side = None
-        self._kv_pending: list = []
         self.weight_bytes = sum(v.buf.numel() for l in self.layers
                                 for v in (l.q, l.k, l.v, l.o, l.gate, l.up, l.down))
 
@@ -216,78 +276,113 @@ class LinearStack:
         if self.world > 1:
             torch.distributed.all_reduce(t, group=self.group)
 
-    # -- q, k, v of one input. At decode sizes they are one launch. At prefill sizes k and v go to
-    #    side streams: when a rank's projections are small (tensor parallel shards) the three
-    #    persistent GEMMs fit on the SMs side by side instead of queueing behind one another.
-    def _qkv(self, l: LayerWeights, hq, m: int, emit: bool) -> None:
+    # -- q, k, v of one input: one launch at every width (the streaming kernel at decode sizes, one
+    #    persistent GEMM grid over the tiles of all three views at prefill sizes).
+    def _qkv(self, l: LayerWeights, hq, m: int, emit: bool, sync=None) -> None:
         b = self.b
         qpart = (l.q, None, self.qq, DIV_O_IN) if emit else (l.q, self.qb, None, 0.0)
-        if m <= 16 or not self.kv_side_streams:
-            b.linears_q4(hq, DIV_NORM_OUT, [qpart, (l.k, self.kb, None, 0.0), (l.v, self.vb, None, 0.0)], m)
-            return
-        if self._side is None:
-            self._side = [torch.cuda.Stream(device=b.device), torch.cuda.Stream(device=b.device)]
-        main = torch.cuda.current_stream()
-        ready = torch.cuda.Event()
-        ready.record(main)
-        b.linears_q4(hq, DIV_NORM_OUT, [qpart], m)
-        for side, (w, yb) in zip(self._side, ((l.k, self.kb), (l.v, self.vb))):
-            side.wait_event(ready)
-            with torch.cuda.stream(side):
-                b.linears_q4(hq, DIV_NORM_OUT, [(w, yb, None, 0.0)], m)
-                done = torch.cuda.Event()
-                done.record(side)
-            self._kv_pending.append(done)
+        parts = [qpart, (l.k, self.kb, None, 0.0), (l.v, self.vb, None, 0.0)]
+        if sync is not None:
+            b.tp_linears_q4(hq, DIV_NORM_OUT, parts, m, sync)
+        else:
+            b.linears_q4(hq, DIV_NORM_OUT, parts, m)
 
-    def _join_kv(self) -> None:
-        """k and v read the norm's blob: they must be done before it is written again."""
-        main = torch.cuda.current_stream()
-        for ev in self._kv_pending:
-            main.wait_event(ev)
-        self._kv_pending.clear()
-
-    def enable_fused_tp(self, m: int) -> bool:
+    def enable_fused_tp(self, m: int, sync_mode: str = "flags") -> bool:
         """Set up the symmetric buffers of the fused scatter / gather path for steps of m tokens.
         False (and nothing changed) where it does not apply."""
         if self.world == 1 or not self.a4 or m <= 16 or m % (self.world * 128) != 0 or m > self.max_tokens:
             return False
         self.fabric = TpFabric(self.b, self.group if self.group is not None else torch.distributed.group.WORLD,
-                               self.rank, self.world, m, self.spec.hidden)
+                               self.rank, self.world, m, self.spec.hidden, self.spec.layers, sync_mode)
         return True
 
-    def forward_fused_tp(self, xb_in: torch.Tensor) -> torch.Tensor:
+    def forward_fused_tp(self, xb_in: torch.Tensor, own_rows_only: bool = False) -> torch.Tensor:
         """The step with communication fused into the kernels on either side of it. Token rows
         are owned by ranks in equal blocks. o and down store their bf16 partial tiles straight into
-        the owning rank's slots (GEMM epilogue, TMA stores over NVLink); the norm adds the slots to
-        its own rows of the f32 residual, normalises them, and writes the NVFP4 result into every
-        rank's blob. Four stream barriers per layer keep the phases apart."""
+        the owning rank's slots (GEMM epilogue, TMA stores over NVLink) and raise a flag there; the
+        norm waits for the flags, adds the slots to its own rows of the f32 residual, normalises
+        them, writes the NVFP4 result into every rank's blob and raises the flag the next linears
+        wait for. ``xb_in`` is [m, hidden] bf16, or with ``own_rows_only`` just this rank's
+        [m / world, hidden] rows of it (all the step reads)."""
         b, s, f = self.b, self.spec, self.fabric
         h, m, rows, world = s.hidden, f.m, f.rows, self.world
         r0 = self.rank * rows
         launches0 = b.launch_count()
         x_own = self.x[: rows * h]
-        x_own.copy_(xb_in.reshape(-1)[r0 * h:(r0 + rows) * h])
+        src = xb_in.reshape(-1)
+        x_own.copy_(src[: rows * h] if own_rows_only else src[r0 * h:(r0 + rows) * h])
         hq = (f.codes, f.atoms)
+        flags = f.sync_mode == "flags"
+        if flags:
+            b.tp_step_begin(f.epoch)
         nslots = 0
-        for l in self.layers:
-            b.tp_norm_q4(x_own, f.slots, nslots, rows * h, self.norm_w, f.codes_ptrs, f.atoms_ptrs, r0, rows, h,
-                         s.norm_eps, DIV_NORM_OUT)
-            nslots = world
-            f.barrier()                                   # every rank's rows of the blob are in place
-            self._qkv(l, hq, m, True)
-            b.tp_linear_q4_scatter(self.qq, DIV_O_IN, l.o, m, f.maps, rows)
-            self._join_kv()
-            f.barrier()                                   # all partial sums of o have landed
-            b.tp_norm_q4(x_own, f.slots, world, rows * h, self.norm_w, f.codes_ptrs, f.atoms_ptrs, r0, rows, h,
-                         s.norm_eps, DIV_NORM_OUT)
-            f.barrier()
-            b.linear_swiglu_q4_to_q4(hq, DIV_NORM_OUT, l.gate, l.up, m, self.gq, DIV_DOWN_IN)
-            b.tp_linear_q4_scatter(self.gq, DIV_DOWN_IN, l.down, m, f.maps, rows)
-            f.barrier()
-        b.tp_finish(x_own, f.slots, world, rows * h, f.out_ptrs, r0, rows, h)
-        f.barrier()
+        for op, li, wait, signal in fused_step_schedule(len(self.layers)):
+            sync = f.sync(wait, signal)
+            l = self.layers[li] if li < len(self.layers) else None
+            if op == "norm":
+                b.tp_norm_q4(x_own, f.slots, nslots, rows * h, self.norm_w, f.codes_ptrs, f.atoms_ptrs, r0, rows, h,
+                             s.norm_eps, DIV_NORM_OUT, sync=sync)
+                nslots = world
+                f.barrier()                               # (barrier mode) every rank's rows of the blob are in place
+            elif op == "qkv":
+                self._qkv(l, hq, m, True, sync=sync)
+            elif op == "gate_up":
+                if flags:
+                    b.tp_linear_swiglu_q4_to_q4(hq, DIV_NORM_OUT, l.gate, l.up, m, self.gq, DIV_DOWN_IN, sync=sync)
+                else:
+                    b.linear_swiglu_q4_to_q4(hq, DIV_NORM_OUT, l.gate, l.up, m, self.gq, DIV_DOWN_IN)
+            elif op == "o_scatter":
+                b.tp_linear_q4_scatter(self.qq, DIV_O_IN, l.o, m, f.maps, rows, sync=sync)
+                f.barrier()                               # (barrier mode) all partial sums of o have landed
+            elif op == "down_scatter":
+                b.tp_linear_q4_scatter(self.gq, DIV_DOWN_IN, l.down, m, f.maps, rows, sync=sync)
+                f.barrier()
+            elif op == "finish":
+                b.tp_finish(x_own, f.slots, world, rows * h, f.out_ptrs, r0, rows, h, sync=sync)
+                f.barrier()
+            elif op == "wait" and flags:
+                b.tp_wait(sync)                           # every rank's rows of the output are in place
         self.launches_per_step = b.launch_count() - launches0
         return f.out
+
+    def forward_gathered(self, xb_in: torch.Tensor, m: int) -> torch.Tensor:
+        """The sharded step with library collectives only and the fused step's arithmetic: after
+        each row-split projection the ranks' bf16 partial sums are all-gathered and added in rank
+        order in f32 (what the fused norm does with its slots) to a replicated residual, so every
+        value equals ``forward_fused_tp``'s bit for bit. The checker of the fused step, and the step
+        to use where symmetric memory is not available."""
+        b, s = self.b, self.spec
+        h, world = s.hidden, self.world
+        assert self.a4 and 16 < m <= self.max_tokens
+        self.x[: m * h].copy_(xb_in.reshape(-1)[: m * h])
+        if not hasattr(self, "_gather"):
+            self._gather = torch.zeros(world, self.max_tokens * h, dtype=torch.bfloat16, device=b.device)
+            self._part = torch.zeros(self.max_tokens * h, dtype=torch.float32, device=b.device)
+
+        def summed():
+            """sum over ranks, in rank order, of the bf16 partial sums in pb"""
+            if world > 1:
+                torch.distributed.all_gather_into_tensor(self._gather.view(-1), self.pb, group=self.group)
+            else:
+                self._gather[0].copy_(self.pb)
+            part = self._part
+            part.copy_(self._gather[0])
+            for r in range(1, world):
+                part += self._gather[r]
+            return part
+
+        part = None
+        for l in self.layers:
+            b.add_rms_norm_q4(self.x, part, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT)
+            self._qkv(l, self.hq, m, True)
+            b.linear_q4(self.qq, DIV_O_IN, l.o, None, m, yb=self.pb)
+            part = summed()
+            b.add_rms_norm_q4(self.x, part, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT)
+            b.linear_swiglu_q4_to_q4(self.hq, DIV_NORM_OUT, l.gate, l.up, m, self.gq, DIV_DOWN_IN)
+            b.linear_q4(self.gq, DIV_DOWN_IN, l.down, None, m, yb=self.pb)
+            part = summed()
+        b.add(self.x, part, m * h)
+        return b.bf16_twin_into(self.x, self.outb, m * h)
 
     def forward(self, xb_in: torch.Tensor, m: int) -> torch.Tensor:
         """One step over m tokens: xb_in is bf16 [m, hidden] on the device; returns the final
@@ -321,7 +416,6 @@ class LinearStack:
             else:
                 b.linear_bf16(self.qb, l.o, None, m, yb=self.pb)   # attention passthrough: a = q
             self._all_reduce(self.pb[: m * h])
-            self._join_kv()
             if q4:
                 b.add_rms_norm_q4(self.x, None, self.norm_w, None, self.hq, m, h, s.norm_eps, DIV_NORM_OUT,
                                   xb=self.pb)
