@@ -184,6 +184,19 @@ int velox_sm100_linear_swiglu_act(const velox_sm100_view* gate, const velox_sm10
 int velox_sm100_linears(const float* x, const uint16_t* xb, const velox_sm100_part* parts,
                         int nparts, int m);
 
+/* Backend::embed / embed_from (crates/velox-core/src/backend.rs:1142-1160): out[t, :] = the exact
+ * decode of row row_begin + ids[t] of the parent [n, k]; a row that does not exist gives zeros (ids
+ * written on the device are not checked by the host). `ids` is a device array. Same signature as
+ * velox_portable_embed (crates/velox-cuda/src/portable.rs:92-101; kernels
+ * crates/velox-cuda/kernels/portable_model.cu:485-575). k must be a multiple of 16. */
+int velox_sm100_embed(const uint32_t* ids, int count, const uint8_t* w, int format, long long n, long long k,
+                      long long row_begin, float* out);
+
+/* Backend::matmul (backend.rs:1550-1564): y[m, n] = x[m, k] . w[n, k]^T, all f32, f32 accumulation.
+ * Same signature as velox_portable_matmul (crates/velox-cuda/src/portable.rs:19-26; kernel
+ * crates/velox-cuda/kernels/portable.cu:13-28). */
+int velox_sm100_matmul(const float* x, const float* w, float* y, int m, int n, int k);
+
 /* Exact decode of a view to f32 [rows, k]: the values format::decode_rows produces
  * (crates/velox-core/src/format.rs:426-490), bit for bit. */
 int velox_sm100_dequant_rows(const velox_sm100_view* view, float* out);

@@ -47,7 +47,7 @@ def test_payload_bytes_and_swizzle_agree_with_oracle():
 
 def test_format_names_and_shape_rules():
     assert WeightFormat.from_names("nvfp4", "block_scale_k16_m128x4_v1") is WeightFormat.NVFP4
-    assert WeightFormat.from_names("q4_k", "ggml_block_v1") is WeightFormat.GGML_Q4_K
+    assert WeightFormat.from_names("ggml_q4_k", "ggml_block_v1") is WeightFormat.GGML_Q4_K
     with pytest.raises(Unsupported):
         WeightFormat.from_names("q8_g32_fp16", "row_split_k128_v1")
     with pytest.raises(ShapeError):

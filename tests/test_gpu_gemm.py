@@ -394,4 +394,6 @@ def test_grouped_prefill_linears_on_ragged_views(b, m):
         assert torch.equal(g, w)
         ref = oracle_linear(hb.float().cpu().numpy(), p, NV, n, k, r0, rows, m, ActQuant(ActQuant.NVFP4, 256.0))
         e_conf, e_rms = both_metrics(g.float().cpu().numpy().reshape(m, rows), ref)
-        assert e_rms <= RMS_TOL and e_conf <= 2.0 ** -8, (e_conf, e_rms)   # bf16 output: half an ulp of bf16
+        # bf16 output: half a unit in the last place of every value, so the conformance metric (relative for
+        # large values) is held to 2^-8; max|d|/rms grows with the largest output and is not the measure here
+        assert e_conf <= 2.0 ** -8 and e_rms <= 4e-2, (e_conf, e_rms)

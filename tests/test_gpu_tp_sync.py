@@ -58,7 +58,7 @@ def test_single_rank_step_raises_and_accepts_flags():
     hb = O.quantize_activations(O.rms_norm(acc.cpu().numpy().reshape(m, dim), np.ones(dim, np.float32), 1e-6).reshape(-1),
                                 dim, O.ACT_BF16).reshape(m, dim)
     ref = oracle_linear(hb, payload, NV, n, dim, 0, n, m, ActQuant(ActQuant.NVFP4, 256.0))
-    assert both_metrics(slots.float().cpu().numpy().reshape(m, n), ref)[1] <= 1e-2
+    assert both_metrics(slots.float().cpu().numpy().reshape(m, n), ref)[0] <= 2.0 ** -8     # bf16 output
 
 
 def test_a_wait_nobody_answers_gives_up_and_the_status_can_be_cleared():
@@ -96,4 +96,4 @@ def test_a_wait_nobody_answers_gives_up_and_the_status_can_be_cleared():
     torch.cuda.synchronize()
     assert b.debug_status() == 0
     ref = oracle_linear(hb.float().cpu().numpy(), payload, NV, n, k, 0, n, m, ActQuant(ActQuant.NVFP4, 256.0))
-    assert both_metrics(yb.float().cpu().numpy().reshape(m, n), ref)[1] <= 1e-2
+    assert both_metrics(yb.float().cpu().numpy().reshape(m, n), ref)[0] <= 2.0 ** -8        # bf16 output

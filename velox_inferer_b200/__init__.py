@@ -15,6 +15,9 @@ def __getattr__(name):
     if name == "Sm100Backend":
         from .backend import Sm100Backend
         return Sm100Backend
+    if name in ("Artifact", "ArtifactError", "Loader", "write_container"):
+        from . import artifact
+        return getattr(artifact, name)
     if name in ("LinearStack", "StackSpec"):
         from . import stack
         return getattr(stack, name)

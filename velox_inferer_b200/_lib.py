@@ -89,6 +89,8 @@ SIGNATURES = {
     "velox_sm100_linear_swiglu_act": (_I, [_PV, _PV, _I, C.POINTER(C.c_float)]),
     "velox_sm100_linears": (_I, [_VP, _VP, C.POINTER(Part), _I, _I]),
     "velox_sm100_dequant_rows": (_I, [_PV, _VP]),
+    "velox_sm100_embed": (_I, [_VP, _I, _VP, _I, _LL, _LL, _LL, _VP]),
+    "velox_sm100_matmul": (_I, [_VP, _VP, _VP, _I, _I, _I]),
     "velox_sm100_quantize_act_fp8row": (_I, [_VP, _I, _LL, _VP, _VP]),
     "velox_sm100_quantize_act_nvfp4": (_I, [_VP, _I, _LL, _F, _VP, _VP]),
     "velox_sm100_encode_nvfp4": (_I, [_VP, _LL, _LL, _F, _VP]),

@@ -172,6 +172,37 @@ class Sm100Backend:
         self._bind()
         status(self.lib.velox_sm100_linears(_ptr(x), _ptr(xb), arr, len(parts), m), "sm100 linears")
 
+    def matmul(self, x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, m: int, n: int, k: int) -> None:
+        """Backend::matmul (backend.rs:1550-1564): y[m, n] = x[m, k] . w[n, k]^T, f32."""
+        _dev(x, torch.float32, "matmul x"); _dev(w, torch.float32, "matmul w"); _dev(y, torch.float32, "matmul y")
+        if m <= 0 or n <= 0 or k <= 0 or x.numel() < m * k or w.numel() < n * k or y.numel() < m * n:
+            raise ShapeError(f"matmul [{m},{k}] x [{n},{k}]^T -> [{m},{n}]: buffers {x.numel()}, {w.numel()}, {y.numel()}")
+        self._bind()
+        status(self.lib.velox_sm100_matmul(x.data_ptr(), w.data_ptr(), y.data_ptr(), m, n, k), "sm100 matmul")
+
+    def embed_from(self, ids: torch.Tensor, offset: int, count: int, table: WeightView, out: torch.Tensor) -> None:
+        """Backend::embed_from (backend.rs:1149-1160): rows ``ids[offset : offset + count]`` of the table
+        view, decoded exactly; ``ids`` is a device int32 tensor."""
+        _dev(out, torch.float32, "embed out")
+        if ids.dtype != torch.int32 or not ids.is_cuda:
+            raise ShapeError("embed ids: expected a CUDA int32 tensor")
+        check_weight(table, table.buf.numel())
+        if offset < 0 or count < 0 or offset + count > ids.numel() or out.numel() < count * table.k:
+            raise ShapeError(f"embed: ids {offset}+{count} of {ids.numel()}, out {out.numel()} for {count} x {table.k}")
+        self._bind()
+        status(self.lib.velox_sm100_embed(ids.data_ptr() + 4 * offset, count, table.buf.data_ptr(), int(table.format),
+                                          table.parent_rows, table.k, table.row_begin, out.data_ptr()), "sm100 embed")
+
+    def embed(self, ids, table: WeightView, out: torch.Tensor) -> None:
+        """Backend::embed (backend.rs:1142-1148): host ids, each checked against the view's rows."""
+        ids = [int(i) for i in ids]
+        if any(i < 0 or i >= table.rows for i in ids):
+            raise ShapeError(f"embed: id outside the table's {table.rows} rows")
+        if not ids:
+            return
+        dev_ids = torch.tensor(ids, dtype=torch.int32, device=self.device)
+        self.embed_from(dev_ids, 0, len(ids), table, out)
+
     # ---- neighbours --------------------------------------------------------------------------
     def dequant_rows(self, w: WeightView) -> torch.Tensor:
         """Exact decode of the view, the values format::decode_rows produces."""

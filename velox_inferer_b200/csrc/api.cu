@@ -460,6 +460,29 @@ int velox_sm100_dequant_rows(const velox_sm100_view* view, float* out) {
     return dequant_rows_f32(view, out);
 }
 
+int velox_sm100_embed(const uint32_t* ids, int count, const uint8_t* w, int format, long long n, long long k,
+                      long long row_begin, float* out) {
+    if (!ids || !out || count < 0) return VELOX_ERR_SHAPE;
+    if (count == 0) return 0;
+    velox_sm100_view v{};
+    v.w = w;
+    v.format = format;
+    v.policy = VELOX_POLICY_A16_ONLY;
+    v.n = n;
+    v.k = k;
+    v.row_begin = row_begin;
+    v.rows = 1;     // (check::embed: the table is rows [row_begin, n) of the parent; ids index into it)
+    if (row_begin < 0 || row_begin >= n) return VELOX_ERR_SHAPE;
+    int rc = check_view(&v);
+    if (rc != 0) return rc;
+    return embed_rows_f32(&v, ids, count, out);
+}
+
+int velox_sm100_matmul(const float* x, const float* w, float* y, int m, int n, int k) {
+    if (!x || !w || !y) return VELOX_ERR_SHAPE;
+    return matmul_f32(x, w, y, m, n, k);
+}
+
 int velox_sm100_quantize_act_fp8row(const float* x, int m, long long k, uint8_t* codes,
                                     float* scales) {
     if (!x || !codes || !scales) return VELOX_ERR_SHAPE;

@@ -15,20 +15,27 @@
 
 namespace vx {
 
-// One thread decodes 16 consecutive k of one row.
+// One thread decodes 16 consecutive k of one row. With `ids` the rows are gathered: output row i is
+// parent row row_begin + ids[i], or zeros where that row does not exist (ids written on the device
+// are not checked by the host), which is Backend::embed (crates/velox-core/src/backend.rs:1142-1160;
+// reference kernels crates/velox-cuda/kernels/portable_model.cu:485-575).
 template <int FMT, typename OUT>
 __global__ void __launch_bounds__(256)
 dequant_rows_kernel(const uint8_t* __restrict__ w, long long n, long long k, long long row_begin,
-                    int rows, OUT* __restrict__ out, long long ld_out, long long lo_offset) {
+                    int rows, OUT* __restrict__ out, long long ld_out, long long lo_offset,
+                    const uint32_t* __restrict__ ids) {
     const long long groups_per_row = k / 16;
     const long long total = (long long)rows * groups_per_row;
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long i = idx / groups_per_row;
         const long long g = idx % groups_per_row;
-        const long long r = row_begin + i;
+        const long long r = row_begin + (ids ? (long long)ids[i] : i);
         float v[16];
-        if (FMT == VELOX_FMT_NVFP4) {
+        if (ids && (r < 0 || r >= n)) {
+#pragma unroll
+            for (int j = 0; j < 16; j++) v[j] = 0.0f;
+        } else if (FMT == VELOX_FMT_NVFP4) {
             const long long scale_plane = align256(n * k / 2);
             const uint2 codes = *reinterpret_cast<const uint2*>(w + (r * k + g * 16) / 2);
             const float scale = e4m3_to_f32(w[scale_plane + nvfp4_scale_offset(r, g, k)]);
@@ -101,9 +108,11 @@ dequant_rows_kernel(const uint8_t* __restrict__ w, long long n, long long k, lon
 }
 
 template <typename OUT>
-static int launch_dequant(const velox_sm100_view* v, OUT* out, long long ld_out, long long lo_offset) {
+static int launch_dequant(const velox_sm100_view* v, OUT* out, long long ld_out, long long lo_offset,
+                          const uint32_t* ids = nullptr, int count = 0) {
     if (v->k % 16 != 0) return VELOX_ERR_UNSUPPORTED;
-    const long long total = (long long)v->rows * (v->k / 16);
+    const int rows = ids ? count : v->rows;
+    const long long total = (long long)rows * (v->k / 16);
     long long blocks = (total + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (blocks < 1) blocks = 1;
@@ -112,15 +121,15 @@ static int launch_dequant(const velox_sm100_view* v, OUT* out, long long ld_out,
     switch (v->format) {
         case VELOX_FMT_NVFP4:
             dequant_rows_kernel<VELOX_FMT_NVFP4, OUT><<<(unsigned)blocks, 256, 0, s>>>(
-                v->w, v->n, v->k, v->row_begin, v->rows, out, ld_out, lo_offset);
+                v->w, v->n, v->k, v->row_begin, rows, out, ld_out, lo_offset, ids);
             break;
         case VELOX_FMT_FP8_ROW_BF16:
             dequant_rows_kernel<VELOX_FMT_FP8_ROW_BF16, OUT><<<(unsigned)blocks, 256, 0, s>>>(
-                v->w, v->n, v->k, v->row_begin, v->rows, out, ld_out, lo_offset);
+                v->w, v->n, v->k, v->row_begin, rows, out, ld_out, lo_offset, ids);
             break;
         case VELOX_FMT_GGML_Q4_K:
             dequant_rows_kernel<VELOX_FMT_GGML_Q4_K, OUT><<<(unsigned)blocks, 256, 0, s>>>(
-                v->w, v->n, v->k, v->row_begin, v->rows, out, ld_out, lo_offset);
+                v->w, v->n, v->k, v->row_begin, rows, out, ld_out, lo_offset, ids);
             break;
         default:
             return VELOX_ERR_UNSUPPORTED;
@@ -129,6 +138,10 @@ static int launch_dequant(const velox_sm100_view* v, OUT* out, long long ld_out,
 }
 
 int dequant_rows_f32(const velox_sm100_view* v, float* out) { return launch_dequant<float>(v, out, v->k, 0); }
+
+int embed_rows_f32(const velox_sm100_view* v, const uint32_t* ids, int count, float* out) {
+    return launch_dequant<float>(v, out, v->k, 0, ids, count);
+}
 
 int dequant_rows_bf16(const velox_sm100_view* v, uint16_t* out, long long ld_out, long long lo_offset) {
     return launch_dequant<uint16_t>(v, out, ld_out, lo_offset);

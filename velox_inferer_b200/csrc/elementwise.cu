@@ -722,6 +722,54 @@ int sp_finish(float* acc, const uint16_t* slots, int nslots, long long slot_stri
     return launch_status();
 }
 
+// y[m, n] = x[m, k] . w[n, k]^T in f32 (Backend::matmul, crates/velox-core/src/backend.rs:1550-1564;
+// reference kernel: one warp per output, crates/velox-cuda/kernels/portable.cu:13-28). A 64 x 64
+// output tile per block of 256 threads, 16-wide k slices staged in shared memory (k-major, so a
+// thread's four rows / four columns are one 16-byte load), a 4 x 4 register block per thread and
+// f32 fused multiply-adds in ascending k: each output is one f32 running sum.
+__global__ void __launch_bounds__(256)
+matmul_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, int m, int n, int k) {
+    __shared__ __align__(16) float xs[16][64 + 4];
+    __shared__ __align__(16) float ws[16][64 + 4];
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    const long long row0 = (long long)blockIdx.y * 64, col0 = (long long)blockIdx.x * 64;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < k; k0 += 16) {
+        for (int i = threadIdx.x; i < 64 * 16; i += 256) {
+            const int r = i / 16, c = i % 16;
+            xs[c][r] = (row0 + r < m && k0 + c < k) ? x[(row0 + r) * k + k0 + c] : 0.0f;
+            ws[c][r] = (col0 + r < n && k0 + c < k) ? w[(col0 + r) * k + k0 + c] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < 16; c++) {
+            const float4 a = *reinterpret_cast<const float4*>(&xs[c][ty * 4]);
+            const float4 b = *reinterpret_cast<const float4*>(&ws[c][tx * 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const long long r = row0 + ty * 4 + i, c = col0 + tx * 4 + j;
+            if (r < m && c < n) y[r * n + c] = acc[i][j];
+        }
+}
+
+int matmul_f32(const float* x, const float* w, float* y, int m, int n, int k) {
+    if (m < 1 || n < 1 || k < 1) return VELOX_ERR_SHAPE;
+    const dim3 grid((unsigned)((n + 63) / 64), (unsigned)((m + 63) / 64));
+    if (grid.y > 65535) return VELOX_ERR_UNSUPPORTED;
+    matmul_f32_kernel<<<grid, 256, 0, stream()>>>(x, w, y, m, n, k);
+    return launch_status();
+}
+
 int swiglu(const float* src, long long rows, int src_cols, int gate, int up, int width, float* out) {
     if (rows < 1 || width < 1 || gate < 0 || up < 0 || gate + width > src_cols || up + width > src_cols)
         return VELOX_ERR_SHAPE;

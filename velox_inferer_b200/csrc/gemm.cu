@@ -748,6 +748,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     rb[8 * j] = b0.x; rb[8 * j + 1] = b0.y; rb[8 * j + 2] = b0.z; rb[8 * j + 3] = b0.w;
                     rb[8 * j + 4] = b1.x; rb[8 * j + 5] = b1.y; rb[8 * j + 6] = b1.z; rb[8 * j + 7] = b1.w;
                 }
+                // The stage is handed back to a writer of another proxy (the bulk copies of the scale
+                // producer): the reads above have to be ordered ahead of that proxy's accesses before
+                // the arrive, or a copy can land while a lane's load is still in flight. Measured on
+                // B200 without this fence: a few percent of all tiles but a CTA's first came out with
+                // one k-block's scales of the block four steps later, in single lane quadrants.
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sf_empty(stage));
                 // the MMAs that read this column set (SF_STAGES k-blocks ago) must have completed
@@ -962,10 +968,9 @@ static int launch(bool swiglu, const CUtensorMap& a, GemmMaps& maps, GemmParams&
         else
             make_out_map(&maps.out[i], p.m, p.part[i], out_cols[i], first_row[i]);
     }
-    for (int i = p.nparts; i < MAX_PARTS; i++) {
-        maps.b[i] = maps.b[0];
-        maps.out[i] = a;
-    }
+    // (entries no tile refers to still have to be valid maps; the SwiGLU form uses b[0] and b[1])
+    for (int i = swiglu && p.nparts < 2 ? 2 : p.nparts; i < MAX_PARTS; i++) maps.b[i] = maps.b[0];
+    for (int i = p.nparts; i < MAX_PARTS; i++) maps.out[i] = a;
     const int sms = sm_count();
     TimedRegion timed(KIND == KIND_MXF4 ? TIMED_GEMM_FP4 : KIND == KIND_F8 ? TIMED_GEMM_FP8 : TIMED_GEMM_BF16);
     // More than one token tile: CTA pairs (256 tokens per unit, half the W traffic per CTA).
@@ -1353,10 +1358,8 @@ extern "C" int velox_sm100_linear_nvfp4_a4_static(const uint16_t* xb, const velo
     CUtensorMap ma;
     if ((rc = nvfp4_part(a, p, maps, 0)) != 0) return rc;
     if ((rc = make_map(&ma, codes, false, m, k / 2)) != 0) return rc;
-    for (int i = 0; i < MAX_PARTS; i++) {
-        maps.b[i] = maps.b[0];
-        maps.out[i] = ma;
-    }
+    for (int i = 1; i < MAX_PARTS; i++) maps.b[i] = maps.b[0];
+    for (int i = 0; i < MAX_PARTS; i++) maps.out[i] = ma;
     make_out_map(&maps.out[0], m, p.part[0], w.rows, w.row_begin);
     int sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);

@@ -363,6 +363,10 @@ gemv_nvfp4_tc_kernel(const __grid_constant__ CUtensorMap map_w0, const __grid_co
                     ra[4 * j] = a.x; ra[4 * j + 1] = a.y; ra[4 * j + 2] = a.z; ra[4 * j + 3] = a.w;
                     rb[4 * j] = b.x; rb[4 * j + 1] = b.y; rb[4 * j + 2] = b.z; rb[4 * j + 3] = b.w;
                 }
+                // the stage goes back to a writer of the async proxy (bulk copies): order these
+                // generic-proxy reads ahead of it before the arrive (a copy landing while a lane's
+                // load was in flight corrupted scales in the prefill GEMM, which shares this scheme)
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sf_empty(stage));
                 // the MMAs that read this column set one ring pass ago must have completed

@@ -385,6 +385,9 @@ gemv_nvfp4_tma_kernel(const __grid_constant__ CUtensorMap map_codes0, const __gr
                             }
                         }
                     }
+                    // the stage goes back to the TMA producer (async proxy): order this warp's
+                    // generic-proxy reads of it ahead of that proxy before the arrive
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     __syncwarp();
                     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty_bar(stage)) : "memory");
                     if (++stage == TG_STAGES) {

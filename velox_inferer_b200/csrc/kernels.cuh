@@ -31,6 +31,10 @@ struct LinearArgs {
 };
 
 int dequant_rows_f32(const velox_sm100_view* v, float* out);
+// out[t] = exact decode of parent row v->row_begin + ids[t] (zeros for rows that do not exist).
+int embed_rows_f32(const velox_sm100_view* v, const uint32_t* ids, int count, float* out);
+// y[m, n] = x[m, k] . w[n, k]^T, all f32.
+int matmul_f32(const float* x, const float* w, float* y, int m, int n, int k);
 // lo_offset > 0: also write the bf16 residual of each value lo_offset elements after it.
 int dequant_rows_bf16(const velox_sm100_view* v, uint16_t* out, long long ld_out, long long lo_offset);
 

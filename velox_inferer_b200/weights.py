@@ -18,11 +18,11 @@ class WeightFormat(enum.IntEnum):
 
     FP8_ROW_BF16 = 2   # fp8_e4m3fn_row_bf16 / row_scale_v1
     NVFP4 = 3          # nvfp4 / block_scale_k16_m128x4_v1
-    GGML_Q4_K = 17     # ggml_q4_k / ggml_block_v1
+    GGML_Q4_K = 17     # ggml_q4_k / ggml_block_v1 (crates/velox-core/src/ggml.rs:51-68)
 
     @property
     def format_name(self) -> str:
-        return {2: "fp8_e4m3fn_row_bf16", 3: "nvfp4", 17: "q4_k"}[int(self)]
+        return {2: "fp8_e4m3fn_row_bf16", 3: "nvfp4", 17: "ggml_q4_k"}[int(self)]
 
     @property
     def layout(self) -> str:
@@ -32,7 +32,7 @@ class WeightFormat(enum.IntEnum):
     def from_names(fmt: str, layout: str) -> "WeightFormat":
         table = {("fp8_e4m3fn_row_bf16", "row_scale_v1"): WeightFormat.FP8_ROW_BF16,
                  ("nvfp4", "block_scale_k16_m128x4_v1"): WeightFormat.NVFP4,
-                 ("q4_k", "ggml_block_v1"): WeightFormat.GGML_Q4_K}
+                 ("ggml_q4_k", "ggml_block_v1"): WeightFormat.GGML_Q4_K}
         try:
             return table[(fmt, layout)]
         except KeyError:
