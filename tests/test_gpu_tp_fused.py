@@ -23,5 +23,6 @@ def test_fused_tp_step_is_exact_and_matches_the_all_reduce_step(world):
            "--master-addr", "127.0.0.1", "--master-port", str(29533 + world), os.path.join(here, "tp_fused_worker.py")]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=420, env=env)
-    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    fail = out.stdout[out.stdout.find("TP_FUSED_FAIL"):][:3000] if "TP_FUSED_FAIL" in out.stdout else ""
+    assert out.returncode == 0, fail + out.stdout[-1500:] + out.stderr[-1500:]
     assert "TP_FUSED_OK" in out.stdout

@@ -79,7 +79,7 @@ def check_phases(b, stack, xb, rank, world):
     want = O.linear(np.ascontiguousarray(qv[toks]), l.o.buf.cpu().numpy(), O.FMT_NVFP4, h, l.o.k, 0, h, len(toks),
                     act=O.ACT_EXACT)
     got = stack.pb.float().cpu().numpy().reshape(m, h)[toks]
-    assert O.max_abs_diff(got, want) / O.rms(want) <= 1e-2 and O.max_err(got, want) <= 2.0 ** -8
+    assert O.max_err(got, want) <= 2.0 ** -8, O.max_err(got, want)      # bf16 output: half a unit in the last place
     # norm: residual += slots in rank order (f32), blob = quantiser(bf16 norm)
     x_before = x_own.clone()
     part = f.slots[: rows * h].float()
@@ -163,4 +163,10 @@ def main() -> None:
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except BaseException:      # the launcher's own report drops a rank's traceback: say it where the test looks
+        import traceback
+
+        print(f"TP_FUSED_FAIL rank {os.environ.get('RANK')}:\n{traceback.format_exc()}", flush=True)
+        os._exit(1)
