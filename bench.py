@@ -461,6 +461,10 @@ def main():
                     "traffic_of": "single [25600, 5120] M = 1 launch: 75.9 MB per launch against 73.8 MB algorithmic "
                                   "(profiles/gemv_nvfp4_tc_25600x5120_m1.md); the step's launches were not captured"}
 
+    # where the eager, event-bracketed pass spent its step: the GEMMs, the norms (each including the time
+    # it waited for peers' flags) and everything between kernels
+    roofline["eager_step_ms"] = {k: round(timed[k][0] / args.steps, 3) for k in ("gemm_nvfp4", "gemv", "norm")
+                                 if timed[k][1] > 0}
     cfg = workload_config(args, spec, m, args.tp if fused_tp else False)
     if check is not None:
         cfg["tp_check"] = check

@@ -107,7 +107,9 @@ long long velox_sm100_launch_count(void);
  * event pair on its launch stream (do not enable it while capturing a CUDA graph).
  * velox_sm100_timing_collect synchronises the device and returns, per class, the summed kernel
  * milliseconds and the launch count since the last collect. Classes: 0 GEMV, 1 GEMM NVFP4,
- * 2 GEMM FP8, 3 GEMM bf16, 4 activation quantiser, 5 weight dequantiser. `classes` >= 6. */
+ * 2 GEMM FP8, 3 GEMM bf16, 4 activation quantiser, 5 weight dequantiser, 6 the norms that write
+ * NVFP4 activations (and the tensor-parallel finish). A kernel's time includes what it spends
+ * waiting for peers' flags. `classes` >= 7. */
 int velox_sm100_timing_enable(int on);
 int velox_sm100_timing_collect(double* ms_by_class, long long* count_by_class, int classes);
 

@@ -406,7 +406,7 @@ class Sm100Backend:
         return xb
 
     # ---- measurement hooks (crates/velox-cuda/src/timing.rs) ---------------------------------
-    TIMED_CLASSES = ("gemv", "gemm_nvfp4", "gemm_fp8", "gemm_bf16", "act_quant", "dequant")
+    TIMED_CLASSES = ("gemv", "gemm_nvfp4", "gemm_fp8", "gemm_bf16", "act_quant", "dequant", "norm")
 
     def timing_enable(self, on: bool) -> None:
         self.lib.velox_sm100_timing_enable(int(on))

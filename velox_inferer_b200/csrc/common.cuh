@@ -150,7 +150,7 @@ static inline int launch_status() {
 // VELOX_GPU_TIMING (crates/velox-cuda/src/timing.rs:1-97): when enabled, an event pair brackets
 // the kernel on its launch stream; totals per class are read back after a synchronise.
 enum TimedClass { TIMED_GEMV = 0, TIMED_GEMM_FP4, TIMED_GEMM_FP8, TIMED_GEMM_BF16, TIMED_ACT_QUANT,
-                  TIMED_DEQUANT, TIMED_CLASSES };
+                  TIMED_DEQUANT, TIMED_NORM, TIMED_CLASSES };
 struct TimedRegion {
     int slot;
     explicit TimedRegion(int cls);

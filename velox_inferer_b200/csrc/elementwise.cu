@@ -182,6 +182,7 @@ add_rms_norm_q4_rows_kernel(float* __restrict__ acc, const float* __restrict__ x
     const int T = (int)blockDim.x;   // a multiple of 32, at most 1024
     const long long row = blockIdx.x;
     if (threadIdx.x == 0) grid_launch_dependents();   // a decode linear behind this may start fetching weights
+    grid_dependency_wait();   // (returns at once unless the launch allowed an early start)
     if (sync.wait_phase >= 0) {
         // tensor parallel: the partial-sum slots are complete once every rank's linear has said so
         if (threadIdx.x == 0) tp_wait_flags(sync);
@@ -451,6 +452,7 @@ sp_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ s
     const int T = (int)blockDim.x, tid = (int)threadIdx.x;
     const int c0 = tid * 4, c1 = (T + tid) * 4;
     if (tid == 0) grid_launch_dependents();
+    grid_dependency_wait();   // launched with early start allowed: everything it reads comes from the kernel ahead
     if (sync.wait_phase >= 0) {
         // the partial-sum slots are complete once every rank's row-split linear has said so
         if (tid == 0) tp_wait_flags(sync);
@@ -559,6 +561,8 @@ sp_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ s
 __global__ void __launch_bounds__(256)
 sp_finish_kernel(float* __restrict__ acc, const uint16_t* __restrict__ slots, int nslots, long long slot_stride,
                  const Q4Dest dst, long long row0, long long len, int dim, const __grid_constant__ TpSync sync) {
+    if (threadIdx.x == 0) grid_launch_dependents();
+    grid_dependency_wait();
     if (sync.wait_phase >= 0) {
         if (threadIdx.x == 0) tp_wait_flags(sync);
         __syncthreads();
@@ -585,20 +589,44 @@ sp_finish_kernel(float* __restrict__ acc, const uint16_t* __restrict__ slots, in
     }
 }
 
+// Launch configuration of the step's elementwise kernels: early start allowed (the blocks become
+// resident while the kernel ahead drains and wait for it before their first access).
+struct EarlyLaunch {
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr[1];
+    EarlyLaunch(unsigned blocks, unsigned threads) {
+        static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
+        cfg.gridDim = dim3(blocks);
+        cfg.blockDim = dim3(threads);
+        cfg.stream = stream();
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = early ? 1 : 0;
+    }
+};
+
 static int launch_norm_q4(float* acc, const float* x, const uint16_t* xb, int nslots, long long slot_stride,
                           const float* weight, uint16_t* yb, const Q4Dest& dst, long long row0, int rows,
                           int rows_padded, int dim, float eps, int offset, float divisor, const TpSync& sync) {
     const float off = offset ? 1.0f : 0.0f;
-    if (dim % 256 == 0)
+    TimedRegion timed(TIMED_NORM);
+    cudaError_t e;
+    if (dim % 256 == 0) {
         // one block per row with dim / 8 threads: two 128-bit slices per thread, many warps in flight
-        add_rms_norm_q4_rows_kernel<2, 1024><<<(unsigned)rows_padded, dim / 8, 0, stream()>>>(
-            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor, sync);
-    else if (dim <= 2048)
-        add_rms_norm_q4_rows_kernel<2, 256><<<(unsigned)rows_padded, 256, 0, stream()>>>(
-            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor, sync);
-    else
-        add_rms_norm_q4_rows_kernel<8, 256><<<(unsigned)rows_padded, 256, 0, stream()>>>(
-            acc, x, xb, nslots, slot_stride, weight, yb, dst, row0, rows, dim, eps, off, divisor, sync);
+        EarlyLaunch l((unsigned)rows_padded, (unsigned)(dim / 8));
+        e = cudaLaunchKernelEx(&l.cfg, add_rms_norm_q4_rows_kernel<2, 1024>, acc, x, xb, nslots, slot_stride, weight, yb,
+                               dst, row0, rows, dim, eps, off, divisor, sync);
+    } else if (dim <= 2048) {
+        EarlyLaunch l((unsigned)rows_padded, 256u);
+        e = cudaLaunchKernelEx(&l.cfg, add_rms_norm_q4_rows_kernel<2, 256>, acc, x, xb, nslots, slot_stride, weight, yb,
+                               dst, row0, rows, dim, eps, off, divisor, sync);
+    } else {
+        EarlyLaunch l((unsigned)rows_padded, 256u);
+        e = cudaLaunchKernelEx(&l.cfg, add_rms_norm_q4_rows_kernel<8, 256>, acc, x, xb, nslots, slot_stride, weight, yb,
+                               dst, row0, rows, dim, eps, off, divisor, sync);
+    }
+    if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
 
@@ -641,6 +669,7 @@ int add_rms_norm_q4(float* acc, const float* x, const uint16_t* xb, const float*
                                       divisor);
         };
         cudaError_t e;
+        TimedRegion timed(TIMED_NORM);
         if (threads <= 256)
             e = go(add_rms_norm_q4_stream_kernel<256, 6>, 6);
         else if (threads <= 512)
@@ -693,15 +722,19 @@ int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_str
         }
         const int blocks = rows < sms ? rows : sms;
         const float off = offset ? 1.0f : 0.0f;
+        TimedRegion timed(TIMED_NORM);
+        EarlyLaunch l((unsigned)blocks, (unsigned)(dim / 8));
+        cudaError_t e;
         if (nslots == 2)
-            sp_norm_q4_stream_kernel<2><<<blocks, dim / 8, 0, stream()>>>(acc, slots, slot_stride, weight, dst, row0, rows,
-                                                                            dim, eps, off, divisor, ts);
+            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<2>, acc, slots, slot_stride, weight, dst, row0, rows, dim,
+                                   eps, off, divisor, ts);
         else if (nslots == 4)
-            sp_norm_q4_stream_kernel<4><<<blocks, dim / 8, 0, stream()>>>(acc, slots, slot_stride, weight, dst, row0, rows,
-                                                                            dim, eps, off, divisor, ts);
+            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<4>, acc, slots, slot_stride, weight, dst, row0, rows, dim,
+                                   eps, off, divisor, ts);
         else
-            sp_norm_q4_stream_kernel<8><<<blocks, dim / 8, 0, stream()>>>(acc, slots, slot_stride, weight, dst, row0, rows,
-                                                                            dim, eps, off, divisor, ts);
+            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<8>, acc, slots, slot_stride, weight, dst, row0, rows, dim,
+                                   eps, off, divisor, ts);
+        if (e != cudaSuccess) return (int)e;
         return launch_status();
     }
     return launch_norm_q4(acc, nullptr, nslots > 0 ? slots : nullptr, nslots, slot_stride, weight, nullptr, dst, row0,
@@ -718,7 +751,10 @@ int sp_finish(float* acc, const uint16_t* slots, int nslots, long long slot_stri
     TpSync ts;
     const int src = tp_sync_fill_elementwise(&ts, sync);
     if (src != 0) return src;
-    sp_finish_kernel<<<grid_1d(len / 4, 256), 256, 0, stream()>>>(acc, slots, nslots, slot_stride, dst, row0, len, dim, ts);
+    TimedRegion timed(TIMED_NORM);
+    EarlyLaunch l(grid_1d(len / 4, 256), 256u);
+    const cudaError_t e = cudaLaunchKernelEx(&l.cfg, sp_finish_kernel, acc, slots, nslots, slot_stride, dst, row0, len, dim, ts);
+    if (e != cudaSuccess) return (int)e;
     return launch_status();
 }
 

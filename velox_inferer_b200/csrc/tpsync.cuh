@@ -30,14 +30,14 @@ struct TpSync {
     int wait_phase, signal_phase;             // rows of the table; -1 = none
 };
 
-__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+__device__ __forceinline__ unsigned int ld_relaxed_sys_u32(const unsigned int* p) {
     unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
 
-__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_relaxed_sys_u32(unsigned int* p, unsigned int v) {
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ unsigned long long tp_timer_ns() {
@@ -48,29 +48,36 @@ __device__ __forceinline__ unsigned long long tp_timer_ns() {
 
 // Called by one thread, after the kernel's dependency on the launch ahead of it is resolved:
 // returns once every rank's flag in row wait_phase has reached this step's epoch, or false after
-// limit_ns with the status word set.
+// limit_ns with the status word set. The polls are relaxed loads; one system-scope fence after the
+// last of them orders everything this thread (and, behind a barrier, its CTA) reads afterwards
+// behind the peers' writes that preceded their flags.
 static __device__ __noinline__ bool tp_wait_flags(const TpSync& s) {
     if (s.wait_phase < 0 || s.n <= 0) return true;
     const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(s.epoch);
     const unsigned int* row =
         reinterpret_cast<const unsigned int*>(s.flags[s.rank]) + (long long)s.wait_phase * TP_FLAG_STRIDE;
     const unsigned long long t0 = tp_timer_ns();
-    for (int src = 0; src < s.n; src++) {
+    bool ok = true;
+    for (int src = 0; src < s.n && ok; src++) {
         unsigned int spins = 0;
-        while ((int)(ld_acquire_sys_u32(row + src) - want) < 0) {
-            __nanosleep(64);
+        while ((int)(ld_relaxed_sys_u32(row + src) - want) < 0) {
+            __nanosleep(32);
             if ((++spins & 63u) == 0 && tp_timer_ns() - t0 > s.limit_ns) {
                 atomicExch(s.status, ST_TIMEOUT_PEER);
-                return false;
+                ok = false;
+                break;
             }
         }
     }
-    return true;
+    __threadfence_system();
+    return ok;
 }
 
 // Called by one thread of every CTA, behind a CTA-wide barrier that follows the CTA's last store
-// (and the completion of its bulk stores): the CTA that arrives last writes the epoch into row
-// signal_phase, column rank, of every rank's table.
+// (and the completion of its bulk stores): each CTA makes its writes visible system-wide and takes
+// a ticket; the CTA that takes the last one writes the epoch into row signal_phase, column rank, of
+// every rank's table (relaxed stores behind one fence: a release store per peer would serialise a
+// round trip over the links for each of them).
 static __device__ __noinline__ void tp_signal(const TpSync& s, unsigned int ctas) {
     if (s.signal_phase < 0 || s.n <= 0) return;
     __threadfence_system();
@@ -80,7 +87,7 @@ static __device__ __noinline__ void tp_signal(const TpSync& s, unsigned int ctas
     __threadfence_system();
     const unsigned int e = *reinterpret_cast<const volatile unsigned int*>(s.epoch);
     for (int d = 0; d < s.n; d++)
-        st_release_sys_u32(reinterpret_cast<unsigned int*>(s.flags[d]) + (long long)s.signal_phase * TP_FLAG_STRIDE + s.rank, e);
+        st_relaxed_sys_u32(reinterpret_cast<unsigned int*>(s.flags[d]) + (long long)s.signal_phase * TP_FLAG_STRIDE + s.rank, e);
 }
 
 // Host side: the C-ABI description of a launch's waits and signals, completed with the library's
