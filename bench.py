@@ -176,7 +176,9 @@ def workload_config(args, spec, m, fused_tp=False):
                            + ("bf16 partial tiles stored into the owning rank's rows by the GEMM epilogue over NVLink "
                               "(reduce-scatter), NVFP4 norm output stored into every rank (all-gather), ordered by "
                               "per-phase flags in peer memory (bounded waits)" if fused_tp == "flags" else
-                              "the same with signal-pad barrier kernels between the phases" if fused_tp == "barrier" else
+                              "the same flags raised and awaited by one-thread barrier kernels between the phases "
+                              "(bounded waits)" if fused_tp == "kernel" else
+                              "the same with torch's signal-pad barrier kernels between the phases" if fused_tp == "barrier" else
                               "bf16 all-reduce (NCCL) after o and down"),
             "activations": "NVFP4 tensor-core operands written by the producing kernels (ActQuant::Nvfp4, "
                            "per-use divisors 256/128/16); f32 residual stream; bf16 step input and output",
@@ -253,10 +255,12 @@ def main():
                     help="comma-separated subset of: nvfp4,sweep,mlp,formats,decode_stack (default all)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tp-check", action="store_true")
-    ap.add_argument("--tp", choices=("flags", "barrier", "nccl", "fused"), default="flags",
+    ap.add_argument("--tp", choices=("flags", "kernel", "barrier", "nccl", "fused"), default="flags",
                     help="N > 1: communication fused into the GEMM epilogue and the norm over symmetric memory, "
-                         "ordered by flags in peer memory (flags; 'fused' is the same) or by barrier kernels "
-                         "(barrier), or one NCCL all-reduce after o and down (nccl)")
+                         "ordered by flags in peer memory that the kernels themselves raise and poll (flags; "
+                         "'fused' is the same), by one-thread flag-barrier kernels between the phases (kernel), "
+                         "by torch's signal-pad barrier kernels (barrier); or one NCCL all-reduce after o and "
+                         "down (nccl)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)

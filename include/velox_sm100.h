@@ -315,6 +315,9 @@ int velox_sm100_linears_q4(const uint8_t* codes, const uint8_t* atoms, float div
  *    output; signals.
  *  - velox_sm100_tp_wait: a one-thread kernel that only waits (the end of a step: every rank's
  *    output rows are in place).
+ *  - velox_sm100_tp_barrier: a one-thread kernel that raises row signal_phase (= wait_phase) and then
+ *    waits on it: a barrier between two phases as a launch of its own, for steps whose kernels
+ *    run without `sync` (the data kernels then carry no waits; same bounded wait, same status).
  *  - velox_sm100_tp_signal: a one-thread kernel that only signals (tests).
  * `sync` may be NULL everywhere except tp_wait / tp_signal (single rank, or the caller orders the
  * ranks itself). */
@@ -326,6 +329,7 @@ typedef struct velox_sm100_tp_sync {
 } velox_sm100_tp_sync;
 int velox_sm100_tp_step_begin(unsigned int* epoch);
 int velox_sm100_tp_wait(const velox_sm100_tp_sync* sync);
+int velox_sm100_tp_barrier(const velox_sm100_tp_sync* sync);
 int velox_sm100_tp_signal(const velox_sm100_tp_sync* sync);
 int velox_sm100_tp_set_wait_limit_ms(int ms);
 int velox_sm100_tp_make_maps(void* maps_dev, const unsigned long long* slot_ptrs, int n, int rows_per_owner,

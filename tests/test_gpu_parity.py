@@ -418,3 +418,23 @@ def test_elementwise_ops_match_oracle(b):
     want = O.rms_norm(s.reshape(5, 320), wt, 1e-6, offset=True)
     assert O.max_err(y.cpu().numpy(), want.reshape(-1)) <= 1e-5
     assert np.array_equal(bf16_bits(yb), f32_to_bf16_bits(y.cpu().numpy()))
+
+
+@pytest.mark.parametrize("fmt,n,k,m", [(NV, 128, 256, 3), (NV, 256, 256, 40), (F8, 96, 256, 5), (Q4, 64, 512, 20)])
+def test_payload_off_the_16_byte_grid_takes_the_exact_kernel(b, fmt, n, k, m):
+    """A payload that starts 8 bytes into a buffer is a legal view: linear_act reports the rounding
+    of the per-element kernel (none) and linear serves it, instead of a fast path failing late."""
+    r = O.Rng(0xa11)
+    payload = r.random_weight(FMT_O[fmt], n, k)
+    raw = np.concatenate([np.zeros(8, np.uint8), payload])
+    buf = b.upload_bytes(raw)
+    view = WeightView.full(buf[8:], fmt, n, k).with_act(ActPolicy.allow_a4(600.0))
+    assert view.buf.data_ptr() % 16 == 8
+    act = b.linear_act(view, m)
+    assert act.kind == ActQuant.EXACT
+    x = r.vec(m * k, 1.0)
+    y = b.alloc(m * n)
+    b.linear(b.upload(x), view, y, m)
+    want = oracle_linear(x, payload, fmt, n, k, 0, n, m, act)
+    e_conf, e_rms = both_metrics(y.cpu().numpy().reshape(m, n), want)
+    assert e_conf <= LINEAR_TOL and e_rms <= RMS_TOL, (e_conf, e_rms)

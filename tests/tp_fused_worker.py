@@ -121,7 +121,7 @@ def main() -> None:
     whole = LinearStack(b, spec, max_tokens=m, rank=0, world=1, a4=True, seed=5).forward(xb, m).float().clone()
     err_nccl = rel_rms(ref, whole)
     assert err_nccl <= 0.08, ("all-reduce step vs unsharded", err_nccl)
-    for mode in ("flags", "barrier"):
+    for mode in ("flags", "kernel", "barrier"):
         assert stack.enable_fused_tp(m, sync_mode=mode)
         if mode == "flags":
             check_phases(b, stack, xb, rank, world)

@@ -61,6 +61,7 @@ SIGNATURES = {
     "velox_sm100_tp_step_begin": (_I, [_VP]),
     "velox_sm100_tp_wait": (_I, [_VP]),
     "velox_sm100_tp_signal": (_I, [_VP]),
+    "velox_sm100_tp_barrier": (_I, [_VP]),
     "velox_sm100_tp_set_wait_limit_ms": (_I, [_I]),
     "velox_sm100_tp_linears_q4": (_I, [_VP, _VP, _F, _VP, _I, _I, _VP]),
     "velox_sm100_tp_linear_swiglu_q4_to_q4": (_I, [_VP, _VP, _F, _PV, _PV, _I, _VP, _VP, _VP, _F, _VP]),

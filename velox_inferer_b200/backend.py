@@ -348,6 +348,10 @@ class Sm100Backend:
         self._bind()
         status(self.lib.velox_sm100_tp_wait(C.byref(sync)), "sm100 tp_wait")
 
+    def tp_barrier(self, sync) -> None:
+        self._bind()
+        status(self.lib.velox_sm100_tp_barrier(C.byref(sync)), "sm100 tp_barrier")
+
     def tp_signal(self, sync) -> None:
         self._bind()
         status(self.lib.velox_sm100_tp_signal(C.byref(sync)), "sm100 tp_signal")

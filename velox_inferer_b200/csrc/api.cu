@@ -73,6 +73,8 @@ TimedRegion::~TimedRegion() {
 
 int check_view(const velox_sm100_view* v) {
     if (!v || !v->w) return VELOX_ERR_SHAPE;
+    // (the per-tensor divisor and the row scales are read as aligned words by every kernel)
+    if (reinterpret_cast<uintptr_t>(v->w) & 3) return VELOX_ERR_UNSUPPORTED;
     if (v->n <= 0 || v->k <= 0) return VELOX_ERR_SHAPE;
     switch (v->format) {
         case VELOX_FMT_NVFP4:
@@ -101,37 +103,47 @@ struct Plan {
 // Kernel and activation rounding for one view at m rows. The rounding never exceeds the view's
 // policy (crates/velox-conformance/src/lib.rs:64-74): bf16 is always permitted; FP8 rows need
 // AllowA8 or AllowA4; NVFP4 activations need AllowA4 and use its divisor.
-static int fp8_tc_min_m() {
-    static const int v = []() {
-        const char* e = getenv("VELOX_SM100_FP8_TC_MIN_M");
-        return e && atoi(e) > 0 ? atoi(e) : 2;
-    }();
-    return v;
+// FP8 rows at decode width: from this many tokens on the tensor-core kernel (quantiser launch + MMA)
+// beats the unpacking GEMV, measured on [14336, 4096] (17.5 us against 21 us at one token, 24 against
+// 21 at two).
+constexpr int FP8_TC_MIN_M = 2;
+
+static int device_sms() {
+    static int sms[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (sms[dev] == 0) {
+        int n = 0;
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        sms[dev] = n > 0 ? n : 148;
+    }
+    return sms[dev];
 }
 
-// 17 <= m <= 64: true where the byte-balanced streaming kernel is expected to beat the GEMM.
-// VELOX_SM100_SMALL_BATCH = "stream" / "gemm" forces one of them.
+// 17 <= m <= 64: true where the byte-balanced streaming kernel is expected to beat the GEMM. Both
+// models are per-SM rates measured on B200, scaled by the SM count of the device at hand: a CTA of
+// the GEMM streams the K of its tile at about 68 GB/s, the streaming kernel moves about 32 GB/s per
+// SM with every SM busy, plus 3 us of fixed cost and 0.35 us per token of fix-up and stores.
 static bool small_batch_streams(const velox_sm100_view& v, int m) {
-    static const int forced = []() {
-        const char* e = getenv("VELOX_SM100_SMALL_BATCH");
-        return !e ? 0 : !strcmp(e, "stream") ? 1 : !strcmp(e, "gemm") ? 2 : 0;
-    }();
-    if (forced) return forced == 1;
+    const int sms = device_sms();
     const double row_bytes = v.format == VELOX_FMT_NVFP4 ? 0.5625 * (double)v.k : (double)v.k;
     const long long gemm_tiles = (v.rows + 255) / 256;
-    const double gemm_us = (double)((gemm_tiles + 147) / 148) * 256.0 * row_bytes / 68e3;   // one CTA: about 68 GB/s
-    const double stream_us = (double)v.rows * row_bytes / 4.7e6 + 3.0 + 0.35 * m;           // all SMs: about 4.7 TB/s
+    const double gemm_us = (double)((gemm_tiles + sms - 1) / sms) * 256.0 * row_bytes / 68e3;
+    const double stream_us = (double)v.rows * row_bytes / (31.8e3 * sms) + 3.0 + 0.35 * m;
     return gemm_us > stream_us;
 }
 
 static Plan plan_for(const velox_sm100_view& v, int m) {
     Plan p{PATH_GENERIC, VELOX_ACT_EXACT, 0.0f};
     if (v.k % 64 != 0) return p;
+    // Every fast path reads the payload with 16-byte accesses (tensor maps, vector loads). A payload
+    // that does not start on such a boundary (cudaMalloc gives 256) is still a legal view: it takes
+    // the per-element kernel, and linear_act says so up front.
+    if (reinterpret_cast<uintptr_t>(v.w) & 15) return p;
     if (m <= 16) {
         // Decode. Where the view admits NVFP4 activations the stored bytes go to the block-scaled
         // tensor cores as they are; otherwise bf16 activations and the unpacking GEMV.
-        if (v.format == VELOX_FMT_NVFP4 && v.policy == VELOX_POLICY_ALLOW_A4 && v.divisor > 0.0f && gemm_available() &&
-            !getenv("VELOX_SM100_DECODE_BF16")) {
+        if (v.format == VELOX_FMT_NVFP4 && v.policy == VELOX_POLICY_ALLOW_A4 && v.divisor > 0.0f && gemm_available()) {
             p.path = PATH_GEMV_TC;
             p.act = VELOX_ACT_NVFP4;
             p.divisor = v.divisor;
@@ -139,7 +151,7 @@ static Plan plan_for(const velox_sm100_view& v, int m) {
         }
         // (for a single token the unpacking GEMV still wins against quantiser + tensor-core launch)
         if (v.format == VELOX_FMT_FP8_ROW_BF16 && v.policy != VELOX_POLICY_A16_ONLY && v.k % 128 == 0 &&
-            m >= fp8_tc_min_m() && gemm_available() && !getenv("VELOX_SM100_DECODE_BF16")) {
+            m >= FP8_TC_MIN_M && gemm_available()) {
             p.path = PATH_GEMV_TC;
             p.act = VELOX_ACT_FP8_ROW;
             return p;
@@ -189,6 +201,7 @@ static Plan plan_for(const velox_sm100_view& v, int m) {
 static Plan plan_swiglu(const velox_sm100_view& both, const velox_sm100_view& gate,
                         const velox_sm100_view& up, int m) {
     Plan p = plan_for(both, m);
+    if (reinterpret_cast<uintptr_t>(up.w) & 15) return Plan{PATH_GENERIC, VELOX_ACT_EXACT, 0.0f};
     if ((p.path == PATH_GEMM_A4 || p.path == PATH_GEMV_TC) && (gate.row_begin - up.row_begin) % 128 != 0) {
         p.path = p.path == PATH_GEMV_TC && m <= 16 ? PATH_GEMV : PATH_GEMM_BF16;
         p.act = VELOX_ACT_BF16;

@@ -110,7 +110,7 @@ dequant_rows_kernel(const uint8_t* __restrict__ w, long long n, long long k, lon
 template <typename OUT>
 static int launch_dequant(const velox_sm100_view* v, OUT* out, long long ld_out, long long lo_offset,
                           const uint32_t* ids = nullptr, int count = 0) {
-    if (v->k % 16 != 0) return VELOX_ERR_UNSUPPORTED;
+    if (v->k % 16 != 0 || (reinterpret_cast<uintptr_t>(v->w) & 15)) return VELOX_ERR_UNSUPPORTED;   // 16-byte loads
     const int rows = ids ? count : v->rows;
     const long long total = (long long)rows * (v->k / 16);
     long long blocks = (total + 255) / 256;

@@ -316,8 +316,7 @@ __global__ void __launch_bounds__(QM_WARPS * 32, QM_WARPS == 8 ? (NB == 1 ? 3 : 
 }
 
 int gemv_q4k_mma(const LinearArgs& a) {
-    static const bool off = getenv("VELOX_SM100_Q4K_SIMT") != nullptr;
-    if (off || a.w.format != VELOX_FMT_GGML_Q4_K || a.w.k % 256 != 0 || a.m < 1 || a.m > 16 ||
+    if (a.w.format != VELOX_FMT_GGML_Q4_K || a.w.k % 256 != 0 || a.m < 1 || a.m > 16 ||
         a.w.rows < 1 || (reinterpret_cast<uintptr_t>(a.w.w) & 15))
         return VELOX_ERR_UNSUPPORTED;
     const long long k = a.w.k;
@@ -362,9 +361,7 @@ int gemv_q4k_mma(const LinearArgs& a) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
-    static const int forced_mt = getenv("VELOX_SM100_Q4K_ROW_TILES") ? atoi(getenv("VELOX_SM100_Q4K_ROW_TILES")) : 0;
-    const bool one = forced_mt ? forced_mt == 1
-                               : ((a.w.rows + 31) / 32 < 6LL * sms && (size_t)a.m * k * sizeof(uint16_t) <= 160 * 1024);
+    const bool one = (a.w.rows + 31) / 32 < 6LL * sms && (size_t)a.m * k * sizeof(uint16_t) <= 160 * 1024;
     const unsigned blocks = (unsigned)((a.w.rows + (one ? 16 : 32) - 1) / (one ? 16 : 32));
     // Up to eight tokens: four K parts per block, loads at the top of each block of K (72 registers,
     // seven blocks per SM). More tokens: the next block's weight bytes are requested a block ahead,

@@ -55,6 +55,13 @@ __global__ void tp_signal_kernel(const TpSync s) {
     tp_signal(s, 1u);
 }
 
+// One thread: raises this rank's flag on every rank, then waits for every rank's flag - a barrier
+// between two phases of the step as a kernel of its own, with the bounded wait of the in-kernel form.
+__global__ void tp_barrier_kernel(const TpSync s) {
+    tp_signal(s, 1u);
+    tp_wait_flags(s);
+}
+
 static std::mutex g_tp_mu;
 static int* tp_status_ptr() {
     static int* ptrs[64] = {};
@@ -123,6 +130,15 @@ int velox_sm100_tp_wait(const velox_sm100_tp_sync* sync) {
     if (rc != 0) return rc;
     s.signal_phase = -1;
     tp_wait_kernel<<<1, 1, 0, stream()>>>(s);
+    return launch_status();
+}
+
+int velox_sm100_tp_barrier(const velox_sm100_tp_sync* sync) {
+    if (!sync || sync->wait_phase < 0 || sync->signal_phase != sync->wait_phase) return VELOX_ERR_SHAPE;
+    TpSync s;
+    int rc = tp_sync_fill_elementwise(&s, sync);
+    if (rc != 0) return rc;
+    tp_barrier_kernel<<<1, 1, 0, stream()>>>(s);
     return launch_status();
 }
 

@@ -130,10 +130,14 @@ class TpFabric:
     this process (torch symmetric memory: cuMem allocations exchanged once at set-up), so kernels
     store into them with ordinary addresses.
 
-    Ordering between ranks: every kernel that writes into other ranks' memory raises a flag there
-    when it is done, every kernel that reads such data polls its own flags first (bounded waits,
-    include/velox_sm100.h). ``sync_mode="barrier"`` uses signal-pad barrier kernels between the
-    phases instead (the form the flags replaced; kept for comparison)."""
+    Ordering between ranks, ``sync_mode``:
+    ``"flags"``: every kernel that writes into other ranks' memory raises a flag there when it is
+    done, every kernel that reads such data polls its own flags first;
+    ``"kernel"``: the same flags raised and awaited by a one-thread barrier kernel between the
+    phases (the data kernels carry no waits);
+    ``"barrier"``: torch's signal-pad barrier kernels between the phases (kept for comparison; its
+    device-side wait is not bounded).
+    The first two use bounded waits that report through the status word (include/velox_sm100.h)."""
 
     PHASES_PER_LAYER = 4    # norm -> q|k|v, o -> norm, norm -> gate|up, down -> norm
 
@@ -144,7 +148,7 @@ class TpFabric:
         from . import _lib
 
         assert m % (world * 128) == 0 and world <= 8
-        assert sync_mode in ("flags", "barrier")
+        assert sync_mode in ("flags", "kernel", "barrier")
         self.rank, self.world, self.m, self.hidden = rank, world, m, hidden
         self.sync_mode = sync_mode
         self.rows = m // world                               # token rows each rank owns
@@ -190,17 +194,26 @@ class TpFabric:
             return None
         key = (wait, signal)
         if key not in self._syncs:
-            t = self._lib.TpSync()
-            for i, p in enumerate(self.flag_ptrs):
-                t.flag_tables[i] = p
-            t.epoch = self.epoch.data_ptr()
-            t.n, t.rank, t.wait_phase, t.signal_phase = self.world, self.rank, wait, signal
-            self._syncs[key] = t
+            self._syncs[key] = self._make_sync(wait, signal)
         return self._syncs[key]
 
-    def barrier(self) -> None:
-        """Barrier mode only: a signal-pad barrier kernel on the stream."""
-        if self.sync_mode == "barrier":
+    def _make_sync(self, wait: int, signal: int):
+        t = self._lib.TpSync()
+        for i, p in enumerate(self.flag_ptrs):
+            t.flag_tables[i] = p
+        t.epoch = self.epoch.data_ptr()
+        t.n, t.rank, t.wait_phase, t.signal_phase = self.world, self.rank, wait, signal
+        return t
+
+    def barrier(self, phase: int, backend: Sm100Backend) -> None:
+        """The barrier between two phases in the modes that use one: this library's flag barrier on
+        row ``phase``, or torch's signal-pad barrier."""
+        if self.sync_mode == "kernel":
+            key = ("barrier", phase)
+            if key not in self._syncs:
+                self._syncs[key] = self._make_sync(phase, phase)
+            backend.tp_barrier(self._syncs[key])
+        elif self.sync_mode == "barrier":
             self.hdl.barrier(channel=0)
 
 
@@ -313,17 +326,17 @@ class LinearStack:
         x_own.copy_(src[: rows * h] if own_rows_only else src[r0 * h:(r0 + rows) * h])
         hq = (f.codes, f.atoms)
         flags = f.sync_mode == "flags"
-        if flags:
+        if f.sync_mode != "barrier":
             b.tp_step_begin(f.epoch)
         nslots = 0
         for op, li, wait, signal in fused_step_schedule(len(self.layers)):
-            sync = f.sync(wait, signal)
+            sync = f.sync(wait, signal)                   # None unless the kernels carry the flags themselves
             l = self.layers[li] if li < len(self.layers) else None
             if op == "norm":
                 b.tp_norm_q4(x_own, f.slots, nslots, rows * h, self.norm_w, f.codes_ptrs, f.atoms_ptrs, r0, rows, h,
                              s.norm_eps, DIV_NORM_OUT, sync=sync)
                 nslots = world
-                f.barrier()                               # (barrier mode) every rank's rows of the blob are in place
+                f.barrier(signal, b)                      # every rank's rows of the blob are in place
             elif op == "qkv":
                 self._qkv(l, hq, m, True, sync=sync)
             elif op == "gate_up":
@@ -333,13 +346,13 @@ class LinearStack:
                     b.linear_swiglu_q4_to_q4(hq, DIV_NORM_OUT, l.gate, l.up, m, self.gq, DIV_DOWN_IN)
             elif op == "o_scatter":
                 b.tp_linear_q4_scatter(self.qq, DIV_O_IN, l.o, m, f.maps, rows, sync=sync)
-                f.barrier()                               # (barrier mode) all partial sums of o have landed
+                f.barrier(signal, b)                      # all partial sums of o have landed
             elif op == "down_scatter":
                 b.tp_linear_q4_scatter(self.gq, DIV_DOWN_IN, l.down, m, f.maps, rows, sync=sync)
-                f.barrier()
+                f.barrier(signal, b)
             elif op == "finish":
                 b.tp_finish(x_own, f.slots, world, rows * h, f.out_ptrs, r0, rows, h, sync=sync)
-                f.barrier()
+                f.barrier(signal, b)
             elif op == "wait" and flags:
                 b.tp_wait(sync)                           # every rank's rows of the output are in place
         self.launches_per_step = b.launch_count() - launches0
