@@ -193,7 +193,7 @@ def tp_check(b, args, rank, world, m):
     import torch
     import torch.distributed as dist
 
-    from velox_inferer_b200.stack import LinearStack, StackSpec
+    from velox_inferer_b200.stack import ChunkedStack, LinearStack, StackSpec
 
     spec = StackSpec(layers=2)
     gen = torch.Generator().manual_seed(4321)
@@ -215,6 +215,16 @@ def tp_check(b, args, rank, world, m):
             torch.cuda.synchronize()
             fused_ok = fused_ok and bool(torch.equal(fused, gathered)) and b.debug_status() == 0
         mine = fused
+        if args.chunks > 1:
+            ch = ChunkedStack(b, spec, m, rank, world, chunks=args.chunks, seed=0)
+            ok = ch.enable_fused_tp(m, sync_mode="kernel" if args.tp == "flags" else args.tp)
+            for _ in range(2):
+                chunked = ch.forward_fused_tp(xb).view(-1)[:n].clone()
+                torch.cuda.synchronize()
+                ok = ok and bool(torch.equal(chunked, gathered)) and b.debug_status() == 0
+            fused_ok = fused_ok and ok
+            out["chunks"] = args.chunks
+            del ch
     else:
         mine = gathered
     flag = torch.tensor([1 if fused_ok in (True, None) else 0], device=b.device)
@@ -261,6 +271,9 @@ def main():
                          "'fused' is the same), by one-thread flag-barrier kernels between the phases (kernel), "
                          "by torch's signal-pad barrier kernels (barrier); or one NCCL all-reduce after o and "
                          "down (nccl)")
+    ap.add_argument("--chunks", type=int, default=1,
+                    help="N > 1, fused step: token chunks that run side by side on streams of their own, so that one "
+                         "chunk's transfers overlap another's compute (1: the whole step as one chain)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
@@ -275,7 +288,7 @@ def main():
     import torch.distributed as dist
 
     from velox_inferer_b200 import Sm100Backend
-    from velox_inferer_b200.stack import LinearStack, StackSpec
+    from velox_inferer_b200.stack import ChunkedStack, LinearStack, StackSpec
 
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -301,7 +314,11 @@ def main():
         if not check["ok"]:
             raise SystemExit(f"[bench] the sharded step failed its correctness check: {check}")
 
-    stack = LinearStack(b, spec, max_tokens=m, rank=rank, world=world, a4=True, seed=0)
+    chunked = world > 1 and args.tp != "nccl" and args.chunks > 1 and m % (args.chunks * world * 128) == 0
+    if chunked:
+        stack = ChunkedStack(b, spec, m, rank, world, chunks=args.chunks, seed=0)
+    else:
+        stack = LinearStack(b, spec, max_tokens=m, rank=rank, world=world, a4=True, seed=0)
     gen = torch.Generator().manual_seed(1234)
     x_host = torch.randn(m, spec.hidden, generator=gen).to(torch.bfloat16).pin_memory()
     y_host = torch.empty(m, spec.hidden, dtype=torch.bfloat16).pin_memory()
@@ -315,7 +332,7 @@ def main():
     fused_tp = False
     if world > 1 and args.tp != "nccl":
         try:
-            fused_tp = stack.enable_fused_tp(m, sync_mode=args.tp)
+            fused_tp = stack.enable_fused_tp(m, sync_mode="kernel" if chunked and args.tp == "flags" else args.tp)
         except Exception as exc:  # symmetric memory not available here: the NCCL step still is
             print(f"[bench] fused tensor parallelism not available ({exc}); using NCCL all-reduce",
                   file=sys.stderr, flush=True)
@@ -388,23 +405,25 @@ def main():
     #      step reads only this rank's token rows and every rank ends with the whole output, so a rank
     #      copies its own rows in and out (the job moves each byte once). ----
     own = fused_tp and world > 1
-    rows = m // world if own else m
-    r0 = rank * rows if own else 0
-    x_src = x_host[r0:r0 + rows]
-    y_dst = y_host[r0:r0 + rows]
-    x_in = x_dev.view(-1)[r0 * spec.hidden:(r0 + rows) * spec.hidden]
+    nchunks = args.chunks if chunked else 1
+    mc = m // nchunks
+    rows = mc // world if own else m          # rows of each chunk this rank copies
+    spans = [(c * mc + rank * rows, rows) for c in range(nchunks)] if own else [(0, m)]
+    h = spec.hidden
+    result = (lambda: stack.out) if chunked else (lambda: stack.fabric.out if fused_tp else stack.outb)
 
     def e2e_pass(with_step):
         barrier()
         e0.record()
         for _ in range(args.steps):
-            x_in.copy_(x_src.view(-1), non_blocking=True)
+            for r0, n in spans:
+                x_dev.view(-1)[r0 * h:(r0 + n) * h].copy_(x_host[r0:r0 + n].view(-1), non_blocking=True)
             if with_step:
-                out = (step() or (stack.fabric.out if fused_tp else stack.outb)) if use_graph else forward()
+                out = (step() or result()) if use_graph else forward()
             else:
-                out = stack.fabric.out if fused_tp else stack.outb
-            y_dst.copy_(out.view(-1)[r0 * spec.hidden:(r0 + rows) * spec.hidden].view(rows, spec.hidden),
-                        non_blocking=True)
+                out = result()
+            for r0, n in spans:
+                y_host[r0:r0 + n].copy_(out.view(-1)[r0 * h:(r0 + n) * h].view(n, h), non_blocking=True)
         e1.record()
         barrier()
         tt = torch.tensor([e0.elapsed_time(e1) / args.steps], device=b.device)
@@ -470,6 +489,8 @@ def main():
     roofline["eager_step_ms"] = {k: round(timed[k][0] / args.steps, 3) for k in ("gemm_nvfp4", "gemv", "norm")
                                  if timed[k][1] > 0}
     cfg = workload_config(args, spec, m, args.tp if fused_tp else False)
+    if chunked:
+        cfg["parallelism"] += f"; the step's tokens run as {nchunks} chunks side by side on streams of their own"
     if check is not None:
         cfg["tp_check"] = check
     line = {
@@ -479,8 +500,9 @@ def main():
         "data": "synthetic", "config": cfg,
         "e2e": {"value": m / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "copy_only_ms_per_step": copy_ms,
-                "h2d_bytes_per_step": rows * spec.hidden * 2 * world, "d2h_bytes_per_step": rows * spec.hidden * 2 * world,
-                "copies": (f"each of the {world} ranks copies its own {rows} token rows in and out" if own
+                "h2d_bytes_per_step": sum(n for _, n in spans) * h * 2 * world,
+                "d2h_bytes_per_step": sum(n for _, n in spans) * h * 2 * world,
+                "copies": (f"each of the {world} ranks copies its own {rows * nchunks} token rows in and out" if own
                            else "the whole step input in, the whole output out")},
         "gpu_launches": int(launches), "cuda_graph": bool(use_graph), "clocks": clocks, "roofline": roofline,
         "tflops_per_gpu": per_rank_flops / (ms * 1e-3) / 1e12,

@@ -7,7 +7,8 @@ Exact checks, phase by phase and for whole steps:
   * the residual after the fused norm is the f32 sum, in rank order, of the slots, and the NVFP4 blob
     every rank holds afterwards is the oracle's quantiser applied to the norm's bf16 result;
   * whole steps of `forward_fused_tp` equal `forward_gathered` (library all-gather, same arithmetic)
-    bit for bit, repeatedly, and every rank ends with the same output;
+    bit for bit, repeatedly, and every rank ends with the same output; so do the same steps run as
+    two token chunks on streams of their own;
 and, because a sharded step rounds each shard's partial sums to bf16, a statistical check against the
 unsharded step on one GPU."""
 import os
@@ -21,7 +22,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from oracle import oracle as O  # noqa: E402
 from velox_inferer_b200 import Sm100Backend  # noqa: E402
-from velox_inferer_b200.stack import (DIV_NORM_OUT, DIV_O_IN, LinearStack, StackSpec, fused_step_schedule)  # noqa: E402
+from velox_inferer_b200.stack import (DIV_NORM_OUT, DIV_O_IN, ChunkedStack, LinearStack, StackSpec,
+                                      fused_step_schedule)  # noqa: E402
 
 
 def rel_rms(a, c):
@@ -155,6 +157,27 @@ def main() -> None:
         for o in others:
             assert torch.equal(o, mine)
         dist.barrier()
+    # the same step as two token chunks side by side on streams of their own, eagerly and as a graph
+    chunked = ChunkedStack(b, spec, m, rank, world, chunks=2, seed=5)
+    assert chunked.enable_fused_tp(m, sync_mode="kernel")
+    for _ in range(3):
+        got = chunked.forward_fused_tp(xb).clone()
+        torch.cuda.synchronize()
+        assert b.debug_status() == 0
+        assert torch.equal(got[: m * spec.hidden], exact.view(-1)[: m * spec.hidden]), "chunked"
+    dist.barrier()
+    side = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        chunked.forward_fused_tp(xb)
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    assert b.debug_status() == 0
+    assert torch.equal(chunked.out[: m * spec.hidden], exact.view(-1)[: m * spec.hidden]), "chunked graph"
+    graph.reset()
+    del graph
+    dist.barrier()
     if rank == 0:
         print("TP_FUSED_OK", world, err, err_nccl, flush=True)
     torch.cuda.synchronize()

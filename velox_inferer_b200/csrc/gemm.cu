@@ -224,6 +224,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem = *tmem_slot_ptr;
 
+    // Registers follow the work: the four warps that only issue copies and MMAs and the four that
+    // move scales give most of theirs back, and the eight epilogue warps take them, so that a
+    // warp can hold its whole part of the accumulator (128 values) at once and hands tensor memory
+    // back after one round trip instead of four.
+    // (each role executes the instruction at the head of its own branch: every warp of a group of
+    // four the same one)
+#define VX_REGS_ISSUE() asm volatile("setmaxnreg.dec.sync.aligned.u32 48;" ::: "memory")
+#define VX_REGS_MOVER() asm volatile("setmaxnreg.dec.sync.aligned.u32 80;" ::: "memory")
+#define VX_REGS_EPILOGUE() asm volatile("setmaxnreg.inc.sync.aligned.u32 192;" ::: "memory")
+
     // Work units: tiles of 128 x CG tokens by 256 weight rows, walked by CTA (pair) number.
     const int unit = CG == 2 ? (int)blockIdx.x / 2 : (int)blockIdx.x;
     const int units = (int)gridDim.x / CG;
@@ -267,6 +277,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     if (warp == 0) {
         // ---------------- operand producer: this CTA's x tile and W rows per k-block ----------------
         // (whole warp in the loop, one elected lane issuing, as in the MMA warp below)
+        VX_REGS_ISSUE();
         {
             int stage = 0;
             uint32_t phase = 0;
@@ -340,6 +351,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
     } else if (warp == 1 && rank != 0) {
         // ---------------- pair, second CTA: tell the MMA issuer when this CTA's operands have landed ----------------
+        VX_REGS_ISSUE();
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
@@ -363,6 +375,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // The whole warp walks the loop and one elected lane issues: addresses, descriptors and
         // barrier operands are then warp-uniform values, which is what the asynchronous tensor
         // instructions take; a loop run by a single diverged lane pays a register move per operand.
+        VX_REGS_ISSUE();
         {
             int stage = 0, sstage = 0;
             uint32_t phase = 0, sphase = 0, acc_phase = 0;
@@ -426,6 +439,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
     } else if (warp >= EPI_WARP0 && warp < EPI_WARP0 + 8) {
         // ---------------- epilogue: eight warps, two per lane quadrant, each taking half the columns ----------------
+        VX_REGS_EPILOGUE();
         const int quad = warp % 4;
         const int hsel = (warp - EPI_WARP0) / 4;
         uint32_t acc_phase = 0;
@@ -545,18 +559,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 // per chunk), release tensor memory so the next tile's MMAs can start, and only then
                 // spend time on shared-memory staging and the tensor-map stores.
                 uint32_t pk[MINE][16];
+                {
+                    uint32_t r[MINE][32], r2[SWIGLU ? MINE : 1][32];
 #pragma unroll
-                for (int i = 0; i < MINE; i++) {
-                    const int ch = hsel * MINE + i;
-                    uint32_t r[32], r2[32];
-                    float v[32];
-                    tc_ld32(taddr + ch * 32, r);
-                    if (SWIGLU) tc_ld32(taddr + 128 + ch * 32, r2);
+                    for (int i = 0; i < MINE; i++) {
+                        const int ch = hsel * MINE + i;
+                        tc_ld32(taddr + ch * 32, r[i]);
+                        if (SWIGLU) tc_ld32(taddr + 128 + ch * 32, r2[SWIGLU ? i : 0]);
+                    }
                     tc_wait_ld();
-                    if (i == MINE - 1) release_acc();
-                    compute(ch, r, SWIGLU ? r2 : r, v);
+                    release_acc();
 #pragma unroll
-                    for (int c = 0; c < 16; c++) pk[i][c] = pack_bf16(v[2 * c], v[2 * c + 1]);
+                    for (int i = 0; i < MINE; i++) {
+                        float v[32];
+                        compute(hsel * MINE + i, r[i], SWIGLU ? r2[SWIGLU ? i : 0] : r[i], v);
+#pragma unroll
+                        for (int c = 0; c < 16; c++) pk[i][c] = pack_bf16(v[2 * c], v[2 * c + 1]);
+                    }
                 }
                 if (emit_q) {
                     // The output as the next linear's NVFP4 activations, quantised from the bf16
@@ -647,16 +666,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 }
                 }
             } else {
+                uint32_t r[MINE][32], r2[SWIGLU ? MINE : 1][32];
+#pragma unroll
                 for (int i = 0; i < MINE; i++) {
                     const int ch = hsel * MINE + i;
-                    uint32_t r[32], r2[32];
+                    tc_ld32(taddr + ch * 32, r[i]);
+                    if (SWIGLU) tc_ld32(taddr + 128 + ch * 32, r2[SWIGLU ? i : 0]);
+                }
+                tc_wait_ld();
+                release_acc();
+#pragma unroll
+                for (int i = 0; i < MINE; i++) {
                     float v[32];
-                    tc_ld32(taddr + ch * 32, r);
-                    if (SWIGLU) tc_ld32(taddr + 128 + ch * 32, r2);
-                    tc_wait_ld();
-                    if (i == MINE - 1) release_acc();
-                    compute(ch, r, SWIGLU ? r2 : r, v);
-                    store_direct(ch, v);
+                    compute(hsel * MINE + i, r[i], SWIGLU ? r2[SWIGLU ? i : 0] : r[i], v);
+                    store_direct(hsel * MINE + i, v);
                 }
             }
             acc_phase ^= 1u;
@@ -672,6 +695,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     } else if (KIND == KIND_MXF4 && warp == 2) {
         // ---------------- scale producer: whole 512-byte atoms, x then the two W halves ----------------
         // (in a pair each CTA needs the scales of its own tokens and of all 256 weight rows)
+        VX_REGS_ISSUE();
         {
             int stage = 0;
             uint32_t phase = 0;
@@ -726,6 +750,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // Lane i of the warp serving lane quadrant q writes rows i, i+32, i+64, i+96 of each
         // 128-row atom: the 16 bytes of atom row i are the four 32-bit columns of that atom,
         // replicated in every quadrant as the block-scaled MMA reads them.
+        VX_REGS_MOVER();
         const int quad = warp % 4;
         int stage = 0;
         uint32_t phase = 0;
@@ -777,6 +802,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
         }
     }
+
+    else if (warp < 4) {
+        VX_REGS_ISSUE();       // warps without a role in this form of the kernel
+    } else {
+        VX_REGS_MOVER();
+    }
+#undef VX_REGS_ISSUE
+#undef VX_REGS_MOVER
+#undef VX_REGS_EPILOGUE
 
     // Nobody leaves while the partner may still signal this CTA's barriers or read its shared memory.
     tc_fence_before();

@@ -427,7 +427,10 @@ int gemv(const LinearArgs& a) {
             if (rc != VELOX_ERR_UNSUPPORTED) return rc;
         }
             return a.swiglu ? gemv_fmt<VELOX_FMT_NVFP4, true>(a) : gemv_fmt<VELOX_FMT_NVFP4, false>(a);
-        case VELOX_FMT_FP8_ROW_BF16:
+        case VELOX_FMT_FP8_ROW_BF16: {
+            const int rc = gemv_fp8_mma(a);
+            if (rc != VELOX_ERR_UNSUPPORTED) return rc;
+        }
             return a.swiglu ? gemv_fmt<VELOX_FMT_FP8_ROW_BF16, true>(a)
                             : gemv_fmt<VELOX_FMT_FP8_ROW_BF16, false>(a);
         case VELOX_FMT_GGML_Q4_K: {

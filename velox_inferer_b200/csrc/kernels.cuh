@@ -71,6 +71,8 @@ int add_rms_norm_twin(float* acc, const float* x, const uint16_t* xb, const floa
 int bf16_twin(const float* x, uint16_t* xb, long long len);
 // Q4_K decode on the warp-level tensor-core MMA (plain form, m <= 16, k % 256 == 0); else VELOX_ERR_UNSUPPORTED.
 int gemv_q4k_mma(const LinearArgs& a);
+// FP8-row decode with bf16 activations on the same MMA (2 <= m <= 16, k % 64 == 0); else VELOX_ERR_UNSUPPORTED.
+int gemv_fp8_mma(const LinearArgs& a);
 int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
                uint8_t* const* codes, uint8_t* const* atoms, int ndst, long long row0, int rows, int dim, float eps,
                int offset, float divisor, const velox_sm100_tp_sync* sync);

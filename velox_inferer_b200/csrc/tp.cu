@@ -55,11 +55,31 @@ __global__ void tp_signal_kernel(const TpSync s) {
     tp_signal(s, 1u);
 }
 
-// One thread: raises this rank's flag on every rank, then waits for every rank's flag - a barrier
-// between two phases of the step as a kernel of its own, with the bounded wait of the in-kernel form.
+// A barrier between two phases of the step as a kernel of its own (one warp): lane r raises this
+// rank's flag on rank r with a release store (the writes of the kernels ahead in the stream come
+// before it) and then waits, bounded like every wait here, for rank r's flag on this rank. The ranks
+// are served side by side, so the barrier costs one round trip over the links, not one per rank.
 __global__ void tp_barrier_kernel(const TpSync s) {
-    tp_signal(s, 1u);
-    tp_wait_flags(s);
+    const int r = (int)threadIdx.x;
+    if (r < s.n) {
+        const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(s.epoch);
+        const long long at = (long long)s.wait_phase * TP_FLAG_STRIDE;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<unsigned int*>(s.flags[r]) + at + s.rank),
+                     "r"(want)
+                     : "memory");
+        const unsigned int* mine = reinterpret_cast<const unsigned int*>(s.flags[s.rank]) + at + r;
+        const unsigned long long t0 = tp_timer_ns();
+        unsigned int spins = 0, seen;
+        for (;;) {
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if ((int)(seen - want) >= 0) break;
+            if ((++spins & 63u) == 0 && tp_timer_ns() - t0 > s.limit_ns) {
+                atomicExch(s.status, ST_TIMEOUT_PEER);
+                break;
+            }
+        }
+    }
+    __syncwarp();
 }
 
 static std::mutex g_tp_mu;
@@ -138,7 +158,7 @@ int velox_sm100_tp_barrier(const velox_sm100_tp_sync* sync) {
     TpSync s;
     int rc = tp_sync_fill_elementwise(&s, sync);
     if (rc != 0) return rc;
-    tp_barrier_kernel<<<1, 1, 0, stream()>>>(s);
+    tp_barrier_kernel<<<1, 32, 0, stream()>>>(s);
     return launch_status();
 }
 

@@ -232,7 +232,7 @@ class LinearStack:
     """The stack on one rank of a tensor-parallel group of ``world`` ranks."""
 
     def __init__(self, backend: Sm100Backend, spec: StackSpec, max_tokens: int, rank: int = 0,
-                 world: int = 1, a4: bool = True, seed: int = 0, group=None):
+                 world: int = 1, a4: bool = True, seed: int = 0, group=None, weights_of: "LinearStack" = None):
         self.b, self.spec, self.rank, self.world, self.group = backend, spec, rank, world, group
         self.max_tokens = max_tokens
         s = spec
@@ -242,7 +242,11 @@ class LinearStack:
         pol = (lambda d: ActPolicy.allow_a4(d)) if a4 else (lambda d: ActPolicy.a16_only())
         self.layers: List[LayerWeights] = []
         gen = torch.Generator(device=dev)
-        for layer in range(s.layers):
+        if weights_of is not None:
+            # a second set of activation buffers over the same weights (token chunks of one step)
+            assert (weights_of.spec, weights_of.rank, weights_of.world, weights_of.a4) == (spec, rank, world, a4)
+            self.layers = weights_of.layers
+        for layer in range(s.layers if weights_of is None else 0):
             def make(proj: int, n: int, k: int) -> torch.Tensor:
                 gen.manual_seed(seed * 1_000_003 + layer * 16 + proj)
                 w = torch.randn(n, k, generator=gen, device=dev, dtype=torch.float32) * 0.02
@@ -447,3 +451,57 @@ class LinearStack:
         out = b.bf16_twin_into(self.x, self.outb, m * h)
         self.launches_per_step = b.launch_count() - launches0   # this library's kernels per step
         return out
+
+
+class ChunkedStack:
+    """The fused tensor-parallel step over token chunks that run side by side: the step's tokens are
+    cut into ``chunks`` equal parts, each with its own activation buffers, symmetric memory and
+    stream, all over one set of weights. A token's result does not depend on which other tokens
+    share its launch, so the outputs are those of the unchunked step bit for bit; what changes is
+    the schedule: while one chunk's row-split linear waits for its partial sums to cross the links
+    (its CTAs have exited, its stores are in flight), another chunk's kernels have the SMs. Worth it
+    where the links' time is comparable with the compute (many ranks), at the price of reading the
+    weights once per chunk."""
+
+    def __init__(self, backend: Sm100Backend, spec: StackSpec, max_tokens: int, rank: int, world: int,
+                 chunks: int = 2, seed: int = 0, group=None):
+        assert chunks >= 1 and max_tokens % (chunks * world * 128) == 0
+        self.b, self.spec, self.rank, self.world, self.chunks = backend, spec, rank, world, chunks
+        self.m = max_tokens
+        mc = max_tokens // chunks
+        first = LinearStack(backend, spec, mc, rank, world, True, seed, group)
+        self.parts = [first] + [LinearStack(backend, spec, mc, rank, world, True, seed, group, weights_of=first)
+                                for _ in range(chunks - 1)]
+        self.streams = [torch.cuda.Stream(device=backend.device) for _ in range(chunks)]
+        self.weight_bytes = first.weight_bytes
+        self.layers = first.layers
+        self.out = torch.zeros(max_tokens * spec.hidden, dtype=torch.bfloat16, device=backend.device)
+        self.launches_per_step = 0
+
+    def enable_fused_tp(self, m: int, sync_mode: str = "kernel") -> bool:
+        assert m == self.m
+        if sync_mode == "flags":
+            # Kernels that hold every SM while they wait for a peer must not share a GPU with the
+            # other chunk's kernels the peer is waiting for in turn; barriers between the phases
+            # are one-warp kernels and cannot starve anything.
+            raise ValueError("chunks run with barrier kernels between the phases ('kernel' or 'barrier')")
+        return all(p.enable_fused_tp(m // self.chunks, sync_mode) for p in self.parts)
+
+    def forward_fused_tp(self, xb_in: torch.Tensor) -> torch.Tensor:
+        """xb_in: [m, hidden] bf16 on the device; returns the whole output [m, hidden] (every rank)."""
+        h, mc = self.spec.hidden, self.m // self.chunks
+        main = torch.cuda.current_stream(self.b.device)
+        start = torch.cuda.Event()
+        start.record(main)
+        launches = 0
+        for c, (p, st) in enumerate(zip(self.parts, self.streams)):
+            st.wait_event(start)
+            with torch.cuda.stream(st):
+                out = p.forward_fused_tp(xb_in.reshape(-1)[c * mc * h:(c + 1) * mc * h])
+                self.out[c * mc * h:(c + 1) * mc * h].copy_(out.view(-1)[: mc * h])
+                done = torch.cuda.Event()
+                done.record(st)
+            main.wait_event(done)
+            launches += p.launches_per_step
+        self.launches_per_step = launches
+        return self.out
