@@ -114,6 +114,10 @@ GEMV_CASES = [
     (Q4, 100, 256, 5, 77, 11), (Q4, 72, 5120, 0, 72, 4), (Q4, 2100, 1024, 16, 2050, 2),
     (Q4, 28700, 256, 0, 28700, 3), (Q4, 28700, 512, 9, 28650, 12),
     (Q4, 48, 25600, 0, 48, 2),    # a down projection's K: eight K parts per block, the longest sums
+    # FP8 rows with bf16 activations on the MMA kernel: two row tiles per block (many rows), eight K
+    # parts (few rows, long K), one and two token tiles, ragged rows and a view off the row-tile grid
+    (F8, 38000, 128, 5, 37990, 3), (F8, 38000, 64, 0, 38000, 12), (F8, 48, 8192, 0, 48, 10),
+    (F8, 100, 4096, 7, 77, 6), (F8, 64, 64, 0, 64, 2),
 ]
 
 
@@ -142,6 +146,40 @@ def test_linear_decode_widths_match_oracle(b, fmt, n, k, begin, rows, m):
         y2 = b.alloc(m * rows)
         b.linear_bf16(b.bf16_twin(b.upload(x)), view, y2, m)
         assert np.array_equal(y2.cpu().numpy().view(np.uint32), got.reshape(-1).view(np.uint32))
+
+
+def test_fp8_decode_takes_every_code_and_a_wide_range_of_activations(b):
+    """The FP8-row decode kernel for bf16 activations re-labels E4M3 bytes as bf16 numbers: every
+    finite code (subnormals, zeros and the largest values of both signs) and activations over sixteen
+    decades must come out as the oracle's exact decode gives them."""
+    n, k, m = 64, 512, 8
+    codes = (np.arange(n * k, dtype=np.int64) * 37 % 256).astype(np.uint8)
+    codes[(codes & 0x7F) == 0x7F] = 0x06           # the two NaN codes: a subnormal instead
+    scales = (2.0 ** np.linspace(-10, 6, n)).astype(np.float32)
+    plane = (n * k + 255) // 256 * 256
+    payload = np.zeros(plane + 2 * n, dtype=np.uint8)
+    payload[: n * k] = codes
+    payload[plane:] = f32_to_bf16_bits(scales).astype("<u2").view(np.uint8)
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal(m * k) * 10.0 ** rng.uniform(-8, 8, m * k)).astype(np.float32)
+    view = make_view(b, payload, F8, n, k, 0, n)
+    act = b.linear_act(view, m)
+    assert act == ActQuant(ActQuant.BF16)
+    want = oracle_linear(x, payload, F8, n, k, 0, n, m, act)
+    y = b.alloc(m * n)
+    b.linear(b.upload(x), view, y, m)
+    got = y.cpu().numpy().reshape(m, n)
+    assert np.all(np.isfinite(got))
+    # sums of terms sixteen decades apart: held relative to the size of the terms, not of the sum
+    scale = np.abs(x.reshape(m, k)).max(axis=1)[:, None] * scales[None, :] * 448.0
+    assert np.max(np.abs(got - want) / scale) <= 1e-5
+    # and one-hot activations pick single weights: each output is one decoded weight times x, exactly
+    for col in (0, 1, 2, 3, 17, 255, 511):
+        xh = np.zeros((m, k), dtype=np.float32)
+        xh[:, col] = 2.0 ** np.arange(-3, m - 3)
+        b.linear(b.upload(xh.reshape(-1)), view, y, m)
+        w = O.decode_rows(O.FMT_FP8, payload, n, k, 0, n)[:, col]
+        assert np.array_equal(y.cpu().numpy().reshape(m, n), (xh[:, col][:, None] * w[None, :]).astype(np.float32))
 
 
 # ---- decode on the block-scaled tensor cores (views that admit NVFP4 activations) --------------
@@ -320,6 +358,7 @@ def _swiglu_want(x, payload_g, payload_u, fmt, ng, nu, k, bg, bu, w, m, act):
 @pytest.mark.parametrize("fmt,k,w,m,order", [
     (NV, 512, 256, 1, "gate_up"), (NV, 512, 256, 7, "up_gate"), (NV, 1024, 128, 16, "split"),
     (F8, 512, 96, 4, "gate_up"), (Q4, 512, 40, 3, "split"),
+    (F8, 1024, 72, 2, "up_gate"), (F8, 4096, 100, 13, "gate_up"), (F8, 64, 38000, 9, "gate_up"), (F8, 256, 50, 16, "split"),
     # Q4_K pairs on the MMA kernel: both row orders in one parent, ragged rows, one and two token tiles
     (Q4, 1024, 72, 1, "gate_up"), (Q4, 2560, 100, 8, "up_gate"), (Q4, 512, 200, 13, "gate_up"),
 ])

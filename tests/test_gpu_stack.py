@@ -37,13 +37,14 @@ def _oracle_stack(b, stack, spec, x, m):
             x = (x + pb).astype(np.float32)
         hb = _bf16(O.rms_norm(x, ones, spec.norm_eps))
         qb = _bf16(lin(hb, l.q, DIV_NORM_OUT))
+        kv = (_bf16(lin(hb, l.k, DIV_NORM_OUT)), _bf16(lin(hb, l.v, DIV_NORM_OUT)))
         pb = _bf16(lin(qb, l.o, DIV_O_IN))
         x = (x + pb).astype(np.float32)
         hb = _bf16(O.rms_norm(x, ones, spec.norm_eps))
         g, u = lin(hb, l.gate, DIV_NORM_OUT), lin(hb, l.up, DIV_NORM_OUT)
         gb = _bf16(O.swiglu(np.concatenate([g, u], axis=1), m, 2 * g.shape[1], 0, g.shape[1], g.shape[1]))
         pb = _bf16(lin(gb, l.down, DIV_DOWN_IN))
-    return _bf16((x + pb).astype(np.float32))
+    return _bf16((x + pb).astype(np.float32)), kv
 
 
 @pytest.mark.parametrize("m", [3, 40, 200])
@@ -57,8 +58,14 @@ def test_stack_matches_oracle_sequence(m):
     torch.cuda.synchronize()
     assert b.lib.velox_sm100_debug_status() == 0
     got = out[: m * spec.hidden].float().cpu().numpy().reshape(m, spec.hidden)
-    want = _oracle_stack(b, stack, spec, xb.float().cpu().numpy(), m)
+    want, (want_k, want_v) = _oracle_stack(b, stack, spec, xb.float().cpu().numpy(), m)
     # every stage rounds to bf16 (2^-9 relative); two layers of it stay within a few bf16 ulps
     err = O.max_abs_diff(got, want) / O.rms(want)
     assert err <= 2e-2, err
     assert np.mean(np.abs(got - want) <= 2.0 ** -7 * (np.abs(want) + 0.05)) > 0.999
+    # the k and v projections of the last layer (they feed nothing further in this stack): same launch
+    # as q, checked on their own
+    for buf, want_p in ((stack.kb, want_k), (stack.vb, want_v)):
+        got_p = buf[: m * spec.kv_dim].float().cpu().numpy().reshape(m, spec.kv_dim)
+        assert O.max_abs_diff(got_p, want_p) / O.rms(want_p) <= 2e-2
+        assert np.mean(np.abs(got_p - want_p) <= 2.0 ** -7 * (np.abs(want_p) + 0.05)) > 0.999

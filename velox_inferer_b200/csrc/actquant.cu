@@ -19,6 +19,7 @@ quantize_fp8row_kernel(const float* __restrict__ x, const uint16_t* __restrict__
     __shared__ float red[8];
     const long long row = blockIdx.x;
     if (threadIdx.x == 0) grid_launch_dependents();   // the linear behind this may start fetching weights
+    grid_dependency_wait();                           // (launched early itself: x, and readers of the old codes)
     float amax = 0.0f;
     for (long long c = threadIdx.x; c < k; c += blockDim.x)
         amax = fmaxf(amax, fabsf(load_act(x, xb, row * k + c)));
@@ -45,6 +46,7 @@ quantize_nvfp4_kernel(const float* __restrict__ x, const uint16_t* __restrict__ 
     const long long groups = k / 16;
     const long long total = (long long)rows_padded * groups;
     if (threadIdx.x == 0) grid_launch_dependents();   // the linear behind this may start fetching weights
+    grid_dependency_wait();                           // (launched early itself: x, and readers of the old codes)
     for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
          idx += (long long)gridDim.x * blockDim.x) {
         const long long row = idx / groups, g = idx % groups;
@@ -137,8 +139,10 @@ int quantize_act_fp8row(const float* x, const uint16_t* xb, int m, long long k, 
                         float* scales) {
     if (m < 1 || k < 1) return VELOX_ERR_SHAPE;
     TimedRegion timed(TIMED_ACT_QUANT);
-    quantize_fp8row_kernel<<<(unsigned)m, 256, 0, stream()>>>(x, xb, k, codes, scales);
-    return launch_status();
+    EarlyLaunch l((unsigned)m, 256u);
+    const cudaError_t e = cudaLaunchKernelEx(&l.cfg, quantize_fp8row_kernel, x, xb, k, codes, scales);
+    note_launch();
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 int quantize_act_nvfp4(const float* x, const uint16_t* xb, int m, long long k, float divisor,
@@ -146,9 +150,11 @@ int quantize_act_nvfp4(const float* x, const uint16_t* xb, int m, long long k, f
     if (m < 1 || k < 64 || k % 64 != 0) return VELOX_ERR_SHAPE;
     const int rows_padded = (m + 127) / 128 * 128;
     TimedRegion timed(TIMED_ACT_QUANT);
-    quantize_nvfp4_kernel<<<grid_for((long long)rows_padded * (k / 16)), 256, 0, stream()>>>(
-        x, xb, m, rows_padded, k, divisor, codes, scale_atoms);
-    return launch_status();
+    EarlyLaunch l(grid_for((long long)rows_padded * (k / 16)), 256u);
+    const cudaError_t e = cudaLaunchKernelEx(&l.cfg, quantize_nvfp4_kernel, x, xb, m, rows_padded, k, divisor, codes,
+                                             scale_atoms);
+    note_launch();
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 // The same launch without the optional event timing (which creates events): for callers that must

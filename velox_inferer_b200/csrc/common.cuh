@@ -2,6 +2,8 @@
 // decoders, the bf16 rounding the twins use, launch-stream selection and grow-only scratch.
 #pragma once
 
+#include <cstdlib>
+
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_fp4.h>
@@ -132,6 +134,24 @@ __device__ __forceinline__ float warp_max(float v) {
 // Launch stream of the calling thread.
 cudaStream_t stream();
 void set_stream(cudaStream_t s);
+
+// Launch configuration of the small kernels between the linears (norms, activation quantisers):
+// early start allowed, so the blocks become resident while the kernel ahead drains and wait for it
+// (grid_dependency_wait) before their first access. VELOX_SM100_NO_EARLY_START=1 turns it off.
+struct EarlyLaunch {
+    cudaLaunchConfig_t cfg{};
+    cudaLaunchAttribute attr[1];
+    EarlyLaunch(unsigned blocks, unsigned threads) {
+        static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
+        cfg.gridDim = dim3(blocks);
+        cfg.blockDim = dim3(threads);
+        cfg.stream = stream();
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = early ? 1 : 0;
+    }
+};
 
 // Grow-only device scratch, one pool per purpose and device. Never freed: captured CUDA graphs
 // may reference it (velox_common.cuh:49-70).

@@ -8,8 +8,8 @@
 // dequant_rows_bf16: the operand the bf16 tensor-core GEMM multiplies. NVFP4 -> e2m1*e4m3 (six
 // significant bits: exact in bf16; the 1/divisor factor is applied to the f32 accumulator), FP8 ->
 // the E4M3 value (exact; the row scale is applied to the accumulator), Q4_K -> the decoded value
-// as two bf16 terms hi + lo (hi = bf16(v), lo = bf16(v - hi)) laid side by side along K, so the
-// GEMM's f32 accumulation sees the value to about 2^-17 relative.
+// as three bf16 terms (bf16(v), bf16 of the remainder, bf16 of what is left of that) laid side by
+// side along K, so the GEMM's f32 accumulation sees the f32 value exactly.
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -92,13 +92,19 @@ dequant_rows_kernel(const uint8_t* __restrict__ w, long long n, long long k, lon
             o4[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             o4[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
             if (lo_offset > 0) {
-                // second bf16 term: the part of the value its first bf16 rounding dropped
+                // second and third bf16 term: what the roundings before dropped (each difference is
+                // exact in f32; three terms of eight bits hold the 24-bit value)
+                uint32_t third[8];
 #pragma unroll
                 for (int j = 0; j < 8; j++) {
                     const float r0 = v[2 * j] - round_bf16(v[2 * j]);
                     const float r1 = v[2 * j + 1] - round_bf16(v[2 * j + 1]);
                     packed[j] = (uint32_t)bf16_bits(r0) | ((uint32_t)bf16_bits(r1) << 16);
+                    third[j] = (uint32_t)bf16_bits(r0 - round_bf16(r0)) | ((uint32_t)bf16_bits(r1 - round_bf16(r1)) << 16);
                 }
+                uint4* t4 = reinterpret_cast<uint4*>(o + 2 * lo_offset);
+                t4[0] = make_uint4(third[0], third[1], third[2], third[3]);
+                t4[1] = make_uint4(third[4], third[5], third[6], third[7]);
                 uint4* l4 = reinterpret_cast<uint4*>(o + lo_offset);
                 l4[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 l4[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);

@@ -589,22 +589,6 @@ sp_finish_kernel(float* __restrict__ acc, const uint16_t* __restrict__ slots, in
     }
 }
 
-// Launch configuration of the step's elementwise kernels: early start allowed (the blocks become
-// resident while the kernel ahead drains and wait for it before their first access).
-struct EarlyLaunch {
-    cudaLaunchConfig_t cfg{};
-    cudaLaunchAttribute attr[1];
-    EarlyLaunch(unsigned blocks, unsigned threads) {
-        static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
-        cfg.gridDim = dim3(blocks);
-        cfg.blockDim = dim3(threads);
-        cfg.stream = stream();
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = early ? 1 : 0;
-    }
-};
 
 static int launch_norm_q4(float* acc, const float* x, const uint16_t* xb, int nslots, long long slot_stride,
                           const float* weight, uint16_t* yb, const Q4Dest& dst, long long row0, int rows,

@@ -117,6 +117,7 @@ struct GemmParams {
     const float* tok_scale;
     const CUtensorMap* out_maps;   // optional (tensor parallel): one output map per owning rank, in global memory;
     int rows_per_owner;            // token rows [o * rows_per_owner, (o + 1) * rows_per_owner) go to out_maps[o]
+    int acc_chunk;  // bf16 kind, 0 = off: k-blocks summed in tensor memory before the epilogue takes the sum over
     int early;      // the launch may start before the kernel ahead of it has finished (see the producers)
     int* status;
     PartParams part[MAX_PARTS];
@@ -164,6 +165,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const uint32_t acc_full = bars + 8u * (3 * OP_STAGES + 4 * SF_STAGES);
     const uint32_t acc_empty = acc_full + 8u;
     const uint32_t tmem_slot = acc_full + 16u;
+    // second accumulator (bf16 kind with chunked sums): buffer b's barriers and first column
+    auto cfull = [&](uint32_t b) { return acc_full + 24u * b; };
+    auto cempty = [&](uint32_t b) { return acc_empty + 24u * b; };
+    const bool chunked = KIND == KIND_BF16 && p.acc_chunk > 0;
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -198,6 +203,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
         mbar_init(acc_full, 1);
         mbar_init(acc_empty, 8 * CG);
+        mbar_init(cfull(1), 1);
+        mbar_init(cempty(1), 8 * CG);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&maps.b[0]) : "memory");
@@ -382,12 +389,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             bool ok = true;
             const uint32_t idesc = instr_desc<KIND, CG>();
             const bool leader = elect_one();
+            // Chunked sums (bf16 kind): every acc_chunk k-blocks go to the other of two accumulators and
+            // are handed to the epilogue, which adds the chunks with round-to-nearest adds. The tensor
+            // core's own f32 accumulation truncates, and over a long K that bias reaches the fourth
+            // digit of sums that cancel.
+            uint32_t chunk_no = 0, buf = 0;
             for (int tile = unit; tile < num_tiles && ok; tile += units) {
-                if (!(CG == 2 ? mbar_wait_cluster(acc_empty, acc_phase ^ 1u) : mbar_wait(acc_empty, acc_phase ^ 1u))) {
+                if (!chunked &&
+                    !(CG == 2 ? mbar_wait_cluster(acc_empty, acc_phase ^ 1u) : mbar_wait(acc_empty, acc_phase ^ 1u))) {
                     if (leader) atomicExch(p.status, ST_TIMEOUT_ACC_EMPTY);
                     break;
                 }
                 for (int kb = 0; kb < p.k_blocks; kb++) {
+                    const bool chunk_head = chunked && kb % p.acc_chunk == 0;
+                    if (chunk_head) {
+                        buf = chunk_no & 1u;
+                        const uint32_t par = ((chunk_no >> 1) & 1u) ^ 1u;
+                        if (!(CG == 2 ? mbar_wait_cluster(cempty(buf), par) : mbar_wait(cempty(buf), par))) {
+                            if (leader) atomicExch(p.status, ST_TIMEOUT_ACC_EMPTY);
+                            ok = false;
+                            break;
+                        }
+                    }
                     if (!mbar_wait(op_full(stage), phase) ||
                         (CG == 2 && !mbar_wait_cluster(peer_full(stage), phase))) {
                         if (leader) atomicExch(p.status, ST_TIMEOUT_FULL);
@@ -407,21 +430,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t sb = sa + A_BYTES;
                     const uint64_t da = smem_desc_sw128(sa), db = smem_desc_sw128(sb);
                     const uint32_t tsf = tmem + TMEM_SF_COL + sstage * TMEM_SF_SET;
+                    const uint32_t tacc = tmem + (chunked ? buf * (uint32_t)BN : 0u);
+                    const bool fresh = chunked ? chunk_head : kb == 0;   // the first MMA overwrites the accumulator
+                    const bool chunk_tail = chunked && (kb % p.acc_chunk == p.acc_chunk - 1 || kb == p.k_blocks - 1);
                     if (leader) {
                         // advancing 32 bytes along K inside the swizzle row: +2 in the address field
                         if (steps == 4) {
-                            tc_mma<KIND, CG>(tmem, da, db, idesc, kb != 0 ? 1u : 0u, tsf, tsf + 16);
-                            tc_mma<KIND, CG>(tmem, da + 2u, db + 2u, idesc, 1u, tsf + 4, tsf + 24);
-                            tc_mma<KIND, CG>(tmem, da + 4u, db + 4u, idesc, 1u, tsf + 8, tsf + 32);
-                            tc_mma<KIND, CG>(tmem, da + 6u, db + 6u, idesc, 1u, tsf + 12, tsf + 40);
+                            tc_mma<KIND, CG>(tacc, da, db, idesc, fresh ? 0u : 1u, tsf, tsf + 16);
+                            tc_mma<KIND, CG>(tacc, da + 2u, db + 2u, idesc, 1u, tsf + 4, tsf + 24);
+                            tc_mma<KIND, CG>(tacc, da + 4u, db + 4u, idesc, 1u, tsf + 8, tsf + 32);
+                            tc_mma<KIND, CG>(tacc, da + 6u, db + 6u, idesc, 1u, tsf + 12, tsf + 40);
                         } else {
                             for (int j = 0; j < steps; j++)
-                                tc_mma<KIND, CG>(tmem, da + 2u * j, db + 2u * j, idesc, (kb | j) != 0 ? 1u : 0u,
+                                tc_mma<KIND, CG>(tacc, da + 2u * j, db + 2u * j, idesc, fresh && j == 0 ? 0u : 1u,
                                                  tsf + 4 * j, tsf + 16 + 8 * j);
                         }
                         commit(op_empty(stage));
                         if (KIND == KIND_MXF4) commit(tsf_empty(sstage));
+                        if (chunk_tail) commit(cfull(buf));
                     }
+                    if (chunk_tail) chunk_no++;
                     if (++stage == OP_STAGES) {
                         stage = 0;
                         phase ^= 1u;
@@ -433,7 +461,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         }
                     }
                 }
-                if (ok && leader) commit(acc_full);
+                if (ok && leader && !chunked) commit(acc_full);
                 acc_phase ^= 1u;
             }
         }
@@ -442,7 +470,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         VX_REGS_EPILOGUE();
         const int quad = warp % 4;
         const int hsel = (warp - EPI_WARP0) / 4;
-        uint32_t acc_phase = 0;
+        uint32_t acc_phase = 0, epi_chunk = 0;
         const bool store_thread = (warp - EPI_WARP0) % 4 == 0 && lane == 0;   // one per column half
         const uint32_t my_box = staging + (uint32_t)hsel * 16384u;
         const int bar_id = 1 + hsel;                                          // the four warps of a half
@@ -459,11 +487,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const uint16_t* cs1 = pp.col_scale[1];
             const long long cs_rows0 = pp.b_rows_total[0], cs_rows1 = pp.b_rows_total[1];
             const long long vb0 = pp.valid_begin[0], ve0 = pp.valid_end[0], vb1 = pp.valid_begin[1], ve1 = pp.valid_end[1];
-            if (!mbar_wait(acc_full, acc_phase, 60)) {
-                if (lane == 0) atomicExch(p.status, ST_TIMEOUT_ACC_FULL);
-                break;
+            if (!chunked) {
+                if (!mbar_wait(acc_full, acc_phase, 60)) {
+                    if (lane == 0) atomicExch(p.status, ST_TIMEOUT_ACC_FULL);
+                    break;
+                }
+                tc_fence_after();
             }
-            tc_fence_after();
             const float s0 = p.alpha / d0, s1 = p.alpha / d1;
             const int row_in_tile = quad * 32 + lane;
             const long long token = (long long)mt * BM + row_in_tile;
@@ -547,11 +577,64 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         if (row0 + c >= vb && row0 + c < ve) pp.y[o0 + c] = v[c];
                 }
             };
-            auto release_acc = [&]() {
+            auto release_acc = [&](uint32_t b = 0u) {
                 // this warp's part of the accumulator is in registers: hand it back to the MMA issuer
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) arrive_lead(acc_empty);
+                if (lane == 0) arrive_lead(cempty(b));
+            };
+            // This warp's 128 accumulator values (SwiGLU: 64 gate + 64 up) into registers, and tensor
+            // memory handed back. Chunked sums: the chunks arrive one after the other in the two
+            // accumulators and are added here, in order, with round-to-nearest adds.
+            auto drain = [&](uint32_t (&r)[MINE][32], uint32_t (&r2)[SWIGLU ? MINE : 1][32]) -> bool {
+                if (!chunked) {
+#pragma unroll
+                    for (int i = 0; i < MINE; i++) {
+                        const int ch = hsel * MINE + i;
+                        tc_ld32(taddr + ch * 32, r[i]);
+                        if (SWIGLU) tc_ld32(taddr + 128 + ch * 32, r2[SWIGLU ? i : 0]);
+                    }
+                    tc_wait_ld();
+                    release_acc();
+                    return true;
+                }
+                const int nchunks = (p.k_blocks + p.acc_chunk - 1) / p.acc_chunk;
+#pragma unroll
+                for (int i = 0; i < MINE; i++)
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        r[i][j] = 0u;
+                        if (SWIGLU) r2[SWIGLU ? i : 0][j] = 0u;
+                    }
+#pragma unroll 1
+                for (int c = 0; c < nchunks; c++) {
+                    const uint32_t b = epi_chunk & 1u;
+                    if (!mbar_wait(cfull(b), (epi_chunk >> 1) & 1u, 60)) {
+                        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_ACC_FULL);
+                        return false;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int i = 0; i < MINE; i++) {
+                        const int ch = hsel * MINE + i;
+                        uint32_t t[32];
+                        tc_ld32(taddr + b * (uint32_t)BN + ch * 32, t);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            r[i][j] = __float_as_uint(__uint_as_float(r[i][j]) + __uint_as_float(t[j]));
+                        if (SWIGLU) {
+                            tc_ld32(taddr + b * (uint32_t)BN + 128 + ch * 32, t);
+                            tc_wait_ld();
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                r2[SWIGLU ? i : 0][j] = __float_as_uint(__uint_as_float(r2[SWIGLU ? i : 0][j]) + __uint_as_float(t[j]));
+                        }
+                    }
+                    release_acc(b);
+                    epi_chunk++;
+                }
+                return true;
             };
             const bool emit_q = pp.q_codes != nullptr && mt < p.tiles_m;
             if (staged || pp.q_codes != nullptr) {
@@ -561,14 +644,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 uint32_t pk[MINE][16];
                 {
                     uint32_t r[MINE][32], r2[SWIGLU ? MINE : 1][32];
-#pragma unroll
-                    for (int i = 0; i < MINE; i++) {
-                        const int ch = hsel * MINE + i;
-                        tc_ld32(taddr + ch * 32, r[i]);
-                        if (SWIGLU) tc_ld32(taddr + 128 + ch * 32, r2[SWIGLU ? i : 0]);
-                    }
-                    tc_wait_ld();
-                    release_acc();
+                    if (!drain(r, r2)) break;
 #pragma unroll
                     for (int i = 0; i < MINE; i++) {
                         float v[32];
@@ -667,14 +743,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 }
             } else {
                 uint32_t r[MINE][32], r2[SWIGLU ? MINE : 1][32];
-#pragma unroll
-                for (int i = 0; i < MINE; i++) {
-                    const int ch = hsel * MINE + i;
-                    tc_ld32(taddr + ch * 32, r[i]);
-                    if (SWIGLU) tc_ld32(taddr + 128 + ch * 32, r2[SWIGLU ? i : 0]);
-                }
-                tc_wait_ld();
-                release_acc();
+                if (!drain(r, r2)) break;
 #pragma unroll
                 for (int i = 0; i < MINE; i++) {
                     float v[32];
@@ -1060,6 +1129,7 @@ static void common_params(GemmParams& p, int m) {
     p.nparts = 1;
     p.status = status_ptr();
     p.alpha = 1.0f;
+    p.acc_chunk = 0;
     p.sync.wait_phase = p.sync.signal_phase = -1;
     static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
     p.early = early ? 1 : 0;
@@ -1253,10 +1323,12 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
 
     if (act != VELOX_ACT_BF16) return VELOX_ERR_UNSUPPORTED;
     // bf16 activations x weights dequantised to bf16 in scratch (view rows only, row 0 = row_begin).
-    // Q4_K values are not bf16 numbers: they go in as hi + lo, two bf16 terms side by side along K
-    // ([rows, 2k]) multiplied by the same activations, which the producer re-reads for the second half.
+    // Q4_K values are not bf16 numbers: they go in as three bf16 terms side by side along K
+    // ([rows, 3k]: bf16(v), bf16 of what that dropped, bf16 of what is left; together the f32 value
+    // exactly), each multiplied by the same activations, which the producer re-reads for every
+    // third. Two terms (2^-17) were not enough for the 2e-4 conformance bound on sums that cancel.
     const bool split = w.format == VELOX_FMT_GGML_Q4_K;
-    const long long kw = split ? 2 * k : k;
+    const long long kw = split ? 3 * k : k;
     const size_t wbytes = (size_t)w.rows * kw * 2;
     uint16_t* wq = static_cast<uint16_t*>(scratch(SCRATCH_WEIGHT_BF16, wbytes * (sw ? 2 : 1)));
     if (!wq) return (int)cudaErrorMemoryAllocation;
@@ -1277,6 +1349,9 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
     p.k_steps = (int)(kw / 16);
     p.k_elems_per_block = 64;
     p.a_k_blocks = (int)((k / 16 + 3) / 4);
+    // Q4_K values are large next to sums that cancel: four k-blocks (one 256-value block of the
+    // format) per accumulator, the chunks added by the epilogue
+    if (split) p.acc_chunk = 4;
     const velox_sm100_view* hv[2] = {&w, &w1};
     for (int h = 0; h < 2; h++) {
         const velox_sm100_view& v = *hv[h];

@@ -260,7 +260,7 @@ static int launch_fp8(const Fp8Params& p, bool swiglu) {
 }
 
 int gemv_fp8_mma(const LinearArgs& a) {
-    if (a.w.format != VELOX_FMT_FP8_ROW_BF16 || a.w.k % 64 != 0 || a.m < 2 || a.m > 16 || a.w.rows < 1 ||
+    if (a.w.format != VELOX_FMT_FP8_ROW_BF16 || a.w.k % 64 != 0 || a.m < 1 || a.m > 16 || a.w.rows < 1 ||
         (reinterpret_cast<uintptr_t>(a.w.w) & 15) || a.w.k % 16 != 0)
         return VELOX_ERR_UNSUPPORTED;
     const long long k = a.w.k;

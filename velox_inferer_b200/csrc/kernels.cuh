@@ -35,7 +35,7 @@ int dequant_rows_f32(const velox_sm100_view* v, float* out);
 int embed_rows_f32(const velox_sm100_view* v, const uint32_t* ids, int count, float* out);
 // y[m, n] = x[m, k] . w[n, k]^T, all f32.
 int matmul_f32(const float* x, const float* w, float* y, int m, int n, int k);
-// lo_offset > 0: also write the bf16 residual of each value lo_offset elements after it.
+// lo_offset > 0: also write the two bf16 remainder terms of each value, lo_offset and 2 lo_offset elements after it.
 int dequant_rows_bf16(const velox_sm100_view* v, uint16_t* out, long long ld_out, long long lo_offset);
 
 // Memory-bound path, m <= 16, k % 64 == 0.
@@ -71,7 +71,7 @@ int add_rms_norm_twin(float* acc, const float* x, const uint16_t* xb, const floa
 int bf16_twin(const float* x, uint16_t* xb, long long len);
 // Q4_K decode on the warp-level tensor-core MMA (plain form, m <= 16, k % 256 == 0); else VELOX_ERR_UNSUPPORTED.
 int gemv_q4k_mma(const LinearArgs& a);
-// FP8-row decode with bf16 activations on the same MMA (2 <= m <= 16, k % 64 == 0); else VELOX_ERR_UNSUPPORTED.
+// FP8-row decode with bf16 activations on the same MMA (m <= 16, k % 64 == 0); else VELOX_ERR_UNSUPPORTED.
 int gemv_fp8_mma(const LinearArgs& a);
 int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_stride, const float* weight,
                uint8_t* const* codes, uint8_t* const* atoms, int ndst, long long row0, int rows, int dim, float eps,
