@@ -265,12 +265,12 @@ def main():
                     help="comma-separated subset of: nvfp4,sweep,mlp,formats,decode_stack (default all)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tp-check", action="store_true")
-    ap.add_argument("--tp", choices=("flags", "kernel", "barrier", "nccl", "fused"), default="flags",
+    ap.add_argument("--tp", choices=("flags", "kernel", "barrier", "nccl", "fused"), default="kernel",
                     help="N > 1: communication fused into the GEMM epilogue and the norm over symmetric memory, "
-                         "ordered by flags in peer memory that the kernels themselves raise and poll (flags; "
-                         "'fused' is the same), by one-thread flag-barrier kernels between the phases (kernel), "
-                         "by torch's signal-pad barrier kernels (barrier); or one NCCL all-reduce after o and "
-                         "down (nccl)")
+                         "ordered by the library's own one-warp flag-barrier kernels between the phases (kernel, "
+                         "the default: bounded waits on flags in peer memory), by flags that the GEMM and norm "
+                         "kernels themselves raise and poll (flags; 'fused' is the same), by torch's signal-pad "
+                         "barrier kernels (barrier); or one NCCL all-reduce after o and down (nccl)")
     ap.add_argument("--chunks", type=int, default=1,
                     help="N > 1, fused step: token chunks that run side by side on streams of their own, so that one "
                          "chunk's transfers overlap another's compute (1: the whole step as one chain)")

@@ -14,7 +14,7 @@ def _gpus() -> int:
     return torch.cuda.device_count() if torch.cuda.is_available() else 0
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_fused_tp_step_is_exact_and_matches_the_all_reduce_step(world):
     if _gpus() < world:
         pytest.skip(f"needs {world} GPUs")

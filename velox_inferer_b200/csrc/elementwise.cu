@@ -443,12 +443,17 @@ add_rms_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restric
 // The sequence-parallel norm in the same persistent, fetch-ahead form: NS partial-sum slots added in
 // slot order, the NVFP4 row written at row0 + row of every destination blob. (One block per SM:
 // a rank owns few rows and the slots' values take the registers.)
-template <int NS>
+// QUAD (rows and row0 multiples of 128): a block takes the four rows q, q + 32, q + 64, q + 96 of a
+// 128-row tile, whose scale bytes share one 16-byte piece of every scale atom; the pieces are put
+// together in shared memory and go to each destination as 16-byte stores instead of sixteen
+// single bytes, which is what a link between GPUs wants.
+template <int NS, bool QUAD>
 __global__ void __launch_bounds__(1024, 1)
 sp_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ slots, long long slot_stride,
                          const float* __restrict__ weight, const Q4Dest dst, long long row0, int rows, int dim,
                          float eps, float offset, float divisor, const __grid_constant__ TpSync sync) {
     __shared__ float red[2][32];
+    __shared__ __align__(16) uint8_t quad_scales[QUAD ? 128 : 1][16];   // [atom along K][4 rows x 4 groups]
     const int T = (int)blockDim.x, tid = (int)threadIdx.x;
     const int c0 = tid * 4, c1 = (T + tid) * 4;
     if (tid == 0) grid_launch_dependents();
@@ -470,10 +475,13 @@ sp_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ s
             b1[sl] = __ldcs(reinterpret_cast<const uint2*>(slots + sl * slot_stride + base + c1));
         }
     };
-    long long row = blockIdx.x;
-    if (row < rows) fetch(row);
+    // the i-th row of this block
+    const long long quad_first = (long long)(blockIdx.x / 32) * 128 + blockIdx.x % 32;
+    auto row_at = [&](int i) { return QUAD ? quad_first + 32LL * i : (long long)blockIdx.x + (long long)i * gridDim.x; };
+    if (row_at(0) < rows) fetch(row_at(0));
     int par = 0;
-    for (; row < rows; row += gridDim.x, par ^= 1) {
+    for (int ri = 0; (!QUAD || ri < 4) && row_at(ri) < rows; ri++, par ^= 1) {
+        const long long row = row_at(ri);
         float4 v[2] = {a0, a1};
         float4 part[2];
 #pragma unroll
@@ -490,8 +498,8 @@ sp_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ s
                 }
             }
         }
-        const long long next = row + gridDim.x;
-        if (next < rows) fetch(next);   // in flight while this row is finished
+        const long long next = row_at(ri + 1);
+        if ((!QUAD || ri < 3) && next < rows) fetch(next);   // in flight while this row is finished
         const long long base = row * dim, obase = (row0 + row) * dim;
 #pragma unroll
         for (int it = 0; it < 2; it++) {
@@ -544,9 +552,18 @@ sp_norm_q4_stream_kernel(float* __restrict__ acc, const uint16_t* __restrict__ s
                 const long long soff = nvfp4_scale_offset(row0 + row, c / 16, dim);
                 for (int d = 0; d < dst.n; d++) {
                     *reinterpret_cast<uint2*>(dst.codes[d] + (obase + c) / 2) = pk;
-                    dst.atoms[d][soff] = (uint8_t)sb;
+                    if (!QUAD) dst.atoms[d][soff] = (uint8_t)sb;
                 }
+                if (QUAD) quad_scales[c / 64][ri * 4 + (c / 16) % 4] = (uint8_t)sb;
             }
+        }
+    }
+    if (QUAD) {
+        __syncthreads();
+        if (tid < dim / 64) {
+            const uint4 piece = *reinterpret_cast<const uint4*>(quad_scales[tid]);
+            const long long off = (((row0 + quad_first) / 128) * (dim / 64) + tid) * 512 + (quad_first % 32) * 16;
+            for (int d = 0; d < dst.n; d++) *reinterpret_cast<uint4*>(dst.atoms[d] + off) = piece;
         }
     }
     if (sync.signal_phase >= 0) {
@@ -709,15 +726,27 @@ int sp_norm_q4(float* acc, const uint16_t* slots, int nslots, long long slot_str
         TimedRegion timed(TIMED_NORM);
         EarlyLaunch l((unsigned)blocks, (unsigned)(dim / 8));
         cudaError_t e;
-        if (nslots == 2)
-            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<2>, acc, slots, slot_stride, weight, dst, row0, rows, dim,
-                                   eps, off, divisor, ts);
+        // whole 128-row scale tiles (what a rank of a tensor-parallel group owns): four rows per block
+        const bool quad = rows % 128 == 0 && row0 % 128 == 0 && dim <= 8192;
+        if (quad) l.cfg.gridDim = dim3((unsigned)(rows / 4));
+        if (quad && nslots == 2)
+            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<2, true>, acc, slots, slot_stride, weight, dst, row0, rows,
+                                   dim, eps, off, divisor, ts);
+        else if (quad && nslots == 4)
+            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<4, true>, acc, slots, slot_stride, weight, dst, row0, rows,
+                                   dim, eps, off, divisor, ts);
+        else if (quad)
+            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<8, true>, acc, slots, slot_stride, weight, dst, row0, rows,
+                                   dim, eps, off, divisor, ts);
+        else if (nslots == 2)
+            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<2, false>, acc, slots, slot_stride, weight, dst, row0, rows,
+                                   dim, eps, off, divisor, ts);
         else if (nslots == 4)
-            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<4>, acc, slots, slot_stride, weight, dst, row0, rows, dim,
-                                   eps, off, divisor, ts);
+            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<4, false>, acc, slots, slot_stride, weight, dst, row0, rows,
+                                   dim, eps, off, divisor, ts);
         else
-            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<8>, acc, slots, slot_stride, weight, dst, row0, rows, dim,
-                                   eps, off, divisor, ts);
+            e = cudaLaunchKernelEx(&l.cfg, sp_norm_q4_stream_kernel<8, false>, acc, slots, slot_stride, weight, dst, row0, rows,
+                                   dim, eps, off, divisor, ts);
         if (e != cudaSuccess) return (int)e;
         return launch_status();
     }

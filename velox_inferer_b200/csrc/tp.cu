@@ -61,6 +61,12 @@ __global__ void tp_signal_kernel(const TpSync s) {
 // are served side by side, so the barrier costs one round trip over the links, not one per rank.
 __global__ void tp_barrier_kernel(const TpSync s) {
     const int r = (int)threadIdx.x;
+    // Launched with early start allowed, and lets the launch behind it start early too: the warp is
+    // resident while the kernel ahead drains, and the next kernel sets itself up (and requests its
+    // weights) while this one waits for the peers. The wait below is what orders the data: it
+    // returns once the kernel ahead has completed and its writes, remote ones included, are done.
+    if (r == 0) grid_launch_dependents();
+    grid_dependency_wait();
     if (r < s.n) {
         const unsigned int want = *reinterpret_cast<const volatile unsigned int*>(s.epoch);
         const long long at = (long long)s.wait_phase * TP_FLAG_STRIDE;
@@ -158,8 +164,10 @@ int velox_sm100_tp_barrier(const velox_sm100_tp_sync* sync) {
     TpSync s;
     int rc = tp_sync_fill_elementwise(&s, sync);
     if (rc != 0) return rc;
-    tp_barrier_kernel<<<1, 32, 0, stream()>>>(s);
-    return launch_status();
+    EarlyLaunch l(1u, 32u);
+    const cudaError_t e = cudaLaunchKernelEx(&l.cfg, tp_barrier_kernel, s);
+    note_launch();
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
 }
 
 int velox_sm100_tp_signal(const velox_sm100_tp_sync* sync) {
