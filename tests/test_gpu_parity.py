@@ -232,16 +232,16 @@ def test_linear_swiglu_decode_nvfp4_activations(b, k, w, m, order):
     (64, 512, 0, 64, 9), (64, 128, 0, 64, 2), (512, 2048, 64, 384, 8), (300, 256, 0, 300, 5),
     (160, 1024, 16, 128, 16), (1280, 4096, 0, 1280, 3),
 ])
-def test_linear_decode_fp8_rows_on_tensor_cores(b, n, k, begin, rows, m):
-    """FP8-row views that admit FP8 activations decode through kind::f8f6f4: ragged row counts,
-    views starting inside a 128-row tile, K splits (long K, few tiles)."""
+def test_linear_decode_fp8_rows_under_allow_a8(b, n, k, begin, rows, m):
+    """FP8-row views that admit FP8 activations still decode with bf16 activations (the warp-MMA
+    kernel is faster than quantiser + block-scaled kernel at these widths, and rounds less): ragged
+    row counts, views starting inside a 128-row tile, long K with few tiles."""
     r = O.Rng(17)
     payload = r.random_weight(FMT_O[F8], n, k)
     x = r.vec(m * k, 1.0)
     view = make_view(b, payload, F8, n, k, begin, rows, ActPolicy.allow_a8())
     act = b.linear_act(view, m)
-    # two tokens and more take the tensor cores; a single token is faster on the unpacking GEMV
-    assert act == (ActQuant(ActQuant.FP8_ROW) if m >= 2 else ActQuant(ActQuant.BF16))
+    assert act == ActQuant(ActQuant.BF16) and act.permitted(view.act)
     want = oracle_linear(x, payload, F8, n, k, begin, rows, m, act)
     y = b.alloc(m * rows + 2)
     yb = torch.zeros(m * rows, dtype=torch.bfloat16, device=y.device)
@@ -265,7 +265,7 @@ def test_linear_swiglu_decode_fp8_rows(b):
     parent = WeightView.full(b.upload_bytes(p), F8, 2 * w, k).with_act(ActPolicy.allow_a8())
     gate, up = parent.rows_view(0, w), parent.rows_view(w, w)
     act = b.linear_swiglu_act(gate, up, m)
-    assert act == ActQuant(ActQuant.FP8_ROW)
+    assert act == ActQuant(ActQuant.BF16)
     want = _swiglu_want(x, p, p, F8, 2 * w, 2 * w, k, 0, w, w, m, act)
     out = b.alloc(m * w)
     b.linear_swiglu(b.upload(x), gate, up, out, m)

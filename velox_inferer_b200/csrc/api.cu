@@ -103,11 +103,6 @@ struct Plan {
 // Kernel and activation rounding for one view at m rows. The rounding never exceeds the view's
 // policy (crates/velox-conformance/src/lib.rs:64-74): bf16 is always permitted; FP8 rows need
 // AllowA8 or AllowA4; NVFP4 activations need AllowA4 and use its divisor.
-// FP8 rows at decode width: from this many tokens on the tensor-core kernel (quantiser launch + MMA)
-// beats the unpacking GEMV, measured on [14336, 4096] (17.5 us against 21 us at one token, 24 against
-// 21 at two).
-constexpr int FP8_TC_MIN_M = 2;
-
 static int device_sms() {
     static int sms[64] = {};
     int dev = 0;
@@ -149,13 +144,10 @@ static Plan plan_for(const velox_sm100_view& v, int m) {
             p.divisor = v.divisor;
             return p;
         }
-        // (for a single token the unpacking GEMV still wins against quantiser + tensor-core launch)
-        if (v.format == VELOX_FMT_FP8_ROW_BF16 && v.policy != VELOX_POLICY_A16_ONLY && v.k % 128 == 0 &&
-            m >= FP8_TC_MIN_M && gemm_available()) {
-            p.path = PATH_GEMV_TC;
-            p.act = VELOX_ACT_FP8_ROW;
-            return p;
-        }
+        // FP8 rows at decode width keep bf16 activations whatever the policy admits: the warp-MMA
+        // kernel that re-labels E4M3 bytes as bf16 ([14336, 4096]: 15 us at 1 to 8 tokens, 19 at 16)
+        // beats the FP8 quantiser launch plus the block-scaled tensor-core kernel (21 to 25 us),
+        // and rounds less.
         p.path = PATH_GEMV;
         p.act = VELOX_ACT_BF16;
         return p;

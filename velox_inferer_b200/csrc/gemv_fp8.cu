@@ -16,8 +16,9 @@
 // lane holds: lane (g, t) loads 16 consecutive bytes of rows g and g + 8 per 64-weight chunk, and
 // the activations are fetched and paired in the matching order.
 //
-// Work split as in the Q4_K kernel: a block owns 16 MT rows, its warps each take a part of K, and
-// the parts are added in warp order at the end (results do not depend on timing). The fused SwiGLU
+// Work split as in the Q4_K kernel: a block owns 16 MT rows, its warps (four or eight) each take
+// a part of K, and the parts are added in warp order at the end (results do not depend
+// on timing). The fused SwiGLU
 // form runs the gate view and then the up view's rows through the same loop.
 //
 // Reference counterpart: linear_gemv_kernel on Fp8RowBf16,
@@ -306,17 +307,15 @@ int gemv_fp8_mma(const LinearArgs& a) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (sms <= 0) sms = 148;
     }
-    // Two row tiles per block halve what a block reads of the activations per weight byte; one where
-    // that would leave the machine short of blocks. Few row tiles with a long K: eight K parts.
+    // Many rows: two row tiles per block halve what a block reads of the activations per weight byte.
+    // Few row tiles with a long K (a down projection): eight K parts per block, so that the machine
+    // has warps to hide latency with. More K parts than that were slower wherever tried (sixteen
+    // on [5120, 25600]: 40 us against 37; eight instead of four on [14336, 4096]: 16.7 against 15.3).
     const long long tiles = (a.w.rows + 15) / 16;
-    const bool wide = tiles >= 16LL * sms;
-    const bool deep = !wide && tiles * 4 < 12LL * sms && k >= 8 * 64 * 8;
-    if (a.m <= 8) {
-        if (wide) return launch_fp8<2, 1, 4>(p, a.swiglu);
-        return deep ? launch_fp8<1, 1, 8>(p, a.swiglu) : launch_fp8<1, 1, 4>(p, a.swiglu);
-    }
-    if (wide) return launch_fp8<2, 2, 4>(p, a.swiglu);
-    return deep ? launch_fp8<1, 2, 8>(p, a.swiglu) : launch_fp8<1, 2, 4>(p, a.swiglu);
+    const bool two = a.m > 8;
+    if (tiles >= 16LL * sms) return two ? launch_fp8<2, 2, 4>(p, a.swiglu) : launch_fp8<2, 1, 4>(p, a.swiglu);
+    if (tiles * 4 < 12LL * sms && k >= 8 * 64 * 8) return two ? launch_fp8<1, 2, 8>(p, a.swiglu) : launch_fp8<1, 1, 8>(p, a.swiglu);
+    return two ? launch_fp8<1, 2, 4>(p, a.swiglu) : launch_fp8<1, 1, 4>(p, a.swiglu);
 }
 
 }  // namespace vx
