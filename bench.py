@@ -525,10 +525,13 @@ def main():
 
 
 # DRAM bytes per GEMM launch of the prefill step on one GPU, from an ncu capture of the step's own
-# launches (two layers of the same stack: the layers are identical, so the per-launch average is the
-# 64-layer step's); see the file named beside it.
-STACK_GEMM_TRAFFIC_PER_LAUNCH = None
-STACK_GEMM_TRAFFIC_OF = "profiles/stack_prefill_launch_list.md (no DRAM-byte capture of the step's launches yet)"
+# launches (four layers of the same stack: the layers are identical, so the per-launch average is the
+# 64-layer step's): 89.8 MB read + 8.0 MB written on average over the step's four launches
+# (q|k|v 36.2, o 33.2, gate|up 172.6, down 149.9 MB; the stored operands they must read are 35.4, 33.0,
+# 153.4 and 103.2 MB). See the file named beside it.
+STACK_GEMM_TRAFFIC_PER_LAUNCH = 97_717_568
+STACK_GEMM_TRAFFIC_OF = ("profiles/stack_prefill_gemm_dram_traffic.md: dram__bytes_read.sum + dram__bytes_write.sum, "
+                         "mean over the 16 gemm_kernel launches of one 4-layer step")
 
 
 def _time_replays(replay, launches_per_replay, gpu_index=0, warm_s=0.2, timed_s=0.3):
