@@ -176,7 +176,7 @@ def workload_config(args, spec, m, fused_tp=False):
                            + ("bf16 partial tiles stored into the owning rank's rows by the GEMM epilogue over NVLink "
                               "(reduce-scatter), NVFP4 norm output stored into every rank (all-gather), ordered by "
                               "per-phase flags in peer memory (bounded waits)" if fused_tp == "flags" else
-                              "the same flags raised and awaited by one-thread barrier kernels between the phases "
+                              "the same flags raised and awaited by one-warp barrier kernels between the phases "
                               "(bounded waits)" if fused_tp == "kernel" else
                               "the same with torch's signal-pad barrier kernels between the phases" if fused_tp == "barrier" else
                               "bf16 all-reduce (NCCL) after o and down"),

@@ -315,9 +315,11 @@ int velox_sm100_linears_q4(const uint8_t* codes, const uint8_t* atoms, float div
  *    output; signals.
  *  - velox_sm100_tp_wait: a one-thread kernel that only waits (the end of a step: every rank's
  *    output rows are in place).
- *  - velox_sm100_tp_barrier: a one-thread kernel that raises row signal_phase (= wait_phase) and then
- *    waits on it: a barrier between two phases as a launch of its own, for steps whose kernels
- *    run without `sync` (the data kernels then carry no waits; same bounded wait, same status).
+ *  - velox_sm100_tp_barrier: a one-warp kernel that raises row signal_phase (= wait_phase) on every
+ *    rank and then waits on it, all ranks side by side: a barrier between two phases as a launch
+ *    of its own, for steps whose kernels run without `sync` (the data kernels then carry no
+ *    waits; same bounded wait, same status). Launched with early start allowed; the launch behind
+ *    it may start early too and is ordered by its own wait for this kernel.
  *  - velox_sm100_tp_signal: a one-thread kernel that only signals (tests).
  * `sync` may be NULL everywhere except tp_wait / tp_signal (single rank, or the caller orders the
  * ranks itself). */

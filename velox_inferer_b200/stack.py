@@ -133,7 +133,7 @@ class TpFabric:
     Ordering between ranks, ``sync_mode``:
     ``"flags"``: every kernel that writes into other ranks' memory raises a flag there when it is
     done, every kernel that reads such data polls its own flags first;
-    ``"kernel"``: the same flags raised and awaited by a one-thread barrier kernel between the
+    ``"kernel"``: the same flags raised and awaited by a one-warp barrier kernel between the
     phases (the data kernels carry no waits);
     ``"barrier"``: torch's signal-pad barrier kernels between the phases (kept for comparison; its
     device-side wait is not bounded).
