@@ -69,6 +69,11 @@ def test_fp8_prefill_with_fp8_row_activations(b, n, k, begin, rows, m):
 @pytest.mark.parametrize("fmt,n,k,begin,rows,m", [
     (NV, 384, 1024, 64, 256, 21), (NV, 384, 1024, 64, 256, 96), (NV, 256, 512, 0, 256, 64),
     (F8, 256, 512, 0, 256, 64), (F8, 200, 320, 17, 150, 70), (NV, 8192, 256, 0, 8192, 100),
+    # FP8 rows above one token tile: stored bytes converted inside the GEMM (no bf16 scratch): ragged
+    # tokens and rows, a view starting off the tile grid and ending at the parent's last row, a long
+    # K (several passes over both rings), many tiles per CTA pair
+    (F8, 256, 512, 0, 256, 130), (F8, 700, 1024, 17, 683, 300), (F8, 300, 8192, 40, 200, 257),
+    (F8, 40000, 64, 128, 39000, 513),
 ])
 def test_a16_only_views_round_to_bf16_at_most(b, fmt, n, k, begin, rows, m):
     act, got, want = _run_linear(b, fmt, n, k, begin, rows, m, A16)
@@ -77,19 +82,22 @@ def test_a16_only_views_round_to_bf16_at_most(b, fmt, n, k, begin, rows, m):
     assert e_conf <= LINEAR_TOL and e_rms <= RMS_TOL, (e_conf, e_rms)
 
 
-@pytest.mark.parametrize("n,k,rows,m", [(64, 512, 64, 33), (300, 1024, 300, 130)])
-def test_q4k_prefill_within_rms_tolerance(b, n, k, rows, m):
-    # Q4_K values (d*sc*q - dmin*m) are rounded to bf16 for the tensor cores: inside the
-    # benchmark's 1e-2*rms bound, outside the 2e-4 conformance metric (the reference notes the same
-    # for its own f32 kernels at large K, conformance lib.rs:3973-3976).
+@pytest.mark.parametrize("n,k,rows,m", [(64, 512, 64, 33), (300, 1024, 300, 130), (96, 2560, 96, 70), (520, 2560, 520, 300)])
+def test_q4k_prefill_meets_both_bounds(b, n, k, rows, m):
+    # Q4_K values (d*sc*q - dmin*m) go to the tensor cores as three bf16 terms, summed in chunks of
+    # four k-blocks that the epilogue adds: the 2e-4 conformance metric holds on the reference's
+    # random blocks too (values up to 30, sums that cancel).
     act, got, want = _run_linear(b, Q4, n, k, 0, rows, m, A16)
     assert act.kind == ActQuant.BF16
-    assert both_metrics(got, want)[1] <= RMS_TOL
+    e_conf, e_rms = both_metrics(got, want)
+    assert e_conf <= LINEAR_TOL and e_rms <= RMS_TOL, (e_conf, e_rms)
 
 
 @pytest.mark.parametrize("fmt,policy,k,w,m,order", [
     (NV, A4, 512, 256, 37, "gate_up"), (NV, A4, 512, 256, 130, "up_gate"), (NV, A4, 1024, 128, 64, "split"),
     (NV, A16, 512, 256, 40, "gate_up"), (F8, A8, 512, 192, 70, "gate_up"), (F8, A16, 512, 96, 33, "split"),
+    # FP8 rows with bf16 activations above one token tile: converted inside the GEMM
+    (F8, A16, 1024, 200, 300, "up_gate"), (F8, A16, 512, 96, 130, "split"), (F8, A16, 2048, 300, 257, "gate_up"),
 ])
 def test_linear_swiglu_prefill(b, fmt, policy, k, w, m, order):
     r = O.Rng(0x5e2)

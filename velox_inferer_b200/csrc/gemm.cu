@@ -71,6 +71,8 @@ struct Plan {
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_SF_COL = 256;  // scale sets follow the accumulator
 constexpr int TMEM_SF_SET = 48;   // per set: 16 columns of x scales, 32 columns of W scales
+constexpr int RAW_STAGES = 3;          // ring of stored-byte tiles (bf16 kind with conversion in the kernel) ...
+constexpr int RAW_STAGE_BYTES = 8192;  // ... in the shared memory the scale ring has in the NVFP4 kind
 constexpr int GEMM_THREADS = 512;
 constexpr int EPI_WARP0 = 4;     // warps 4..11 drain the accumulator, two per lane quadrant
 constexpr int MOVER_WARP0 = 12;  // warps 12..15 move scales into tensor memory
@@ -117,6 +119,8 @@ struct GemmParams {
     const float* tok_scale;
     const CUtensorMap* out_maps;   // optional (tensor parallel): one output map per owning rank, in global memory;
     int rows_per_owner;            // token rows [o * rows_per_owner, (o + 1) * rows_per_owner) go to out_maps[o]
+    int raw_fmt;    // bf16 kind, pairs only, 0 = off: the W maps describe stored bytes (1: FP8 rows) that four
+                    // warps turn into bf16 operands in shared memory, instead of bf16 scratch
     int acc_chunk;  // bf16 kind, 0 = off: k-blocks summed in tensor memory before the epilogue takes the sum over
     int early;      // the launch may start before the kernel ahead of it has finished (see the producers)
     int* status;
@@ -169,6 +173,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     auto cfull = [&](uint32_t b) { return acc_full + 24u * b; };
     auto cempty = [&](uint32_t b) { return acc_empty + 24u * b; };
     const bool chunked = KIND == KIND_BF16 && p.acc_chunk > 0;
+    // stored-byte ring (bf16 kind, conversion in the kernel)
+    auto raw_full = [&](int s) { return acc_full + 40u + 8u * s; };
+    auto raw_empty = [&](int s) { return acc_full + 64u + 8u * s; };
+    const bool raw = KIND == KIND_BF16 && CG == 2 && p.raw_fmt != 0;
     uint32_t* tmem_slot_ptr = reinterpret_cast<uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
 
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -191,9 +199,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < OP_STAGES; s++) {
-            mbar_init(op_full(s), 1);
+            mbar_init(op_full(s), raw ? 3 : 1);   // the producer's arrive, plus two converting warps'
             mbar_init(op_empty(s), 1);
             mbar_init(peer_full(s), 1);
+        }
+        for (int s = 0; s < RAW_STAGES; s++) {
+            mbar_init(raw_full(s), 1);
+            mbar_init(raw_empty(s), 2);
         }
         for (int s = 0; s < SF_STAGES; s++) {
             mbar_init(sf_full(s), 1);
@@ -286,8 +298,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // (whole warp in the loop, one elected lane issuing, as in the MMA warp below)
         VX_REGS_ISSUE();
         {
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, rstage = 0;
+            uint32_t phase = 0, rphase = 0;
             bool ok = true;
             const bool leader = elect_one();
             // Weights that are read from their stored payload do not depend on the kernel ahead of
@@ -326,7 +338,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t sa = base + stage * OP_STAGE_BYTES;
                     const uint32_t sb = sa + A_BYTES;
                     const int kx = kb * p.k_elems_per_block;
-                    if (leader) {
+                    if (raw) {
+                        // x as usual; this CTA's 128 W rows as stored bytes into the byte ring, from
+                        // where four warps convert them into the stage
+                        if (!mbar_wait(raw_empty(rstage), rphase ^ 1u, 20)) {
+                            if (leader) atomicExch(p.status, ST_TIMEOUT_EMPTY);
+                            ok = false;
+                            break;
+                        }
+                        if (leader) {
+                            mbar_arrive_expect_tx(op_full(stage), A_BYTES);
+                            tma_load_2d(sa, &tmap_a, op_full(stage), (kb % p.a_k_blocks) * p.k_elems_per_block, mt * BM);
+                            mbar_arrive_expect_tx(raw_full(rstage), RAW_STAGE_BYTES);
+                            tma_load_2d(sf_ring + rstage * RAW_STAGE_BYTES, rank ? mb1 : mb0, raw_full(rstage), kb * 64,
+                                        rank ? r1 : r0);
+                        }
+                        if (++rstage == RAW_STAGES) {
+                            rstage = 0;
+                            rphase ^= 1u;
+                        }
+                    } else if (leader) {
                         mbar_arrive_expect_tx(op_full(stage), A_BYTES + PL::B_BYTES);
                         if (waited)
                             tma_load_2d(sa, &tmap_a, op_full(stage), (kb % p.a_k_blocks) * p.k_elems_per_block,
@@ -872,6 +903,69 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         }
     }
 
+    else if (KIND == KIND_BF16 && warp >= MOVER_WARP0) {
+        // ---------------- converters (bf16 kind on stored bytes): byte ring -> bf16 W operand of the stage ----------------
+        // FP8 rows: thread (row = ct / 4 + 16 j, piece = ct % 4) takes 16 stored bytes and writes 16
+        // bf16 numbers, two 16-byte pieces of the row's 128-byte line at the places the 128-byte
+        // swizzle puts them (piece index xor row % 8). An E4M3 byte re-labelled as bf16 is the value
+        // times 2^-120, subnormals included; the bf16 multiply by 2^120 is exact.
+        VX_REGS_MOVER();
+        if (raw) {
+            // Two groups of two warps take the k-blocks in turn, so that one group's wait, loads,
+            // stores and fence overlap the other's (a single group's round trip per k-block was
+            // longer than the k-block's MMAs).
+            const int group = (warp - MOVER_WARP0) / 2;
+            const int ct = (int)threadIdx.x - (MOVER_WARP0 + 2 * group) * 32;   // 0..63 within the group
+            const int piece = ct % 4;
+            bool ok = true;
+            const __nv_bfloat162 up = __floats2bfloat162_rn(1.329227995784916e36f, 1.329227995784916e36f);   // 2^120
+            long long it = 0;   // k-blocks since the kernel began (all tiles of this CTA)
+            for (int tile = unit; tile < num_tiles && ok; tile += units) {
+                for (int kb = 0; kb < p.k_blocks; kb++, it++) {
+                    if ((int)(it & 1) != group) continue;
+                    const int stage = (int)(it % OP_STAGES), rstage = (int)(it % RAW_STAGES);
+                    const uint32_t phase = (uint32_t)(it / OP_STAGES) & 1u, rphase = (uint32_t)(it / RAW_STAGES) & 1u;
+                    if (!mbar_wait(raw_full(rstage), rphase, 20) || !mbar_wait(op_empty(stage), phase ^ 1u, 20)) {
+                        if (lane == 0) atomicExch(p.status, ST_TIMEOUT_FULL);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t src = sf_ring + rstage * RAW_STAGE_BYTES;
+                    const uint32_t dstb = base + stage * OP_STAGE_BYTES + A_BYTES;
+#pragma unroll 2
+                    for (int j = 0; j < 8; j++) {
+                        const int row = ct / 4 + 16 * j;
+                        const uint4 q = lds16(src + row * 64 + piece * 16);
+                        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 4; i++) {
+                            const uint32_t odd = ((w[i] >> 4) & 0x07F007F0u) | (w[i] & 0x80008000u);   // bytes 1, 3
+                            const uint32_t v = w[i] << 8;
+                            const uint32_t even = ((v >> 4) & 0x07F007F0u) | (v & 0x80008000u);        // bytes 0, 2
+                            uint32_t lo = __byte_perm(even, odd, 0x5410u), hi = __byte_perm(even, odd, 0x7632u);
+                            __nv_bfloat162 a = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&lo), up);
+                            __nv_bfloat162 b = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&hi), up);
+                            o[2 * i] = *reinterpret_cast<uint32_t*>(&a);
+                            o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b);
+                        }
+                        const uint32_t line = dstb + row * 128;
+                        sts16(line + (((2 * piece) ^ (row & 7)) << 4), make_uint4(o[0], o[1], o[2], o[3]));
+                        sts16(line + (((2 * piece + 1) ^ (row & 7)) << 4), make_uint4(o[4], o[5], o[6], o[7]));
+                    }
+                    // the MMA (asynchronous proxy) reads what these generic-proxy stores wrote, and the
+                    // next bulk copy into the byte stage follows the loads above
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(op_full(stage));
+                        mbar_arrive(raw_empty(rstage));
+                    }
+                }
+            }
+        }
+    }
+
     else if (warp < 4) {
         VX_REGS_ISSUE();       // warps without a role in this form of the kernel
     } else {
@@ -978,6 +1072,19 @@ int gemm_make_rs_maps(void* maps_dev, const unsigned long long* ptrs, int n, int
     // pageable source: the copy has read `maps` by the time the call returns
     cudaError_t e = cudaMemcpyAsync(maps_dev, maps, sizeof(CUtensorMap) * n, cudaMemcpyHostToDevice, stream());
     return e == cudaSuccess ? 0 : (int)e;
+}
+
+// Stored bytes of a row-major matrix [rows, row_bytes] as 128-row x 64-byte boxes, no swizzle (the
+// byte ring of the bf16 kind's in-kernel conversion).
+static int make_raw_map(CUtensorMap* map, const void* ptr, long long rows, long long row_bytes) {
+    const cuuint64_t dims[2] = {(cuuint64_t)row_bytes, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+    const cuuint32_t box[2] = {64u, 128u};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : VELOX_ERR_UNSUPPORTED;
 }
 
 // Tensor map over the bf16 output columns [col, col + out_cols) of a part's yb, for whole-tile
@@ -1130,6 +1237,7 @@ static void common_params(GemmParams& p, int m) {
     p.status = status_ptr();
     p.alpha = 1.0f;
     p.acc_chunk = 0;
+    p.raw_fmt = 0;
     p.sync.wait_phase = p.sync.signal_phase = -1;
     static const bool early = getenv("VELOX_SM100_NO_EARLY_START") == nullptr;
     p.early = early ? 1 : 0;
@@ -1329,11 +1437,18 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
     // third. Two terms (2^-17) were not enough for the 2e-4 conformance bound on sums that cancel.
     const bool split = w.format == VELOX_FMT_GGML_Q4_K;
     const long long kw = split ? 3 * k : k;
-    const size_t wbytes = (size_t)w.rows * kw * 2;
-    uint16_t* wq = static_cast<uint16_t*>(scratch(SCRATCH_WEIGHT_BF16, wbytes * (sw ? 2 : 1)));
-    if (!wq) return (int)cudaErrorMemoryAllocation;
-    if ((rc = dequant_rows_bf16(&w, wq, kw, split ? k : 0)) != 0) return rc;
-    if (sw && (rc = dequant_rows_bf16(&w1, wq + (size_t)w.rows * kw, kw, split ? k : 0)) != 0) return rc;
+    // FP8 rows above one token tile (CTA pairs): no scratch at all; the kernel converts the stored
+    // bytes on their way into the operand stage.
+    const bool raw = w.format == VELOX_FMT_FP8_ROW_BF16 && a.m > BM && k % 64 == 0 &&
+                     (!sw || w1.format == VELOX_FMT_FP8_ROW_BF16);
+    uint16_t* wq = nullptr;
+    if (!raw) {
+        const size_t wbytes = (size_t)w.rows * kw * 2;
+        wq = static_cast<uint16_t*>(scratch(SCRATCH_WEIGHT_BF16, wbytes * (sw ? 2 : 1)));
+        if (!wq) return (int)cudaErrorMemoryAllocation;
+        if ((rc = dequant_rows_bf16(&w, wq, kw, split ? k : 0)) != 0) return rc;
+        if (sw && (rc = dequant_rows_bf16(&w1, wq + (size_t)w.rows * kw, kw, split ? k : 0)) != 0) return rc;
+    }
     const uint16_t* xb = a.xb;
     if (!xb || (reinterpret_cast<uintptr_t>(xb) & 15)) {
         uint16_t* xs = static_cast<uint16_t*>(scratch(SCRATCH_X_BF16, (size_t)a.m * k * 2));
@@ -1349,28 +1464,47 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
     p.k_steps = (int)(kw / 16);
     p.k_elems_per_block = 64;
     p.a_k_blocks = (int)((k / 16 + 3) / 4);
-    // Q4_K values are large next to sums that cancel: four k-blocks (one 256-value block of the
-    // format) per accumulator, the chunks added by the epilogue
-    if (split) p.acc_chunk = 4;
+    // The tensor cores' running f32 sum truncates, and over a long K that bias reaches the fourth
+    // digit of sums that cancel (Q4_K blocks with values up to 30 at K = 2560, FP8 rows at K = 8192):
+    // four k-blocks per accumulator, the chunks added by the epilogue with ordinary f32 adds (eight
+    // k-blocks per chunk failed the bound on the K = 8192 case).
+    if (kw > 4 * 64) p.acc_chunk = 4;
     const velox_sm100_view* hv[2] = {&w, &w1};
-    for (int h = 0; h < 2; h++) {
-        const velox_sm100_view& v = *hv[h];
-        if (v.format == VELOX_FMT_NVFP4)
-            pp.wdiv[h] = reinterpret_cast<const float*>(v.w + align256(v.n * k / 2) + v.n * k / 16);
-        if (v.format == VELOX_FMT_FP8_ROW_BF16)
-            pp.col_scale[h] = reinterpret_cast<const uint16_t*>(v.w + align256(v.n * k)) + v.row_begin;
-        pp.b_rows_total[h] = v.rows;
-        pp.valid_begin[h] = 0;
-        pp.valid_end[h] = v.rows;
+    if ((rc = make_map(&ma, xb, true, a.m, k)) != 0) return rc;
+    if (raw) {
+        // parent coordinates, as in the FP8 kind: the maps describe the stored code planes
+        p.raw_fmt = 1;
+        for (int h = 0; h < 2; h++) {
+            const velox_sm100_view& v = *hv[h];
+            pp.col_scale[h] = reinterpret_cast<const uint16_t*>(v.w + align256(v.n * k));
+            pp.b_rows_total[h] = v.n;
+            pp.valid_begin[h] = v.row_begin;
+            pp.valid_end[h] = v.row_begin + v.rows;
+        }
+        pp.b_row0[0] = w.row_begin;
+        pp.b_row0[1] = sw ? w1.row_begin : w.row_begin + 128;
+        pp.out_row0 = w.row_begin;
+        if ((rc = make_raw_map(&maps.b[0], w.w, w.n, k)) != 0) return rc;
+        if ((rc = make_raw_map(&maps.b[1], w1.w, w1.n, k)) != 0) return rc;
+    } else {
+        for (int h = 0; h < 2; h++) {
+            const velox_sm100_view& v = *hv[h];
+            if (v.format == VELOX_FMT_NVFP4)
+                pp.wdiv[h] = reinterpret_cast<const float*>(v.w + align256(v.n * k / 2) + v.n * k / 16);
+            if (v.format == VELOX_FMT_FP8_ROW_BF16)
+                pp.col_scale[h] = reinterpret_cast<const uint16_t*>(v.w + align256(v.n * k)) + v.row_begin;
+            pp.b_rows_total[h] = v.rows;
+            pp.valid_begin[h] = 0;
+            pp.valid_end[h] = v.rows;
+        }
+        pp.b_row0[0] = 0;
+        pp.b_row0[1] = sw ? 0 : 128;
+        pp.out_row0 = 0;
+        if ((rc = make_map(&maps.b[0], wq, true, w.rows, kw)) != 0) return rc;
+        if ((rc = make_map(&maps.b[1], sw ? wq + (size_t)w.rows * kw : wq, true, w.rows, kw)) != 0) return rc;
     }
-    pp.b_row0[0] = 0;
-    pp.b_row0[1] = sw ? 0 : 128;
     pp.b_tile_rows = sw ? 128 : 256;
     pp.tiles_n = (int)((w.rows + pp.b_tile_rows - 1) / pp.b_tile_rows);
-    pp.out_row0 = 0;
-    if ((rc = make_map(&ma, xb, true, a.m, k)) != 0) return rc;
-    if ((rc = make_map(&maps.b[0], wq, true, w.rows, kw)) != 0) return rc;
-    if ((rc = make_map(&maps.b[1], sw ? wq + (size_t)w.rows * kw : wq, true, w.rows, kw)) != 0) return rc;
     p.k_blocks = (p.k_steps + 3) / 4;
     const long long oc = w.rows, fr = 0;
     return launch<KIND_BF16>(sw, ma, maps, p, &oc, &fr);
