@@ -58,6 +58,7 @@ def test_nvfp4_prefill_with_nvfp4_activations(b, n, k, begin, rows, m):
 
 @pytest.mark.parametrize("n,k,begin,rows,m", [
     (512, 1024, 64, 384, 130), (256, 512, 0, 256, 64), (96, 384, 0, 96, 40), (300, 256, 7, 290, 100),
+    (300, 8192, 40, 200, 257),    # a long K: sums in chunks, added by the epilogue
 ])
 def test_fp8_prefill_with_fp8_row_activations(b, n, k, begin, rows, m):
     act, got, want = _run_linear(b, F8, n, k, begin, rows, m, A8)

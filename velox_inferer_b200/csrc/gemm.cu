@@ -121,7 +121,7 @@ struct GemmParams {
     int rows_per_owner;            // token rows [o * rows_per_owner, (o + 1) * rows_per_owner) go to out_maps[o]
     int raw_fmt;    // bf16 kind, pairs only, 0 = off: the W maps describe stored bytes (1: FP8 rows) that four
                     // warps turn into bf16 operands in shared memory, instead of bf16 scratch
-    int acc_chunk;  // bf16 kind, 0 = off: k-blocks summed in tensor memory before the epilogue takes the sum over
+    int acc_chunk;  // bf16 and FP8 kinds, 0 = off: k-blocks summed in tensor memory before the epilogue takes the sum over
     int early;      // the launch may start before the kernel ahead of it has finished (see the producers)
     int* status;
     PartParams part[MAX_PARTS];
@@ -172,7 +172,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     // second accumulator (bf16 kind with chunked sums): buffer b's barriers and first column
     auto cfull = [&](uint32_t b) { return acc_full + 24u * b; };
     auto cempty = [&](uint32_t b) { return acc_empty + 24u * b; };
-    const bool chunked = KIND == KIND_BF16 && p.acc_chunk > 0;
+    const bool chunked = KIND != KIND_MXF4 && p.acc_chunk > 0;   // (the NVFP4 kind's scale sets take the second accumulator's columns)
     // stored-byte ring (bf16 kind, conversion in the kernel)
     auto raw_full = [&](int s) { return acc_full + 40u + 8u * s; };
     auto raw_empty = [&](int s) { return acc_full + 64u + 8u * s; };
@@ -1425,6 +1425,7 @@ int gemm_linear(const LinearArgs& a, int act, float divisor) {
         if ((rc = make_map(&maps.b[1], w1.w, false, w1.n, k)) != 0) return rc;
         p.k_blocks = (p.k_steps + 3) / 4;
         p.a_k_blocks = p.k_blocks;
+        if (p.k_blocks > 4) p.acc_chunk = 4;   // (see the bf16 kind below: sums of 512 products, then f32 adds)
         const long long oc = w.rows, fr = 0;
         return launch<KIND_F8>(sw, ma, maps, p, &oc, &fr);
     }
