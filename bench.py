@@ -339,8 +339,17 @@ def main():
             print(f"[bench] fused tensor parallelism not available ({exc}); using NCCL all-reduce",
                   file=sys.stderr, flush=True)
     forward = (lambda: stack.forward_fused_tp(x_dev)) if fused_tp else (lambda: stack.forward(x_dev, m))
-    for _ in range(max(args.warmup, 3)):
+    for i in range(max(args.warmup, 3)):
         forward()
+        if i == 0 and world > 1:
+            # Every device-side wait of the sharded step gives up after two seconds; a step has hundreds of
+            # them, so a step in which they all ran out would take many minutes. Look after the first one.
+            torch.cuda.synchronize()
+            bad = torch.tensor([b.debug_status()], dtype=torch.int32, device=b.device)
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX)
+            if int(bad.item()) != 0:
+                raise SystemExit(f"a bounded device wait ran out in the first step (status {int(bad.item())}): "
+                                 "the step is not timed")
     barrier()
 
     # A step is hundreds of launches: it is captured once and replayed as one CUDA graph, as the
