@@ -713,10 +713,15 @@ def components(b, peaks, stack, args, graph=True):
             calls = [lambda v=v: b.linear_bf16(xb, v, None, m, yb=yb) for v in views]
             us, _ = _timed_cell(b, calls, graph, burst_only=True)
             us_s, clk = _timed_cell(b, calls, graph)
+            q4 = blob_of(m, k, 256.0)
+            us_q, _ = _timed_cell(b, [lambda v=v: b.linear_q4(q4, 256.0, v, None, m, yb=yb) for v in views], graph,
+                                  burst_only=True)
             out["config1_prefill_gemm_nvfp4_25600x5120_m2048"] = {
                 "burst": _tensor_cell(us, flops(m), peaks, None, note="bf16 x in: quantiser launch included; a burst of launches"),
+                "burst_fp4_blob_in": _tensor_cell(us_q, flops(m), peaks, None,
+                                                  note="the GEMM launch alone: activations arrive as the NVFP4 blob a producer wrote"),
                 "sustained": _tensor_cell(us_s, flops(m), peaks, clk, sustained=True, note="0.5 s under the power cap")}
-            del xb, yb
+            del xb, yb, q4
         if on("sweep"):
             sweep = {}
             for m in (1, 4, 16, 64, 256, 2048):
