@@ -1,5 +1,5 @@
-"""Multi-GPU checks of the fused tensor-parallel step (two GPUs, and four where the box has them;
-skipped on fewer). Ranks run as child processes with NVLS off."""
+"""Multi-GPU checks of the fused tensor-parallel step (two GPUs, and four and eight where the box
+has them; skipped on fewer). Ranks run as child processes with NVLS off."""
 import os
 import subprocess
 import sys
